@@ -1,0 +1,132 @@
+// C ABI of the surfel tracer (include/dst.h): handle life cycle, argument checks, error strings.
+#include "dst_common.cuh"
+#include <stdarg.h>
+#include <string.h>
+#include <new>
+
+static char g_global_err[512] = "";
+
+int dst_set_error(dst_handle* h, int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(h ? h->err : g_global_err, 512, fmt, ap);
+    va_end(ap);
+    return code;
+}
+void dst_global_error(const char* msg) { snprintf(g_global_err, sizeof(g_global_err), "%s", msg); }
+
+namespace {
+struct DeviceGuard {
+    int prev = -1; bool ok = true;
+    explicit DeviceGuard(int dev) { if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; } if (prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false; }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+}
+
+extern "C" {
+
+int dst_create(int device, dst_handle** out) {
+    if (!out) { dst_global_error("dst_create: out is null"); return DST_E_ARG; }
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        dst_global_error("dst_create: no CUDA device is available (this library has no CPU path)");
+        return DST_E_CUDA;
+    }
+    if (device < 0 || device >= count) { dst_global_error("dst_create: device index out of range"); return DST_E_ARG; }
+    DeviceGuard g(device);
+    if (!g.ok) { dst_global_error("dst_create: cudaSetDevice failed"); return DST_E_CUDA; }
+    dst_handle* h = new (std::nothrow) dst_handle();
+    if (!h) { dst_global_error("dst_create: out of host memory"); return DST_E_NOMEM; }
+    memset(h, 0, sizeof(*h));
+    h->device = device;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete h; dst_global_error("dst_create: cudaGetDeviceProperties failed"); return DST_E_CUDA; }
+    h->sm_count = prop.multiProcessorCount;
+    if (cudaMalloc(&h->header, 4 * (DST_HDR_FLOATS + 8)) != cudaSuccess || cudaMalloc(&h->status, 4) != cudaSuccess ||
+        cudaMemset(h->header, 0, 4 * (DST_HDR_FLOATS + 8)) != cudaSuccess || cudaMemset(h->status, 0, 4) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(h->header); cudaFree(h->status); delete h;
+        dst_global_error("dst_create: device allocation failed");
+        return DST_E_NOMEM;
+    }
+    *out = h;
+    return DST_OK;
+}
+
+int dst_destroy(dst_handle* h) {
+    if (!h) return DST_OK;
+    DeviceGuard g(h->device);
+    cudaFree(h->nodes); cudaFree(h->quads); cudaFree(h->leaf_gid); cudaFree(h->leaf_parent); cudaFree(h->arrive);
+    cudaFree(h->keys); cudaFree(h->keys_alt); cudaFree(h->vals); cudaFree(h->vals_alt); cudaFree(h->block_hist);
+    cudaFree(h->header); cudaFree(h->status); cudaFree(h->cache); cudaFree(h->arena);
+    delete h;
+    return DST_OK;
+}
+
+const char* dst_last_error(const dst_handle* h) { return h ? h->err : g_global_err; }
+
+int dst_build(dst_handle* h, const float* vertices, int64_t n_vertices, const int32_t* triangles, int64_t n_triangles,
+              int rebuild, void* stream) {
+    if (!h) return DST_E_ARG;
+    if (!vertices) return dst_set_error(h, DST_E_ARG, "vertices is null");
+    if (n_vertices <= 0 || (n_vertices & 3)) return dst_set_error(h, DST_E_ARG, "vertices must hold 4 vertices per surfel, got %lld", (long long)n_vertices);
+    if (triangles && n_triangles * 2 != n_vertices)
+        return dst_set_error(h, DST_E_ARG, "triangles must hold 2 per surfel: %lld triangles for %lld vertices", (long long)n_triangles, (long long)n_vertices);
+    DeviceGuard g(h->device);
+    if (!g.ok) return dst_set_error(h, DST_E_CUDA, "cudaSetDevice(%d) failed", h->device);
+    return dst_bvh_build_impl(h, vertices, n_vertices / 4, rebuild, (cudaStream_t)stream);
+}
+
+int dst_forward(dst_handle* h, const dst_fwd_args* args, void* stream) {
+    if (!h) return DST_E_ARG;
+    if (!args) return dst_set_error(h, DST_E_ARG, "args is null");
+    DeviceGuard g(h->device);
+    if (!g.ok) return dst_set_error(h, DST_E_CUDA, "cudaSetDevice(%d) failed", h->device);
+    return dst_forward_impl(h, args, (cudaStream_t)stream);
+}
+
+int dst_backward(dst_handle* h, const dst_bwd_args* args, void* stream) {
+    if (!h) return DST_E_ARG;
+    if (!args) return dst_set_error(h, DST_E_ARG, "args is null");
+    DeviceGuard g(h->device);
+    if (!g.ok) return dst_set_error(h, DST_E_CUDA, "cudaSetDevice(%d) failed", h->device);
+    return dst_backward_impl(h, args, (cudaStream_t)stream);
+}
+
+int dst_status(dst_handle* h, uint32_t* flags, void* stream) {
+    if (!h || !flags) return DST_E_ARG;
+    DeviceGuard g(h->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    DST_CUDA_TRY(h, cudaMemcpyAsync(flags, h->status, 4, cudaMemcpyDeviceToHost, st));
+    DST_CUDA_TRY(h, cudaMemsetAsync(h->status, 0, 4, st));
+    DST_CUDA_TRY(h, cudaStreamSynchronize(st));
+    return DST_OK;
+}
+
+int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t* device_bytes) {
+    if (!h) return DST_E_ARG;
+    if (surfels) *surfels = h->built ? h->P : 0;
+    if (nodes) *nodes = h->built ? (h->P > 1 ? h->P - 1 : 1) : 0;
+    if (device_bytes) *device_bytes = h->cap * (64 + 48 + 4 + 4 + 4 + 16 + 8) + h->hist_cap * 1024 + h->cache_cap * 64 + h->arena_cap * 4 * DST_ARENA_FLOATS;
+    return DST_OK;
+}
+
+int dst_debug_knearest(dst_handle* h, const float* ray_o, const float* ray_d, int64_t n_rays, unsigned long long* keys,
+                       int32_t* counts, int brute, void* stream) {
+    if (!h) return DST_E_ARG;
+    if (!ray_o || !ray_d || !keys || !counts) return dst_set_error(h, DST_E_ARG, "null pointer");
+    DeviceGuard g(h->device);
+    return dst_knearest_impl(h, ray_o, ray_d, n_rays, keys, counts, brute, (cudaStream_t)stream);
+}
+
+int dst_debug_quad_frames(dst_handle* h, float* out, void* stream) {
+    if (!h) return DST_E_ARG;
+    if (!out) return dst_set_error(h, DST_E_ARG, "null pointer");
+    DeviceGuard g(h->device);
+    return dst_export_frames_impl(h, out, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,153 @@
+// Shared declarations of the B200-native surfel tracer: handle, device-side views, exact-arithmetic helpers.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include "../../include/dst.h"
+
+// ---------------------------------------------------------------------------------------------
+// Hierarchy layout in HBM
+//   nodes      (P-1) x 64 B : boxes of both children + child links + parent (Aila-Laine style,
+//                             one 64-byte fetch = four 16-byte vector loads per visited node)
+//   quads      P x 48 B     : plane frame of each quad in LEAF ORDER (three 16-byte loads per test)
+//   leaf_gid   P x 4 B      : leaf position -> surfel id
+// A child link c >= 0 is an internal node, c < 0 is leaf position ~c.
+// ---------------------------------------------------------------------------------------------
+struct __align__(16) BvhNode {
+    float box[12];      // [0..2] lo of child 0, [3..5] hi of child 0, [6..8] lo of child 1, [9..11] hi of child 1
+    int c0, c1;
+    int parent;         // -1 for the root
+    int pad;
+};
+static_assert(sizeof(BvhNode) == 64, "node must be one 64-byte record");
+
+// header floats: [0..2] scene lo, [3..5] scene hi, [6] largest |coordinate|
+#define DST_HDR_FLOATS 8
+
+struct BvhView {
+    const float4* nodes;
+    const float4* quads;
+    const int* leaf_gid;
+    const float* header;
+    int P;
+};
+
+// Per-surfel shading record rebuilt at the start of every trace call (parameters change each
+// training step): rows of the tangent frame, the frame origin, opacity and scales, 64 B so that
+// one evaluated hit costs two 32-byte sectors instead of four scattered gathers.
+//   f4[0] = (R0.xyz, T.x)  f4[1] = (R1.xyz, T.y)  f4[2] = (R2.xyz, opacity)  f4[3] = (sx, sy, 0, 0)
+struct SurfelCacheView { const float4* rec; };
+
+// packed per-surfel gradient rows (16-byte aligned so that 4-float vector reductions apply):
+//   [0..3] rotation  [4..6] mean  [7] opacity  [8..10] grads3D  [11] -  [12..13] scale  [14..15] others  [16..18] colour  [19] -
+#define DST_ARENA_FLOATS 20
+
+struct dst_handle {
+    int device;
+    char err[512];
+    bool built;
+    int64_t P;            // surfels of the current hierarchy
+    int64_t cap;          // surfels the build buffers can hold
+    BvhNode* nodes;
+    float4* quads;
+    int* leaf_gid;
+    int* leaf_parent;
+    unsigned int* arrive;         // per-node arrival counters of the bottom-up pass
+    unsigned long long *keys, *keys_alt;
+    unsigned int *vals, *vals_alt;
+    unsigned int* block_hist;     // 256 x sort blocks
+    int64_t hist_cap;
+    float* header;                // DST_HDR_FLOATS floats + 8 uint bounds words
+    unsigned int* status;         // device status word
+    float4* cache; int64_t cache_cap;
+    float* arena;  int64_t arena_cap;
+    int sm_count;
+};
+
+#define DST_CUDA_TRY(h, expr)                                                                    \
+    do {                                                                                         \
+        cudaError_t e_ = (expr);                                                                 \
+        if (e_ != cudaSuccess) {                                                                 \
+            snprintf((h)->err, sizeof((h)->err), "%s failed: %s (%s:%d)", #expr,                 \
+                     cudaGetErrorString(e_), __FILE__, __LINE__);                                \
+            return DST_E_CUDA;                                                                   \
+        }                                                                                        \
+    } while (0)
+
+int dst_set_error(dst_handle* h, int code, const char* fmt, ...);
+void dst_global_error(const char* msg);
+
+// host entry points implemented in the kernel translation units
+int dst_bvh_build_impl(dst_handle* h, const float* v, int64_t P, int rebuild, cudaStream_t st);
+int dst_forward_impl(dst_handle* h, const dst_fwd_args* a, cudaStream_t st);
+int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st);
+int dst_knearest_impl(dst_handle* h, const float* ro, const float* rd, int64_t n, unsigned long long* keys,
+                      int32_t* counts, int brute, cudaStream_t st);
+int dst_prepare_cache(dst_handle* h, const dst_trace_inputs* in, cudaStream_t st);
+int dst_export_frames_impl(dst_handle* h, float* out, cudaStream_t st);
+
+#ifdef __CUDACC__
+// ---------------------------------------------------------------------------------------------
+// Exactly rounded binary32 operations. Everything that decides WHICH hits a ray sees (quad frames,
+// the ray/quad predicate, depth bookkeeping, the tangent-plane coordinates) is written with these
+// so that it is reproducible bit for bit on a CPU: one IEEE round-to-nearest per operation, fused
+// multiply-add only where xfma is written.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float xmul(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float xadd(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ float xsub(float a, float b) { return __fsub_rn(a, b); }
+__device__ __forceinline__ float xdiv(float a, float b) { return __fdiv_rn(a, b); }
+__device__ __forceinline__ float xfma(float a, float b, float c) { return __fmaf_rn(a, b, c); }
+__device__ __forceinline__ float xsqrt(float a) { return __fsqrt_rn(a); }
+__device__ __forceinline__ float xdop(float a, float b, float c, float d) { return xfma(a, b, -xmul(c, d)); }
+__device__ __forceinline__ float xdot3(float ax, float ay, float az, float bx, float by, float bz) {
+    return xfma(az, bz, xfma(ay, by, xmul(ax, bx)));
+}
+// the reference's dot(): ((ax*bx + ay*by) + az*bz), each operation rounded
+__device__ __forceinline__ float rdot3(float ax, float ay, float az, float bx, float by, float bz) {
+    return xadd(xadd(xmul(ax, bx), xmul(ay, by)), xmul(az, bz));
+}
+
+struct QuadFrame { float p0x, p0y, p0z, nx, ny, nz, wux, wuy, wuz, wvx, wvy, wvz; };
+
+// Plane frame of the quad (v0, v1, v2, v3): corner p0 = v1, edges eu = v3 - v1, ev = v0 - v1,
+// n = eu x ev, wu = (ev x n)/(n.n), wv = (n x eu)/(n.n).
+__device__ __forceinline__ QuadFrame make_quad_frame(const float* v) {
+    QuadFrame q;
+    q.p0x = v[3]; q.p0y = v[4]; q.p0z = v[5];
+    const float eux = xsub(v[9], v[3]), euy = xsub(v[10], v[4]), euz = xsub(v[11], v[5]);
+    const float evx = xsub(v[0], v[3]), evy = xsub(v[1], v[4]), evz = xsub(v[2], v[5]);
+    q.nx = xdop(euy, evz, euz, evy); q.ny = xdop(euz, evx, eux, evz); q.nz = xdop(eux, evy, euy, evx);
+    const float nn = xdot3(q.nx, q.ny, q.nz, q.nx, q.ny, q.nz);
+    const float cux = xdop(evy, q.nz, evz, q.ny), cuy = xdop(evz, q.nx, evx, q.nz), cuz = xdop(evx, q.ny, evy, q.nx);
+    const float cvx = xdop(q.ny, euz, q.nz, euy), cvy = xdop(q.nz, eux, q.nx, euz), cvz = xdop(q.nx, euy, q.ny, eux);
+    q.wux = xdiv(cux, nn); q.wuy = xdiv(cuy, nn); q.wuz = xdiv(cuz, nn);
+    q.wvx = xdiv(cvx, nn); q.wvy = xdiv(cvy, nn); q.wvz = xdiv(cvz, nn);
+    return q;
+}
+
+#define DST_T_MAX 1e16f
+
+// Ray/quad predicate. Returns true with t in [0, 1e16) and tri = 0/1 (which triangle of the quad,
+// by the side of the shared diagonal). `tcut`: hits with t > tcut are of no interest to the caller
+// (they cannot enter a full k-buffer) and are rejected before the in-quad test.
+__device__ __forceinline__ bool ray_quad(const float4 qa, const float4 qb, const float4 qc,
+                                         float ox, float oy, float oz, float dx, float dy, float dz,
+                                         float tcut, float& t, int& tri) {
+    const float rx = xsub(qa.x, ox), ry = xsub(qa.y, oy), rz = xsub(qa.z, oz);
+    const float nx = qa.w, ny = qb.x, nz = qb.y;
+    const float b = xdot3(nx, ny, nz, dx, dy, dz);
+    if (!(b != 0.0f)) return false;
+    const float a = xdot3(nx, ny, nz, rx, ry, rz);
+    float tt = xdiv(a, b);
+    if (!(tt >= 0.0f && tt < DST_T_MAX)) return false;
+    if (tt > tcut) return false;
+    tt = xadd(tt, 0.0f);
+    const float hx = xfma(tt, dx, -rx), hy = xfma(tt, dy, -ry), hz = xfma(tt, dz, -rz);
+    const float u = xdot3(qb.z, qb.w, qc.x, hx, hy, hz);
+    const float w = xdot3(qc.y, qc.z, qc.w, hx, hy, hz);
+    if (!(u >= 0.0f && u <= 1.0f && w >= 0.0f && w <= 1.0f)) return false;
+    t = tt; tri = (u > w) ? 1 : 0;
+    return true;
+}
+#endif  // __CUDACC__

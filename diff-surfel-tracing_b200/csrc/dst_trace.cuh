@@ -1,0 +1,261 @@
+// Device code shared by the forward and backward trace kernels: the k-nearest hierarchy walk that
+// replaces optixTrace + __anyhit__ot (optix_tracer/forward.cu:117-132, 481-525), the ray/ray-grid
+// mapping, and spherical-harmonics colour.
+#pragma once
+#include "dst_common.cuh"
+
+#define DST_STACK 96                 // >= depth bound of a Karras tree over 63-bit keys + 32-bit index tie-breaks
+#define DST_MAX_CHUNKS 4096          // bound on enumerations per ray segment (the reference loops without one)
+#define DST_MAX_INTERSECTION 256     // optix_tracer/config.h:23
+#define DST_PAD_FACTOR 4e-6f         // box padding per unit of coordinate magnitude, see knearest()
+
+struct TraceCounters { unsigned long long segs, enums, nodes, quads, evals, contribs; };
+
+__device__ __forceinline__ unsigned long long make_key(float t, unsigned int pidx) {
+    return ((unsigned long long)__float_as_uint(t) << 32) | pidx;
+}
+__device__ __forceinline__ float hitkey_t(unsigned long long k) { return __uint_as_float((unsigned int)(k >> 32)); }
+
+// The DST_CHUNK smallest (t, primitive id) hits with 0 <= t < 1e16 from origin o, ascending, in
+// kb[0], kb[KS], kb[2 KS], ... (a column of a shared-memory array). Returns min(#hits, DST_CHUNK).
+//
+// Differences from the reference's scheme (every hit on the whole ray goes through an any-hit
+// program that insertion-sorts into a 16-slot buffer): nodes and quads whose nearest possible t
+// lies beyond the current 16th hit are culled, so the cost is that of a k-nearest query instead
+// of growing with the number of hits behind the chunk.
+//
+// Conservativeness: a hit accepted by ray_quad() lies on the ray within ~20 ulp(M) of the quad,
+// M = |o|_inf + largest |coordinate| of the scene. Child boxes are therefore padded by
+// DST_PAD_FACTOR * M through the per-ray plane offsets (no extra work per node), which also
+// covers the rounding of the slab arithmetic itself.
+template <bool BRUTE, bool COUNT, int KS>
+__device__ __forceinline__ int knearest(const BvhView& bvh, float ox, float oy, float oz, float dx, float dy, float dz,
+                                        unsigned long long* kb, unsigned int* status, TraceCounters& tc) {
+    int n = 0;
+    float kmax = DST_T_MAX;
+    if (bvh.P <= 0) return 0;
+
+    auto offer = [&](int pos) {
+        const float4* qp = bvh.quads + 3 * (size_t)pos;
+        const float4 qa = __ldg(qp), qb = __ldg(qp + 1), qc = __ldg(qp + 2);
+        if (COUNT) tc.quads++;
+        float t; int tri;
+        if (!ray_quad(qa, qb, qc, ox, oy, oz, dx, dy, dz, kmax, t, tri)) return;
+        const unsigned int gid = (unsigned int)__ldg(bvh.leaf_gid + pos);
+        const unsigned long long key = make_key(t, 2u * gid + (unsigned int)tri);
+        if (n == DST_CHUNK) { if (key >= kb[(DST_CHUNK - 1) * KS]) return; n = DST_CHUNK - 1; }
+        int j = n;
+        while (j > 0) {
+            const unsigned long long prev = kb[(j - 1) * KS];
+            if (prev <= key) break;
+            kb[j * KS] = prev; j--;
+        }
+        kb[j * KS] = key;
+        n++;
+        if (n == DST_CHUNK) kmax = hitkey_t(kb[(DST_CHUNK - 1) * KS]);
+    };
+
+    if (BRUTE) {
+        for (int pos = 0; pos < bvh.P; pos++) offer(pos);
+        return n;
+    }
+
+    const float omax = fmaxf(fabsf(ox), fmaxf(fabsf(oy), fabsf(oz)));
+    if (!(omax < INFINITY)) return 0;
+    const float pad = DST_PAD_FACTOR * (omax + __ldg(bvh.header + 6)) + 1e-30f;
+    const float sdx = fabsf(dx) < 1e-20f ? copysignf(1e-20f, dx) : dx;
+    const float sdy = fabsf(dy) < 1e-20f ? copysignf(1e-20f, dy) : dy;
+    const float sdz = fabsf(dz) < 1e-20f ? copysignf(1e-20f, dz) : dz;
+    const float ix = 1.0f / sdx, iy = 1.0f / sdy, iz = 1.0f / sdz;
+    const bool px = !(sdx < 0.0f), py = !(sdy < 0.0f), pz = !(sdz < 0.0f);
+    // entry plane t = near * i - on, exit plane t = far * i - of, with the padding folded in
+    const float onx = fmaf(ox, ix, pad * fabsf(ix)), ofx = fmaf(ox, ix, -pad * fabsf(ix));
+    const float ony = fmaf(oy, iy, pad * fabsf(iy)), ofy = fmaf(oy, iy, -pad * fabsf(iy));
+    const float onz = fmaf(oz, iz, pad * fabsf(iz)), ofz = fmaf(oz, iz, -pad * fabsf(iz));
+
+    unsigned long long stack[DST_STACK];
+    int sp = 0;
+    int cur = 0;
+    while (true) {
+        if (cur >= 0) {
+            const float4* np = bvh.nodes + 4 * (size_t)cur;
+            const float4 a = __ldg(np), b = __ldg(np + 1), c = __ldg(np + 2);
+            const int4 lk = __ldg(reinterpret_cast<const int4*>(np + 3));
+            if (COUNT) tc.nodes++;
+            // child 0: lo (a.x a.y a.z) hi (a.w b.x b.y); child 1: lo (b.z b.w c.x) hi (c.y c.z c.w)
+            const float n0x = px ? a.x : a.w, f0x = px ? a.w : a.x;
+            const float n0y = py ? a.y : b.x, f0y = py ? b.x : a.y;
+            const float n0z = pz ? a.z : b.y, f0z = pz ? b.y : a.z;
+            const float n1x = px ? b.z : c.y, f1x = px ? c.y : b.z;
+            const float n1y = py ? b.w : c.z, f1y = py ? c.z : b.w;
+            const float n1z = pz ? c.x : c.w, f1z = pz ? c.w : c.x;
+            const float tn0 = fmaxf(fmaxf(fmaf(n0x, ix, -onx), fmaf(n0y, iy, -ony)), fmaxf(fmaf(n0z, iz, -onz), 0.0f));
+            const float tf0 = fminf(fminf(fmaf(f0x, ix, -ofx), fmaf(f0y, iy, -ofy)), fmaf(f0z, iz, -ofz));
+            const float tn1 = fmaxf(fmaxf(fmaf(n1x, ix, -onx), fmaf(n1y, iy, -ony)), fmaxf(fmaf(n1z, iz, -onz), 0.0f));
+            const float tf1 = fminf(fminf(fmaf(f1x, ix, -ofx), fmaf(f1y, iy, -ofy)), fmaf(f1z, iz, -ofz));
+            const bool h0 = (tn0 <= tf0) && (tn0 <= kmax);
+            const bool h1 = (tn1 <= tf1) && (tn1 <= kmax);
+            if (h0 && h1) {
+                const bool swap = tn1 < tn0;
+                const int cn = swap ? lk.y : lk.x, cf = swap ? lk.x : lk.y;
+                const float tfar = swap ? tn0 : tn1;
+                if (sp < DST_STACK) stack[sp++] = ((unsigned long long)__float_as_uint(tfar) << 32) | (unsigned int)cf;
+                else atomicOr(status, DST_STATUS_STACK_OVERFLOW);
+                cur = cn;
+                continue;
+            }
+            if (h0) { cur = lk.x; continue; }
+            if (h1) { cur = lk.y; continue; }
+        } else {
+            offer(~cur);
+        }
+        // pop the next subtree that can still hold a hit nearer than the 16th
+        bool found = false;
+        while (sp > 0) {
+            const unsigned long long e = stack[--sp];
+            if (__uint_as_float((unsigned int)(e >> 32)) <= kmax) { cur = (int)(unsigned int)e; found = true; break; }
+        }
+        if (!found) break;
+    }
+    return n;
+}
+
+// Ray index of a thread. Image-like grids (H >= 16) are walked in 8x4 pixel tiles per warp so the
+// rays of a warp stay close in the hierarchy; batched ray lists (few rows) are walked linearly.
+// The reference's launch puts consecutive threads on consecutive ROWS (optix_tracer/forward.cu:433).
+__device__ __forceinline__ long long ray_of_thread(int H, int W, bool tiled) {
+    if (!tiled) {
+        const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+        return r < (long long)H * W ? r : -1;
+    }
+    const int tiles_x = (W + 15) >> 4;
+    const int bx = blockIdx.x % tiles_x, by = blockIdx.x / tiles_x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int x = bx * 16 + (warp & 1) * 8 + (lane & 7);
+    const int y = by * 8 + (warp >> 1) * 4 + (lane >> 3);
+    if (x >= W || y >= H) return -1;
+    return (long long)y * W + x;
+}
+
+// SH constants, optix_tracer/auxiliary.h:26-43
+#define SHC0 0.28209479177387814f
+#define SHC1 0.4886025119029199f
+#define SHC2_0 1.0925484305920792f
+#define SHC2_1 -1.0925484305920792f
+#define SHC2_2 0.31539156525252005f
+#define SHC2_3 -1.0925484305920792f
+#define SHC2_4 0.5462742152960396f
+#define SHC3_0 -0.5900435899266435f
+#define SHC3_1 2.890611442640554f
+#define SHC3_2 -0.4570457994644658f
+#define SHC3_3 0.3731763325901154f
+#define SHC3_4 -0.4570457994644658f
+#define SHC3_5 1.445305721320277f
+#define SHC3_6 -0.5900435899266435f
+
+// loads the first 3*ncoef floats of a row of SH coefficients; vectorised when the row is 16-byte aligned
+__device__ __forceinline__ void load_sh_row(const float* __restrict__ row, int nfloat, bool aligned, float* c) {
+    if (aligned) {
+        const float4* r4 = reinterpret_cast<const float4*>(row);
+        const int nv = nfloat >> 2;
+#pragma unroll
+        for (int i = 0; i < 12; i++) {
+            if (i < nv) { const float4 q = __ldg(r4 + i); c[4 * i] = q.x; c[4 * i + 1] = q.y; c[4 * i + 2] = q.z; c[4 * i + 3] = q.w; }
+        }
+#pragma unroll
+        for (int i = 0; i < 48; i++) if (i >= (nv << 2) && i < nfloat) c[i] = __ldg(row + i);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 48; i++) if (i < nfloat) c[i] = __ldg(row + i);
+    }
+}
+
+// Signed basis factors b[j] such that the reference's expression tree for the SH colour
+// (optix_tracer/forward.cu:18-58) is r = b0*sh0; r = r + b[j]*sh[j] (j = 1..); r + 0.5; max(r, 0),
+// one rounding per operation, in that order.
+__device__ __forceinline__ void sh_basis(int deg, float x, float y, float z, float* b) {
+    b[0] = SHC0;
+    if (deg > 0) {
+        b[1] = -xmul(SHC1, y); b[2] = xmul(SHC1, z); b[3] = -xmul(SHC1, x);
+        if (deg > 1) {
+            const float xx = xmul(x, x), yy = xmul(y, y), zz = xmul(z, z), xy = xmul(x, y), yz = xmul(y, z), xz = xmul(x, z);
+            b[4] = xmul(SHC2_0, xy); b[5] = xmul(SHC2_1, yz);
+            b[6] = xmul(SHC2_2, xsub(xsub(xmul(2.0f, zz), xx), yy));
+            b[7] = xmul(SHC2_3, xz); b[8] = xmul(SHC2_4, xsub(xx, yy));
+            if (deg > 2) {
+                b[9] = xmul(xmul(SHC3_0, y), xsub(xmul(3.0f, xx), yy));
+                b[10] = xmul(xmul(SHC3_1, xy), z);
+                b[11] = xmul(xmul(SHC3_2, y), xsub(xsub(xmul(4.0f, zz), xx), yy));
+                b[12] = xmul(xmul(SHC3_3, z), xsub(xsub(xmul(2.0f, zz), xmul(3.0f, xx)), xmul(3.0f, yy)));
+                b[13] = xmul(xmul(SHC3_4, x), xsub(xsub(xmul(4.0f, zz), xx), yy));
+                b[14] = xmul(xmul(SHC3_5, z), xsub(xx, yy));
+                b[15] = xmul(xmul(SHC3_6, x), xsub(xx, xmul(3.0f, yy)));
+            }
+        }
+    }
+}
+
+// unclamped colour channel ch (0..2) from the loaded coefficient row
+__device__ __forceinline__ float sh_channel(int ncoef, const float* b, const float* c, int ch) {
+    float r = xmul(b[0], c[ch]);
+#pragma unroll
+    for (int j = 1; j < 16; j++) if (j < ncoef) r = xadd(r, xmul(b[j], c[3 * j + ch]));
+    return xadd(r, 0.5f);
+}
+
+// exp for x <= 0 as a fixed sequence of rounded operations (Cody-Waite reduction, degree-7 Taylor
+// polynomial, exact power-of-two scaling): reproducible bit for bit on a CPU, about 1 ulp from a
+// correctly rounded exp. The falloff G = exp(-rho/2) decides which hits contribute
+// (optix_tracer/forward.cu:247-252), so it belongs to the exactly specified part.
+__device__ __forceinline__ float pexp(float x) {
+    if (!(x >= -87.0f)) return (x != x) ? x : 0.0f;
+    if (x > 88.0f) x = 88.0f;
+    const float kf = xsub(xadd(xmul(x, 1.44269504088896341f), 12582912.0f), 12582912.0f);
+    float r = xfma(kf, -0.693145751953125f, x);
+    r = xfma(kf, -1.42860682030941723212e-6f, r);
+    float p = 0.0001984126984126984f;
+    p = xfma(p, r, 0.001388888888888889f);
+    p = xfma(p, r, 0.008333333333333333f);
+    p = xfma(p, r, 0.041666666666666664f);
+    p = xfma(p, r, 0.16666666666666666f);
+    p = xfma(p, r, 0.5f);
+    p = xfma(p, r, 1.0f);
+    p = xfma(p, r, 1.0f);
+    return xmul(p, __int_as_float(((int)kf + 127) << 23));
+}
+
+// Everything the compositing loop needs to know about one gathered hit.
+struct SlotEval {
+    float dpt, X, Y, Z;       // depth along the segment and world position
+    float u, v;               // tangent-plane coordinates in units of the scales
+    float nsign;              // +1 / -1: the normal is flipped toward the ray (DUAL_VISIABLE)
+    float G, alpha;
+    float4 r0, r1, r2, r3;    // the surfel's shading record
+};
+
+// Steps of optix_tracer/forward.cu:211-249 for one k-buffer entry, in the reference's operation
+// order with one rounding per operation: depth, position, compute_transmat_uv (63-90), the
+// visibility / near-depth / support tests and alpha. Returns false where the reference `continue`s.
+// Shared by the forward and backward kernels so that the retrace takes identical decisions.
+__device__ __forceinline__ bool eval_slot(unsigned long long key, float offset, float sox, float soy, float soz,
+                                          float sdx, float sdy, float sdz, float min_depth, const float4* __restrict__ cache,
+                                          int gidx, SlotEval& e) {
+    e.dpt = xadd(hitkey_t(key), offset);
+    e.X = xadd(sox, xmul(e.dpt, sdx)); e.Y = xadd(soy, xmul(e.dpt, sdy)); e.Z = xadd(soz, xmul(e.dpt, sdz));
+    const float4* rec = cache + 4 * (size_t)gidx;
+    e.r0 = __ldg(rec); e.r1 = __ldg(rec + 1); e.r2 = __ldg(rec + 2); e.r3 = __ldg(rec + 3);
+    const float u1 = xadd(rdot3(e.r0.x, e.r0.y, e.r0.z, e.X, e.Y, e.Z), -e.r0.w);
+    const float v1 = xadd(rdot3(e.r1.x, e.r1.y, e.r1.z, e.X, e.Y, e.Z), -e.r1.w);
+    e.u = xdiv(u1, e.r3.x); e.v = xdiv(v1, e.r3.y);
+    const float rho3d = xadd(xmul(e.u, e.u), xmul(e.v, e.v));
+    const float cosv = -rdot3(sdx, sdy, sdz, e.r2.x, e.r2.y, e.r2.z);
+    if (cosv == 0.0f) return false;
+    e.nsign = cosv > 0.0f ? 1.0f : -1.0f;
+    if (e.dpt < min_depth) return false;
+    const float power = -0.5f * rho3d;
+    if (power > 0.0f) return false;
+    e.G = pexp(power);
+    e.alpha = fminf(0.99f, xmul(e.r2.w, e.G));
+    if (e.alpha < 1.0f / 255.0f) return false;
+    return true;
+}

@@ -1,0 +1,289 @@
+"""Binding of libdst_b200.so with the call surface of the reference's extension module.
+
+Mirrors ext.cpp:7-12 of the reference: a state object plus build_acceleration_structure,
+trace_surfels and trace_surfels_backward with the same argument order and return tuples
+(trace_surfels.h:10-83). Tensors are allocated here with torch and handed to the C ABI
+(include/dst.h) as raw device pointers; all work is enqueued on torch's current CUDA stream.
+There is no CPU path: loading fails loudly when the library is missing and every call fails when
+no CUDA device is present.
+"""
+import ctypes as C
+import os
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(os.path.dirname(_PKG), "libdst_b200.so")
+
+NUM_CHANNELS = 3
+AUX_CHANNELS = 2
+MID_CHANNELS = 16
+
+
+class _TraceInputs(C.Structure):
+    _fields_ = ([(n, C.c_int32) for n in ("H", "W", "P", "sh_degree", "sh_coeffs", "max_trace_depth", "mid_stride", "start_from_first")]
+                + [("specular_threshold", C.c_float), ("scale_modifier", C.c_float)]
+                + [(n, C.c_void_p) for n in ("ray_o", "ray_d", "vertices", "background", "means3D", "shs", "colors_precomp",
+                                             "others_precomp", "opacities", "scales", "rotations")])
+
+
+class _FwdArgs(C.Structure):
+    _fields_ = ([("inp", _TraceInputs), ("training", C.c_int32), ("hit_cap", C.c_int32)]
+                + [(n, C.c_void_p) for n in ("out_rgb", "out_dpt", "out_acc", "out_norm", "out_dist", "out_aux", "mid_val", "a_weights",
+                                             "hit_log", "hit_cnt", "counters")])
+
+
+class _BwdArgs(C.Structure):
+    _fields_ = ([("inp", _TraceInputs)]
+                + [(n, C.c_void_p) for n in ("out_rgb", "out_dpt", "out_acc", "out_norm", "out_dist", "out_aux", "mid_val",
+                                             "dL_drgb", "dL_ddpt", "dL_dacc", "dL_dnorm", "dL_ddist", "dL_daux",
+                                             "dL_dray_o", "dL_dray_d", "dL_dmeans3D", "dL_dgrads3D", "dL_dshs", "dL_dcolors",
+                                             "dL_dothers", "dL_dopacities", "dL_dscales", "dL_drotations", "counters")])
+
+
+_lib = None
+
+
+def lib():
+    """Loads the CUDA library on first use; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            raise ImportError(f"{_LIB_PATH} not found: build it with `python diff-surfel-tracing_b200/build.py` "
+                              "(this package has no CPU or eager fallback)")
+        l = C.CDLL(_LIB_PATH)
+        l.dst_create.argtypes = [C.c_int, C.POINTER(C.c_void_p)]
+        l.dst_destroy.argtypes = [C.c_void_p]
+        l.dst_last_error.argtypes = [C.c_void_p]
+        l.dst_last_error.restype = C.c_char_p
+        l.dst_build.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]
+        l.dst_forward.argtypes = [C.c_void_p, C.POINTER(_FwdArgs), C.c_void_p]
+        l.dst_backward.argtypes = [C.c_void_p, C.POINTER(_BwdArgs), C.c_void_p]
+        l.dst_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), C.c_void_p]
+        l.dst_bvh_info.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
+        l.dst_debug_knearest.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+        l.dst_debug_quad_frames.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        _lib = l
+    return _lib
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(state, rc):
+    if rc != 0:
+        msg = lib().dst_last_error(state.handle if state is not None else None)
+        raise RuntimeError((msg or b"unknown error").decode())
+
+
+def _cuda_f32(t, name):
+    """Contiguous float32 CUDA storage of `t`, 16-byte aligned (the kernels use vector loads)."""
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")          # CHECK_INPUT, trace_surfels.cpp:23-24
+    if t.dtype != torch.float32:
+        raise RuntimeError(f"{name} must be float32")
+    t = t.contiguous()
+    if t.data_ptr() % 16 != 0:
+        t = t.clone()
+    return t
+
+
+def _ptr(t):
+    return None if t is None or t.numel() == 0 else t.data_ptr()
+
+
+class OptiXStateWrapper:
+    """Tracer state for the current CUDA device (name kept from the reference, ext.cpp:8).
+
+    The constructor argument (the reference's package directory holding its PTX files,
+    optix_wrapper.cpp:166-204) is accepted and ignored: nothing is compiled at run time.
+    """
+
+    def __init__(self, pkg_dir: str = ""):
+        if not torch.cuda.is_available():
+            raise RuntimeError("diff_surfel_tracing needs a CUDA device; there is no CPU path")
+        self.device = torch.cuda.current_device()
+        h = C.c_void_p()
+        rc = lib().dst_create(self.device, C.byref(h))
+        if rc != 0:
+            raise RuntimeError(lib().dst_last_error(None).decode())
+        self.handle = h
+        self._keep = None
+
+    def __del__(self):
+        try:
+            if getattr(self, "handle", None):
+                lib().dst_destroy(self.handle)
+                self.handle = None
+        except Exception:
+            pass
+
+    def status(self):
+        """Synchronises and returns (then clears) the device status bits (DST_STATUS_* of dst.h)."""
+        f = C.c_uint32(0)
+        _check(self, lib().dst_status(self.handle, C.byref(f), _stream()))
+        return f.value
+
+    def info(self):
+        a, b, c = C.c_int64(), C.c_int64(), C.c_int64()
+        _check(self, lib().dst_bvh_info(self.handle, C.byref(a), C.byref(b), C.byref(c)))
+        return dict(surfels=a.value, nodes=b.value, device_bytes=c.value)
+
+
+def build_acceleration_structure(state, vertices, triangles, rebuild):
+    """trace_surfels.cpp:36-159: (Nv, 3) float vertices, (Nt, 3) int32 triangles, rebuild > 0 builds, 0 refits."""
+    if vertices.dim() != 2 or vertices.size(1) != 3:
+        raise RuntimeError("vertices must have dimensions (num_vertices, 3)")
+    if triangles is not None and (triangles.dim() != 2 or triangles.size(1) != 3):
+        raise RuntimeError("triangles must have dimensions (num_triangles, 3)")
+    v = _cuda_f32(vertices, "vertices")
+    if triangles is not None:
+        if not triangles.is_cuda:
+            raise RuntimeError("triangles must be a CUDA tensor")
+        if triangles.dtype != torch.int32:
+            raise RuntimeError("triangles must be int32")
+        triangles = triangles.contiguous()
+    nt = 0 if triangles is None else triangles.size(0)
+    rc = lib().dst_build(state.handle, v.data_ptr(), v.size(0), _ptr(triangles), nt, int(rebuild), _stream())
+    _check(state, rc)
+    state._keep = (v, triangles)      # the build kernels read them asynchronously on the current stream
+
+
+def _inputs(state, start_from_first, ray_o, ray_d, vertices, background, means3D, shs, degree, colors_precomp,
+            others_precomp, opacities, scales, scale_modifier, rotations, max_trace_depth, specular_threshold):
+    if means3D.dim() != 2 or means3D.size(1) != 3:
+        raise RuntimeError("means3D must have dimensions (num_points, 3)")
+    if ray_o.dim() != 3 or ray_o.size(2) != 3 or ray_o.shape != ray_d.shape:
+        raise RuntimeError("ray_o and ray_d must have dimensions (H, W, 3)")
+    keep = dict(ray_o=_cuda_f32(ray_o, "ray_o"), ray_d=_cuda_f32(ray_d, "ray_d"), vertices=_cuda_f32(vertices, "vertices"),
+                background=_cuda_f32(background, "background"), means3D=_cuda_f32(means3D, "means3D"),
+                shs=_cuda_f32(shs, "shs"), colors_precomp=_cuda_f32(colors_precomp, "colors_precomp"),
+                others_precomp=_cuda_f32(others_precomp, "others_precomp"), opacities=_cuda_f32(opacities, "opacities"),
+                scales=_cuda_f32(scales, "scales"), rotations=_cuda_f32(rotations, "rotations"))
+    if keep["scales"].numel() == 0 or keep["rotations"].numel() == 0:
+        raise RuntimeError("scales and rotations are required (a precomputed covariance is never read by the tracer)")
+    i = _TraceInputs()
+    i.H, i.W, i.P = ray_o.size(0), ray_o.size(1), means3D.size(0)
+    i.sh_degree = int(degree)
+    i.sh_coeffs = keep["shs"].size(1) if keep["shs"].numel() != 0 else 0
+    i.max_trace_depth = int(max_trace_depth)
+    i.mid_stride = MID_CHANNELS * max(2, int(max_trace_depth) + 1)
+    i.start_from_first = int(bool(start_from_first))
+    i.specular_threshold = float(specular_threshold)
+    i.scale_modifier = float(scale_modifier)
+    for n in ("ray_o", "ray_d", "vertices", "background", "means3D", "shs", "colors_precomp", "others_precomp",
+              "opacities", "scales", "rotations"):
+        setattr(i, n, _ptr(keep[n]))
+    return i, keep
+
+
+def trace_surfels(state, training, start_from_first, ray_o, ray_d, vertices, background, means3D, shs, degree,
+                  colors_precomp, others_precomp, opacities, scales, scale_modifier, rotations, transMat_precomp,
+                  viewmatrix, projmatrix, campos, prefiltered, debug, max_trace_depth, specular_threshold,
+                  _diag=None):
+    """trace_surfels.cpp:162-304. Returns out_rgb, out_dpt, out_acc, out_norm, out_dist, out_aux, mid_val, a_weights.
+
+    `mid_val` has 16 * max(2, max_trace_depth + 1) channels (the reference is compiled for one bounce
+    and always returns 32). `_diag`, if a dict, receives per-ray hit logs and traversal counters.
+    """
+    i, keep = _inputs(state, start_from_first, ray_o, ray_d, vertices, background, means3D, shs, degree, colors_precomp,
+                      others_precomp, opacities, scales, scale_modifier, rotations, max_trace_depth, specular_threshold)
+    H, W, P = i.H, i.W, i.P
+    dev = means3D.device
+    f32 = dict(dtype=torch.float32, device=dev)
+    out_rgb = torch.empty((H, W, NUM_CHANNELS), **f32)
+    out_dpt = torch.empty((H, W, 1), **f32)
+    out_acc = torch.empty((H, W, 1), **f32)
+    out_norm = torch.empty((H, W, 3), **f32)
+    out_dist = torch.empty((H, W, 3), **f32)
+    out_aux = torch.empty((H, W, AUX_CHANNELS), **f32)
+    mid_val = torch.empty((H, W, i.mid_stride), **f32)
+    a_weights = torch.empty((P, 1), **f32) if training else None
+    a = _FwdArgs()
+    a.inp = i
+    a.training = int(bool(training))
+    a.out_rgb, a.out_dpt, a.out_acc, a.out_norm = out_rgb.data_ptr(), out_dpt.data_ptr(), out_acc.data_ptr(), out_norm.data_ptr()
+    a.out_dist, a.out_aux, a.mid_val = out_dist.data_ptr(), out_aux.data_ptr(), mid_val.data_ptr()
+    a.a_weights = _ptr(a_weights)
+    if _diag is not None:
+        cap = int(_diag.get("hit_cap", 0))
+        if cap:
+            _diag["hit_log"] = torch.full((H * W, cap), -1, dtype=torch.int32, device=dev)
+            _diag["hit_cnt"] = torch.zeros((H * W,), dtype=torch.int32, device=dev)
+            a.hit_cap, a.hit_log, a.hit_cnt = cap, _diag["hit_log"].data_ptr(), _diag["hit_cnt"].data_ptr()
+        _diag["counters"] = torch.zeros((8,), dtype=torch.int64, device=dev)
+        a.counters = _diag["counters"].data_ptr()
+    _check(state, lib().dst_forward(state.handle, C.byref(a), _stream()))
+    return out_rgb, out_dpt, out_acc, out_norm, out_dist, out_aux, mid_val, a_weights
+
+
+def trace_surfels_backward(state, start_from_first, ray_o, ray_d, vertices, background, means3D, shs, degree, colors_precomp,
+                           others_precomp, opacities, scales, scale_modifier, rotations, transMat_precomp, viewmatrix,
+                           projmatrix, campos, prefiltered, debug, max_trace_depth, specular_threshold,
+                           out_rgb, out_dpt, out_acc, out_norm, out_dist, out_aux, mid_val,
+                           dL_drgb, dL_ddpt, dL_dacc, dL_dnorm, dL_ddist, dL_daux, _diag=None):
+    """trace_surfels.cpp:307-464. Returns the 12 gradients in the reference's order:
+    ray_o, ray_d, means3D, grads3D, grads3D_abs (zeros), shs, colors_precomp, others_precomp,
+    opacities, scales, rotations, transMat_precomp (zeros)."""
+    i, keep = _inputs(state, start_from_first, ray_o, ray_d, vertices, background, means3D, shs, degree, colors_precomp,
+                      others_precomp, opacities, scales, scale_modifier, rotations, max_trace_depth, specular_threshold)
+    H, W, P, M = i.H, i.W, i.P, i.sh_coeffs
+    if mid_val.size(-1) != i.mid_stride:
+        raise RuntimeError(f"mid_val must have {i.mid_stride} channels for max_trace_depth={max_trace_depth}")
+    dev = means3D.device
+    f32 = dict(dtype=torch.float32, device=dev)
+    sv = [_cuda_f32(t, n) for t, n in ((out_rgb, "out_rgb"), (out_dpt, "out_dpt"), (out_acc, "out_acc"), (out_norm, "out_norm"),
+                                         (out_dist, "out_dist"), (out_aux, "out_aux"), (mid_val, "mid_val"))]
+
+    def up(g, shape, name):
+        if g is None:
+            return torch.zeros(shape, **f32)
+        return _cuda_f32(g.expand(shape) if g.shape != torch.Size(shape) else g, name)
+
+    ug = [up(dL_drgb, (H, W, 3), "dL_drgb"), up(dL_ddpt, (H, W, 1), "dL_ddpt"), up(dL_dacc, (H, W, 1), "dL_dacc"),
+          up(dL_dnorm, (H, W, 3), "dL_dnorm"), up(dL_ddist, (H, W, 1), "dL_ddist"), up(dL_daux, (H, W, 2), "dL_daux")]
+    g_ray_o = torch.empty((H, W, 3), **f32)
+    g_ray_d = torch.empty((H, W, 3), **f32)
+    g_means = torch.empty((P, 3), **f32)
+    g_g3d = torch.empty((P, 3), **f32)
+    g_g3d_abs = torch.zeros((P, 3), **f32)
+    g_shs = torch.empty((P, M, 3), **f32)
+    g_colors = torch.empty((P, NUM_CHANNELS), **f32)
+    g_others = torch.empty((P, AUX_CHANNELS), **f32)
+    g_opac = torch.empty((P, 1), **f32)
+    g_scales = torch.empty((P, 2), **f32)
+    g_rot = torch.empty((P, 4), **f32)
+    g_trans = torch.zeros((P, 9), **f32)
+    a = _BwdArgs()
+    a.inp = i
+    (a.out_rgb, a.out_dpt, a.out_acc, a.out_norm, a.out_dist, a.out_aux, a.mid_val) = [t.data_ptr() for t in sv]
+    (a.dL_drgb, a.dL_ddpt, a.dL_dacc, a.dL_dnorm, a.dL_ddist, a.dL_daux) = [t.data_ptr() for t in ug]
+    a.dL_dray_o, a.dL_dray_d, a.dL_dmeans3D, a.dL_dgrads3D = g_ray_o.data_ptr(), g_ray_d.data_ptr(), g_means.data_ptr(), g_g3d.data_ptr()
+    a.dL_dshs = _ptr(g_shs)
+    a.dL_dcolors, a.dL_dothers, a.dL_dopacities = g_colors.data_ptr(), g_others.data_ptr(), g_opac.data_ptr()
+    a.dL_dscales, a.dL_drotations = g_scales.data_ptr(), g_rot.data_ptr()
+    if _diag is not None:
+        _diag["counters"] = torch.zeros((8,), dtype=torch.int64, device=dev)
+        a.counters = _diag["counters"].data_ptr()
+    _check(state, lib().dst_backward(state.handle, C.byref(a), _stream()))
+    return g_ray_o, g_ray_d, g_means, g_g3d, g_g3d_abs, g_shs, g_colors, g_others, g_opac, g_scales, g_rot, g_trans
+
+
+def debug_knearest(state, ray_o, ray_d, brute=False):
+    """The 16 nearest hits of each ray (one enumeration): (keys (n,16) int64 bit patterns, counts (n,))."""
+    ro, rd = _cuda_f32(ray_o.reshape(-1, 3), "ray_o"), _cuda_f32(ray_d.reshape(-1, 3), "ray_d")
+    n = ro.size(0)
+    keys = torch.zeros((n, 16), dtype=torch.int64, device=ro.device)
+    counts = torch.zeros((n,), dtype=torch.int32, device=ro.device)
+    _check(state, lib().dst_debug_knearest(state.handle, ro.data_ptr(), rd.data_ptr(), n, keys.data_ptr(), counts.data_ptr(),
+                                           int(brute), _stream()))
+    return keys, counts
+
+
+def debug_quad_frames(state):
+    """Per-quad plane frames (P, 12) in surfel order, as the build kernels computed them."""
+    info = state.info()
+    out = torch.zeros((info["surfels"], 12), dtype=torch.float32, device=f"cuda:{state.device}")
+    _check(state, lib().dst_debug_quad_frames(state.handle, out.data_ptr(), _stream()))
+    return out

@@ -242,7 +242,7 @@ def make_workload(config: int, P: Optional[int] = None, H: Optional[int] = None,
         rots = _quat_from_normal(normals, g)
         opac = torch.sigmoid(2.0 + torch.randn((P, 1), generator=g))
         out["colors_precomp"] = torch.rand((P, 3), generator=g).contiguous()
-        beams = 64 if W == 64 * 2048 else max(1, int(round(math.sqrt(W / 32))))
+        beams = 64 if (W % 64 == 0 and W >= 64 * 64) else 16 if W % 16 == 0 else 1
         az = W // beams
         ray_o, ray_d = lidar_rays(H, beams, az, g)
         out["upstream"] = ("rgb", "dpt")

@@ -1,0 +1,140 @@
+/*
+ * dst.h - C ABI of the B200-native differentiable surfel tracer.
+ *
+ * One shared library (libdst_b200.so) replaces the reference's host glue and OptiX programs:
+ *   ext.cpp:7-12                         (pybind surface)         -> the functions below
+ *   trace_surfels.cpp:36-159             BuildAccelerationStructure -> dst_build
+ *   trace_surfels.cpp:162-304            TraceSurfelsCUDA           -> dst_forward
+ *   trace_surfels.cpp:307-464            TraceSurfelsBackwardCUDA   -> dst_backward
+ *   optix_tracer/optix_wrapper.cpp:166-222  OptiXStateWrapper ctor/dtor -> dst_create / dst_destroy
+ *   optix_tracer/common.h:38-60          OPTIX_CHECK / CUDA_CHECK   -> int status + dst_last_error
+ *
+ * Conventions: every pointer inside an argument block is a DEVICE pointer on the handle's GPU;
+ * a null pointer means "absent" exactly where the reference treats an empty tensor as absent
+ * (data_ptr() == nullptr, optix_tracer/forward.cu:265, 278). All arrays are contiguous float32
+ * unless stated. `stream` is a cudaStream_t passed as void*; all work is enqueued on it and the
+ * calls do not synchronise. Functions return 0 on success, a negative DST_E_* code otherwise; no
+ * C++ exception crosses this boundary.
+ */
+#ifndef DST_H_INCLUDED
+#define DST_H_INCLUDED
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DST_OK            0
+#define DST_E_ARG        -1   /* bad argument (shape, null pointer, size mismatch)            */
+#define DST_E_CUDA       -2   /* a CUDA runtime call failed; see dst_last_error               */
+#define DST_E_STATE      -3   /* call order (trace or refit before a build)                   */
+#define DST_E_NOMEM      -4   /* device allocation failed                                     */
+
+/* bits of the device status word returned by dst_status */
+#define DST_STATUS_STACK_OVERFLOW  1u   /* traversal stack exhausted: some hits may be missing */
+#define DST_STATUS_CHUNK_LIMIT     2u   /* a ray hit the bound on 16-hit enumerations          */
+
+#define DST_MID_CHANNELS 16             /* per-bounce record, optix_tracer/config.h:7-15       */
+#define DST_CHUNK 16                    /* hits gathered per enumeration, config.h:20          */
+
+typedef struct dst_handle dst_handle;
+
+/* Creates the tracer state for one GPU (replaces OptiXStateWrapper's constructor,
+ * optix_tracer/optix_wrapper.cpp:166-204; no program compilation happens here). */
+int dst_create(int device, dst_handle** out);
+int dst_destroy(dst_handle* h);
+/* Message of the last failure on this handle (h may be NULL for dst_create failures). */
+const char* dst_last_error(const dst_handle* h);
+
+/* Build (rebuild != 0) or refit (rebuild == 0) the hierarchy over the surfel quads
+ * (trace_surfels.cpp:36-159). vertices: (n_vertices, 3) with n_vertices = 4 * surfels, laid out
+ * as example/utils/gaussian_utils.py:176-210 produces them; triangles: (n_triangles, 3) int32,
+ * n_triangles = 2 * surfels, accepted for signature compatibility (the device code of the
+ * reference hard-codes the 4-vertex/2-triangle layout, optix_tracer/backward.cu:583-602) and may
+ * be NULL. A refit keeps the topology of the last build and needs the same surfel count. */
+int dst_build(dst_handle* h, const float* vertices, int64_t n_vertices,
+              const int32_t* triangles, int64_t n_triangles, int rebuild, void* stream);
+
+typedef struct dst_trace_inputs {
+    int32_t H, W;                 /* ray grid: ray index = row * W + col (trace_surfels.cpp:198-200) */
+    int32_t P;                    /* surfels                                                      */
+    int32_t sh_degree, sh_coeffs; /* D and M of optix_tracer/params.h:33 (M = 0 without SH)       */
+    int32_t max_trace_depth;      /* bounces after the primary segment                            */
+    int32_t mid_stride;           /* floats of mid_val per ray, >= 16 * (max_trace_depth + 1)     */
+    int32_t start_from_first;
+    float specular_threshold, scale_modifier;
+    const float *ray_o, *ray_d;   /* (H, W, 3)                                                    */
+    const float *vertices;        /* (4P, 3), the buffer the hierarchy was built/refitted from    */
+    const float *background;      /* (3)                                                          */
+    const float *means3D;         /* (P, 3)                                                       */
+    const float *shs;             /* (P, M, 3) or NULL                                            */
+    const float *colors_precomp;  /* (P, 3) or NULL; exactly one of shs / colors_precomp          */
+    const float *others_precomp;  /* (P, 2) specular, roughness; or NULL                          */
+    const float *opacities;       /* (P, 1)                                                       */
+    const float *scales;          /* (P, 2)                                                       */
+    const float *rotations;       /* (P, 4) as (w, x, y, z)                                       */
+} dst_trace_inputs;
+
+typedef struct dst_fwd_args {
+    dst_trace_inputs in;
+    int32_t training;             /* accumulate per-surfel weights into a_weights                 */
+    int32_t hit_cap;              /* slots per ray of hit_log                                     */
+    /* outputs, all written for every ray (no pre-zeroing needed)                                 */
+    float *out_rgb;               /* (H, W, 3)  */
+    float *out_dpt;               /* (H, W, 1)  */
+    float *out_acc;               /* (H, W, 1)  */
+    float *out_norm;              /* (H, W, 3)  */
+    float *out_dist;              /* (H, W, 3), zeros: distortion is unimplemented upstream       */
+    float *out_aux;               /* (H, W, 2)  */
+    float *mid_val;               /* (H, W, mid_stride); untraced bounces are zero                */
+    float *a_weights;             /* (P, 1), zeroed then accumulated here when training; or NULL  */
+    /* optional diagnostics (NULL to disable)                                                     */
+    int32_t *hit_log;             /* (H*W, hit_cap) contributing primitive ids in compositing order */
+    int32_t *hit_cnt;             /* (H*W) number of contributions over all bounces               */
+    unsigned long long *counters; /* [0] ray segments [1] enumerations [2] nodes visited [3] quads tested
+                                     [4] slots evaluated [5] contributions; accumulated, not zeroed */
+} dst_fwd_args;
+
+typedef struct dst_bwd_args {
+    dst_trace_inputs in;
+    /* state saved by the forward call */
+    const float *out_rgb, *out_dpt, *out_acc, *out_norm, *out_dist, *out_aux, *mid_val;
+    /* upstream gradients, shapes of the forward outputs; dL_ddist is (H, W, 1) and unused       */
+    const float *dL_drgb, *dL_ddpt, *dL_dacc, *dL_dnorm, *dL_ddist, *dL_daux;
+    /* gradient outputs, fully written by the call (no pre-zeroing needed)                        */
+    float *dL_dray_o, *dL_dray_d; /* (H, W, 3)                                                    */
+    float *dL_dmeans3D;           /* (P, 3)                                                       */
+    float *dL_dgrads3D;           /* (P, 3) = sum of dL_dmeans3D * 0.5 * depth                    */
+    float *dL_dshs;               /* (P, M, 3) or NULL                                            */
+    float *dL_dcolors;            /* (P, 3), accumulated in SH mode too (backward.cu:543)         */
+    float *dL_dothers;            /* (P, 2)                                                       */
+    float *dL_dopacities;         /* (P, 1)                                                       */
+    float *dL_dscales;            /* (P, 2)                                                       */
+    float *dL_drotations;         /* (P, 4)                                                       */
+    unsigned long long *counters; /* as in dst_fwd_args, or NULL                                  */
+} dst_bwd_args;
+
+/* Forward trace (trace_surfels.cpp:162-304 + optix_tracer/forward.cu). */
+int dst_forward(dst_handle* h, const dst_fwd_args* args, void* stream);
+/* Backward trace (trace_surfels.cpp:307-464 + optix_tracer/backward.cu). */
+int dst_backward(dst_handle* h, const dst_bwd_args* args, void* stream);
+
+/* Synchronises `stream`, returns and clears the device status word (DST_STATUS_* bits). */
+int dst_status(dst_handle* h, uint32_t* flags, void* stream);
+
+/* Hierarchy facts for tests and reports: surfels, internal nodes, bytes held on the device. */
+int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t* device_bytes);
+
+/* Diagnostics: the DST_CHUNK nearest hits of each ray (one enumeration from the given origins),
+ * keys = (bits of t) << 32 | primitive id, ascending; counts = hits found (<= DST_CHUNK).
+ * brute != 0 tests every quad instead of walking the hierarchy. */
+int dst_debug_knearest(dst_handle* h, const float* ray_o, const float* ray_d, int64_t n_rays,
+                       unsigned long long* keys, int32_t* counts, int brute, void* stream);
+/* Diagnostics: copies the per-quad plane frames (12 floats each, surfel order) to `out`. */
+int dst_debug_quad_frames(dst_handle* h, float* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -19,7 +19,10 @@ enum { OPTIX_RAY_FLAG_NONE = 0 };
     static inline R max(T a, U b) { return (R)a > (R)b ? (R)a : (R)b; }
 ORC_MINMAX(int, int, int) ORC_MINMAX(unsigned, unsigned, unsigned) ORC_MINMAX(unsigned, int, unsigned) ORC_MINMAX(int, unsigned, unsigned)
 ORC_MINMAX(float, float, float) ORC_MINMAX(double, double, double) ORC_MINMAX(float, double, double) ORC_MINMAX(double, float, double)
-static inline float exp(float x) { return expf(x); }          // device code resolves exp(float) to the float overload
+extern int g_orc_portable_exp;                                 // set per run by ref_driver.cpp
+float orc_portable_exp(float x);
+// device code resolves exp(float) to the float overload
+static inline float exp(float x) { return g_orc_portable_exp ? orc_portable_exp(x) : expf(x); }
 static inline float rsqrtf(float x) { return 1.0f / sqrtf(x); }
 static inline void __trap() { abort(); }
 float atomicAdd(float* p, float v);

@@ -67,6 +67,29 @@ static inline bool ray_quad(const QuadRec& q, const float* o, const float* d, fl
     return true;
 }
 
+// Portable exp for x <= 0 (used for the Gaussian falloff, optix_tracer/forward.cu:247): Cody-Waite
+// reduction x = k ln2 + r, degree-7 Taylor polynomial in r, exact scaling by 2^k. Every step is one
+// rounded binary32 operation (or one fused multiply-add where written), so the CUDA kernels
+// reproduce it bit for bit; it agrees with a correctly rounded exp to about 1 ulp.
+static inline float pexp(float x) {
+    if (!(x >= -87.0f)) return (x != x) ? x : 0.0f;
+    if (x > 88.0f) x = 88.0f;
+    float kf = (x * 1.44269504088896341f + 12582912.0f) - 12582912.0f;
+    float r = fmaf(kf, -0.693145751953125f, x);
+    r = fmaf(kf, -1.42860682030941723212e-6f, r);
+    float p = 0.0001984126984126984f;
+    p = fmaf(p, r, 0.001388888888888889f);
+    p = fmaf(p, r, 0.008333333333333333f);
+    p = fmaf(p, r, 0.041666666666666664f);
+    p = fmaf(p, r, 0.16666666666666666f);
+    p = fmaf(p, r, 0.5f);
+    p = fmaf(p, r, 1.0f);
+    p = fmaf(p, r, 1.0f);
+    int32_t bits = ((int32_t)kf + 127) << 23;
+    float sc; memcpy(&sc, &bits, 4);
+    return p * sc;
+}
+
 // 64-bit sort key: (bits of t) << 32 | primitive id. t >= +0 so the bit pattern is monotone.
 static inline uint64_t hit_key(float t, uint32_t pidx) { uint32_t b; memcpy(&b, &t, 4); return ((uint64_t)b << 32) | pidx; }
 static inline float    key_t(uint64_t k) { uint32_t b = (uint32_t)(k >> 32); float t; memcpy(&t, &b, 4); return t; }

@@ -33,6 +33,8 @@ static thread_local uint3 g_idx, g_dim;
 static thread_local unsigned g_p0, g_p1, g_prim;
 static thread_local float g_t;
 static thread_local long g_anyhit, g_enums, g_contrib;
+int g_orc_portable_exp = 0;
+float orc_portable_exp(float x) { return orc::pexp(x); }
 static const orc::Scene* g_scene;
 static const OrcArgs* g_args;
 
@@ -87,7 +89,7 @@ int ref_mid_stride() { return MID_CHANNELS * (MAX_TRACE_DEPTH + 1); }
 // Fills the reference's launch-parameter block (trace_surfels.cpp:235-285, 390-446) and runs
 // its ray-generation program once per ray (optixLaunch(H, W, 1), trace_surfels.cpp:295, 456).
 void ref_run(void* scene, const OrcArgs* a) {
-    g_scene = (const orc::Scene*)scene; g_args = a;
+    g_scene = (const orc::Scene*)scene; g_args = a; g_orc_portable_exp = a->portable_exp;
     params = Params();
     params.P = a->P; params.H = a->H; params.W = a->W; params.D = a->D; params.M = a->M;
     params.max_trace_depth = a->max_trace_depth; params.specular_threshold = a->specular_threshold;

@@ -244,7 +244,7 @@ static void trace_ray(const Ctx& cx, int ray, F3 ray_o, F3 ray_d, float min_dept
             float power = -0.5f * rho3d;
             if (power > 0.0f) continue;                            // :240
             const float opac = A.opacities[gidx];
-            const float G = expf(power);
+            const float G = A.portable_exp ? orc::pexp(power) : expf(power);
             float alpha = std::min(0.99f, opac * G);               // :247
             if (A.fragile && fabsf(alpha - 1.0f / 255.0f) < 3e-8f) A.fragile[ray] = 1;
             if (alpha < 1.0f / 255.0f) continue;
