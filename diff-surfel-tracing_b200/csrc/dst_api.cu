@@ -15,6 +15,24 @@ int dst_set_error(dst_handle* h, int code, const char* fmt, ...) {
 }
 void dst_global_error(const char* msg) { snprintf(g_global_err, sizeof(g_global_err), "%s", msg); }
 
+void dst_prof_mark(dst_handle* h, int kind, int which_end, cudaStream_t st) {
+    if (!h->profiling) return;
+    if (!h->ev[kind]) {
+        h->ev[kind] = new (std::nothrow) cudaEvent_t[2 * DST_PROF_SLOTS];
+        if (!h->ev[kind]) return;
+        for (int i = 0; i < 2 * DST_PROF_SLOTS; i++) cudaEventCreate(&h->ev[kind][i]);
+        h->ev_n[kind] = 0;
+    }
+    if (which_end == 0) {
+        if (h->ev_n[kind] >= DST_PROF_SLOTS) return;
+        cudaEventRecord(h->ev[kind][2 * h->ev_n[kind]], st);
+    } else {
+        if (h->ev_n[kind] >= DST_PROF_SLOTS) return;
+        cudaEventRecord(h->ev[kind][2 * h->ev_n[kind] + 1], st);
+        h->ev_n[kind]++;
+    }
+}
+
 namespace {
 struct DeviceGuard {
     int prev = -1; bool ok = true;
@@ -62,6 +80,9 @@ int dst_destroy(dst_handle* h) {
     cudaFree(h->nodes); cudaFree(h->quads); cudaFree(h->leaf_gid); cudaFree(h->leaf_parent); cudaFree(h->arrive);
     cudaFree(h->keys); cudaFree(h->keys_alt); cudaFree(h->vals); cudaFree(h->vals_alt); cudaFree(h->block_hist);
     cudaFree(h->header); cudaFree(h->status); cudaFree(h->cache); cudaFree(h->arena);
+    for (int k = 0; k < 3; k++) {
+        if (h->ev[k]) { for (int i = 0; i < 2 * DST_PROF_SLOTS; i++) cudaEventDestroy(h->ev[k][i]); delete[] h->ev[k]; }
+    }
     delete h;
     return DST_OK;
 }
@@ -120,6 +141,28 @@ int dst_debug_knearest(dst_handle* h, const float* ray_o, const float* ray_d, in
     if (!ray_o || !ray_d || !keys || !counts) return dst_set_error(h, DST_E_ARG, "null pointer");
     DeviceGuard g(h->device);
     return dst_knearest_impl(h, ray_o, ray_d, n_rays, keys, counts, brute, (cudaStream_t)stream);
+}
+
+int dst_profile_enable(dst_handle* h, int on) {
+    if (!h) return DST_E_ARG;
+    h->profiling = on != 0;
+    return DST_OK;
+}
+
+int dst_profile_read(dst_handle* h, int which, float* ms_sum, int32_t* launches) {
+    if (!h || which < 0 || which > 2 || !ms_sum || !launches) return DST_E_ARG;
+    DeviceGuard g(h->device);
+    float sum = 0.f;
+    const int n = h->ev[which] ? h->ev_n[which] : 0;
+    for (int i = 0; i < n; i++) {
+        float ms = 0.f;
+        DST_CUDA_TRY(h, cudaEventSynchronize(h->ev[which][2 * i + 1]));
+        DST_CUDA_TRY(h, cudaEventElapsedTime(&ms, h->ev[which][2 * i], h->ev[which][2 * i + 1]));
+        sum += ms;
+    }
+    *ms_sum = sum; *launches = n;
+    h->ev_n[which] = 0;
+    return DST_OK;
 }
 
 int dst_debug_quad_frames(dst_handle* h, float* out, void* stream) {

@@ -380,8 +380,10 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
     p.tiled = a->in.H >= 16;
     const long long R = (long long)a->in.H * a->in.W;
     const long long blocks = p.tiled ? (long long)((a->in.W + 15) / 16) * ((a->in.H + 7) / 8) : (R + BWD_THREADS - 1) / BWD_THREADS;
+    dst_prof_mark(h, 2, 0, st);
     if (a->counters) k_backward<true><<<(unsigned int)blocks, BWD_THREADS, 0, st>>>(p);
     else k_backward<false><<<(unsigned int)blocks, BWD_THREADS, 0, st>>>(p);
+    dst_prof_mark(h, 2, 1, st);
     DST_CUDA_TRY(h, cudaGetLastError());
     k_unpack<<<(unsigned int)((P + 255) / 256), 256, 0, st>>>((int)P, h->arena, a->dL_drotations, a->dL_dmeans3D, a->dL_dopacities,
                                                               a->dL_dgrads3D, a->dL_dscales, a->dL_dothers, a->dL_dcolors);

@@ -351,6 +351,9 @@ int dst_bvh_build_impl(dst_handle* h, const float* v, int64_t P, int rebuild, cu
     if (rebuild) {
         int rc = ensure_capacity(h, P);
         if (rc != DST_OK) return rc;
+    }
+    dst_prof_mark(h, 0, 0, st);
+    if (rebuild) {
         h->built = false;
         k_init_bounds<<<1, 32, 0, st>>>(bw);
         const int rgrid = min(grid, h->sm_count * 8);
@@ -374,6 +377,7 @@ int dst_bvh_build_impl(dst_handle* h, const float* v, int64_t P, int rebuild, cu
     DST_CUDA_TRY(h, cudaMemsetAsync(h->arrive, 0, 4 * (size_t)(n > 1 ? n - 1 : 1), st));
     if (n == 1) k_single_leaf<<<1, 1, 0, st>>>(h->nodes, h->leaf_parent, h->arrive);
     k_refit<<<grid, tpb, 0, st>>>(v, n, h->vals, h->nodes, h->leaf_parent, h->arrive, h->quads, h->leaf_gid, h->header);
+    dst_prof_mark(h, 0, 1, st);
     DST_CUDA_TRY(h, cudaGetLastError());
     h->built = true;
     return DST_OK;

@@ -62,7 +62,14 @@ struct dst_handle {
     float4* cache; int64_t cache_cap;
     float* arena;  int64_t arena_cap;
     int sm_count;
+    // optional event timing (dst_profile_enable)
+    int profiling;
+    cudaEvent_t* ev[3];           // per kind: 2 * DST_PROF_SLOTS events (start, stop pairs)
+    int ev_n[3];
 };
+#define DST_PROF_SLOTS 1024
+// records the start (which_end = 0) or stop (1) event of the current launch of `kind`; no-op unless profiling
+void dst_prof_mark(dst_handle* h, int kind, int which_end, cudaStream_t st);
 
 #define DST_CUDA_TRY(h, expr)                                                                    \
     do {                                                                                         \

@@ -249,8 +249,10 @@ int dst_forward_impl(dst_handle* h, const dst_fwd_args* a, cudaStream_t st) {
     const long long R = (long long)a->in.H * a->in.W;
     long long blocks = p.tiled ? (long long)((a->in.W + 15) / 16) * ((a->in.H + 7) / 8) : (R + FWD_THREADS - 1) / FWD_THREADS;
     const bool diag = a->hit_log || a->hit_cnt || a->counters;
+    dst_prof_mark(h, 1, 0, st);
     if (diag) k_forward<false, true><<<(unsigned int)blocks, FWD_THREADS, 0, st>>>(p);
     else k_forward<false, false><<<(unsigned int)blocks, FWD_THREADS, 0, st>>>(p);
+    dst_prof_mark(h, 1, 1, st);
     DST_CUDA_TRY(h, cudaGetLastError());
     return DST_OK;
 }

@@ -62,6 +62,8 @@ def lib():
         l.dst_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), C.c_void_p]
         l.dst_bvh_info.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
         l.dst_debug_knearest.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+        l.dst_profile_enable.argtypes = [C.c_void_p, C.c_int]
+        l.dst_profile_read.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_int32)]
         l.dst_debug_quad_frames.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         _lib = l
     return _lib
@@ -110,6 +112,7 @@ class OptiXStateWrapper:
             raise RuntimeError(lib().dst_last_error(None).decode())
         self.handle = h
         self._keep = None
+        self.grad_bucket = None     # flat buffer holding the per-surfel gradients of the last backward call
 
     def __del__(self):
         try:
@@ -124,6 +127,19 @@ class OptiXStateWrapper:
         f = C.c_uint32(0)
         _check(self, lib().dst_status(self.handle, C.byref(f), _stream()))
         return f.value
+
+    def profile(self, on=True):
+        """Records CUDA events around the build, forward and backward kernels of later calls."""
+        _check(self, lib().dst_profile_enable(self.handle, int(on)))
+
+    def profile_read(self):
+        """{kind: (summed ms, launches)} since the last read; waits for the recorded events."""
+        out = {}
+        for i, k in enumerate(("build", "forward", "backward")):
+            ms, n = C.c_float(0), C.c_int32(0)
+            _check(self, lib().dst_profile_read(self.handle, i, C.byref(ms), C.byref(n)))
+            out[k] = (ms.value, n.value)
+        return out
 
     def info(self):
         a, b, c = C.c_int64(), C.c_int64(), C.c_int64()
@@ -245,15 +261,26 @@ def trace_surfels_backward(state, start_from_first, ray_o, ray_d, vertices, back
           up(dL_dnorm, (H, W, 3), "dL_dnorm"), up(dL_ddist, (H, W, 1), "dL_ddist"), up(dL_daux, (H, W, 2), "dL_daux")]
     g_ray_o = torch.empty((H, W, 3), **f32)
     g_ray_d = torch.empty((H, W, 3), **f32)
-    g_means = torch.empty((P, 3), **f32)
-    g_g3d = torch.empty((P, 3), **f32)
+    # all per-surfel gradients live in ONE flat buffer (16-byte aligned views), so that a multi-GPU
+    # caller sums them with a single all-reduce (shard.allreduce_surfel_gradients)
+    sizes = [("rot", P * 4), ("means", P * 3), ("g3d", P * 3), ("shs", P * M * 3), ("colors", P * NUM_CHANNELS),
+             ("others", P * AUX_CHANNELS), ("opac", P), ("scales", P * 2)]
+    offs, total = {}, 0
+    for name, n in sizes:
+        offs[name] = total
+        total += (n + 3) // 4 * 4
+    bucket = torch.empty((total,), **f32)
+    view = lambda name, n, shape: bucket[offs[name]:offs[name] + n].view(shape)
+    g_rot = view("rot", P * 4, (P, 4))
+    g_means = view("means", P * 3, (P, 3))
+    g_g3d = view("g3d", P * 3, (P, 3))
+    g_shs = view("shs", P * M * 3, (P, M, 3))
+    g_colors = view("colors", P * NUM_CHANNELS, (P, NUM_CHANNELS))
+    g_others = view("others", P * AUX_CHANNELS, (P, AUX_CHANNELS))
+    g_opac = view("opac", P, (P, 1))
+    g_scales = view("scales", P * 2, (P, 2))
     g_g3d_abs = torch.zeros((P, 3), **f32)
-    g_shs = torch.empty((P, M, 3), **f32)
-    g_colors = torch.empty((P, NUM_CHANNELS), **f32)
-    g_others = torch.empty((P, AUX_CHANNELS), **f32)
-    g_opac = torch.empty((P, 1), **f32)
-    g_scales = torch.empty((P, 2), **f32)
-    g_rot = torch.empty((P, 4), **f32)
+    state.grad_bucket = bucket
     g_trans = torch.zeros((P, 9), **f32)
     a = _BwdArgs()
     a.inp = i

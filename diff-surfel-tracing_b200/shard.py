@@ -1,0 +1,40 @@
+"""Multi-GPU plumbing of the tracer: rays shard, surfels replicate, one all-reduce sums the gradients.
+
+The reference is single-GPU. Rays are independent, so a multi-GPU run gives every rank a block of
+rays (image rows, or whole cameras of a batch) and a full copy of the surfels and the hierarchy
+(each rank runs the same deterministic build on the same vertices). The only exchange is the sum
+of the per-surfel gradients after the backward trace; the binding lays all of them out in one
+flat buffer, so it is a single collective.
+"""
+import torch
+import torch.distributed as dist
+
+
+def split_rows(n_rows: int, world: int, rank: int):
+    """Contiguous block [start, stop) of the `n_rows` ray rows owned by `rank`; sizes differ by at most one."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError("bad rank / world size")
+    base, extra = divmod(n_rows, world)
+    start = rank * base + min(rank, extra)
+    return start, start + base + (1 if rank < extra else 0)
+
+
+def shard_rays(ray_o: torch.Tensor, ray_d: torch.Tensor, world: int, rank: int):
+    """This rank's rows of (H, W, 3) ray tensors (views, no copy)."""
+    a, b = split_rows(ray_o.shape[0], world, rank)
+    return ray_o[a:b], ray_d[a:b]
+
+
+def allreduce_bucket(bucket: torch.Tensor, group=None):
+    """In-place sum of a flat gradient buffer over the ranks of `group` (no-op without a process group)."""
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(bucket, op=dist.ReduceOp.SUM, group=group)
+    return bucket
+
+
+def allreduce_surfel_gradients(state, group=None):
+    """Sums the per-surfel gradients of the last backward call of `state` (the tracer's state object)
+    over all ranks, in place and on the current stream: one collective over one flat buffer."""
+    if state.grad_bucket is None:
+        raise RuntimeError("no backward call has been made on this tracer state")
+    return allreduce_bucket(state.grad_bucket, group)

@@ -126,6 +126,15 @@ int dst_status(dst_handle* h, uint32_t* flags, void* stream);
 /* Hierarchy facts for tests and reports: surfels, internal nodes, bytes held on the device. */
 int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t* device_bytes);
 
+/* Timing of the main kernels with CUDA events on the launching stream. While enabled, every
+ * dst_build / dst_forward / dst_backward call records an event pair around its dominant kernel
+ * (which = 0: the whole build or refit sequence, 1: the forward trace kernel, 2: the backward trace
+ * kernel). dst_profile_read waits for the recorded events, returns the summed milliseconds and the
+ * number of launches since the last read, and resets the counters. At most 1024 launches per kind
+ * are kept between reads. */
+int dst_profile_enable(dst_handle* h, int on);
+int dst_profile_read(dst_handle* h, int which, float* ms_sum, int32_t* launches);
+
 /* Diagnostics: the DST_CHUNK nearest hits of each ray (one enumeration from the given origins),
  * keys = (bits of t) << 32 | primitive id, ascending; counts = hits found (<= DST_CHUNK).
  * brute != 0 tests every quad instead of walking the hierarchy. */
