@@ -136,11 +136,11 @@ int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t*
 }
 
 int dst_debug_knearest(dst_handle* h, const float* ray_o, const float* ray_d, int64_t n_rays, unsigned long long* keys,
-                       int32_t* counts, int brute, void* stream) {
+                       int32_t* counts, int brute, const float* t_cut, unsigned long long* counters, void* stream) {
     if (!h) return DST_E_ARG;
     if (!ray_o || !ray_d || !keys || !counts) return dst_set_error(h, DST_E_ARG, "null pointer");
     DeviceGuard g(h->device);
-    return dst_knearest_impl(h, ray_o, ray_d, n_rays, keys, counts, brute, (cudaStream_t)stream);
+    return dst_knearest_impl(h, ray_o, ray_d, n_rays, keys, counts, brute, t_cut, counters, (cudaStream_t)stream);
 }
 
 int dst_profile_enable(dst_handle* h, int on) {

@@ -89,7 +89,7 @@ int dst_bvh_build_impl(dst_handle* h, const float* v, int64_t P, int rebuild, cu
 int dst_forward_impl(dst_handle* h, const dst_fwd_args* a, cudaStream_t st);
 int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st);
 int dst_knearest_impl(dst_handle* h, const float* ro, const float* rd, int64_t n, unsigned long long* keys,
-                      int32_t* counts, int brute, cudaStream_t st);
+                      int32_t* counts, int brute, const float* t_cut, unsigned long long* counters, cudaStream_t st);
 int dst_prepare_cache(dst_handle* h, const dst_trace_inputs* in, cudaStream_t st);
 int dst_export_frames_impl(dst_handle* h, float* out, cudaStream_t st);
 

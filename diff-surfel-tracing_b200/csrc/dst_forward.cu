@@ -184,14 +184,16 @@ __global__ void __launch_bounds__(FWD_THREADS) k_forward(const __grid_constant__
 // one enumeration per ray, for tests of the hierarchy walk against exhaustive testing
 template <bool BRUTE>
 __global__ void __launch_bounds__(FWD_THREADS) k_knearest(BvhView bvh, const float* __restrict__ ro, const float* __restrict__ rd,
-                                                          long long n, unsigned long long* keys, int* counts, unsigned int* status) {
+                                                          long long n, unsigned long long* keys, int* counts, unsigned int* status,
+                                                          const float* __restrict__ t_cut, unsigned long long* counters) {
     __shared__ unsigned long long kbuf[DST_CHUNK * FWD_THREADS];
     const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= n) return;
     unsigned long long* kb = kbuf + threadIdx.x;
-    TraceCounters tc;
-    const int c = knearest<BRUTE, false, FWD_THREADS>(bvh, ro[3 * r], ro[3 * r + 1], ro[3 * r + 2], rd[3 * r], rd[3 * r + 1], rd[3 * r + 2],
-                                                     kb, status, tc);
+    TraceCounters tc = { 0, 0, 0, 0, 0, 0 };
+    const int c = knearest<BRUTE, true, FWD_THREADS>(bvh, ro[3 * r], ro[3 * r + 1], ro[3 * r + 2], rd[3 * r], rd[3 * r + 1], rd[3 * r + 2],
+                                                    kb, status, tc, t_cut ? t_cut[r] : DST_T_MAX);
+    if (counters) { atomicAdd(counters + 2, tc.nodes); atomicAdd(counters + 3, tc.quads); }
     counts[r] = c;
     for (int i = 0; i < DST_CHUNK; i++) keys[r * DST_CHUNK + i] = i < c ? kb[i * FWD_THREADS] : 0ull;
 }
@@ -258,12 +260,12 @@ int dst_forward_impl(dst_handle* h, const dst_fwd_args* a, cudaStream_t st) {
 }
 
 int dst_knearest_impl(dst_handle* h, const float* ro, const float* rd, int64_t n, unsigned long long* keys, int32_t* counts,
-                      int brute, cudaStream_t st) {
+                      int brute, const float* t_cut, unsigned long long* counters, cudaStream_t st) {
     if (!h->built) return dst_set_error(h, DST_E_STATE, "no hierarchy has been built");
     if (n <= 0) return DST_OK;
     const unsigned int blocks = (unsigned int)((n + FWD_THREADS - 1) / FWD_THREADS);
-    if (brute) k_knearest<true><<<blocks, FWD_THREADS, 0, st>>>(dst_bvh_view(h), ro, rd, n, keys, counts, h->status);
-    else k_knearest<false><<<blocks, FWD_THREADS, 0, st>>>(dst_bvh_view(h), ro, rd, n, keys, counts, h->status);
+    if (brute) k_knearest<true><<<blocks, FWD_THREADS, 0, st>>>(dst_bvh_view(h), ro, rd, n, keys, counts, h->status, t_cut, counters);
+    else k_knearest<false><<<blocks, FWD_THREADS, 0, st>>>(dst_bvh_view(h), ro, rd, n, keys, counts, h->status, t_cut, counters);
     DST_CUDA_TRY(h, cudaGetLastError());
     return DST_OK;
 }

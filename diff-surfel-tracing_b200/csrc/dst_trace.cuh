@@ -30,9 +30,10 @@ __device__ __forceinline__ float hitkey_t(unsigned long long k) { return __uint_
 // covers the rounding of the slab arithmetic itself.
 template <bool BRUTE, bool COUNT, int KS>
 __device__ __forceinline__ int knearest(const BvhView& bvh, float ox, float oy, float oz, float dx, float dy, float dz,
-                                        unsigned long long* kb, unsigned int* status, TraceCounters& tc) {
+                                        unsigned long long* kb, unsigned int* status, TraceCounters& tc,
+                                        float kmax0 = DST_T_MAX) {
     int n = 0;
-    float kmax = DST_T_MAX;
+    float kmax = kmax0;          // hits beyond kmax0 are of no interest to the caller
     if (bvh.P <= 0) return 0;
 
     auto offer = [&](int pos) {

@@ -61,7 +61,7 @@ def lib():
         l.dst_backward.argtypes = [C.c_void_p, C.POINTER(_BwdArgs), C.c_void_p]
         l.dst_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), C.c_void_p]
         l.dst_bvh_info.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
-        l.dst_debug_knearest.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+        l.dst_debug_knearest.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
         l.dst_profile_enable.argtypes = [C.c_void_p, C.c_int]
         l.dst_profile_read.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_int32)]
         l.dst_debug_quad_frames.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
@@ -297,14 +297,15 @@ def trace_surfels_backward(state, start_from_first, ray_o, ray_d, vertices, back
     return g_ray_o, g_ray_d, g_means, g_g3d, g_g3d_abs, g_shs, g_colors, g_others, g_opac, g_scales, g_rot, g_trans
 
 
-def debug_knearest(state, ray_o, ray_d, brute=False):
-    """The 16 nearest hits of each ray (one enumeration): (keys (n,16) int64 bit patterns, counts (n,))."""
+def debug_knearest(state, ray_o, ray_d, brute=False, t_cut=None, counters=None):
+    """The 16 nearest hits of each ray (one enumeration): (keys (n,16) int64 bit patterns, counts (n,)).
+    t_cut: optional (n,) float bound per ray; counters: optional int64 tensor of 8 (nodes -> [2], quads -> [3])."""
     ro, rd = _cuda_f32(ray_o.reshape(-1, 3), "ray_o"), _cuda_f32(ray_d.reshape(-1, 3), "ray_d")
     n = ro.size(0)
     keys = torch.zeros((n, 16), dtype=torch.int64, device=ro.device)
     counts = torch.zeros((n,), dtype=torch.int32, device=ro.device)
     _check(state, lib().dst_debug_knearest(state.handle, ro.data_ptr(), rd.data_ptr(), n, keys.data_ptr(), counts.data_ptr(),
-                                           int(brute), _stream()))
+                                           int(brute), _ptr(t_cut), _ptr(counters), _stream()))
     return keys, counts
 
 

@@ -137,9 +137,11 @@ int dst_profile_read(dst_handle* h, int which, float* ms_sum, int32_t* launches)
 
 /* Diagnostics: the DST_CHUNK nearest hits of each ray (one enumeration from the given origins),
  * keys = (bits of t) << 32 | primitive id, ascending; counts = hits found (<= DST_CHUNK).
- * brute != 0 tests every quad instead of walking the hierarchy. */
+ * brute != 0 tests every quad instead of walking the hierarchy. t_cut (n_rays floats, or NULL):
+ * hits beyond t_cut[r] are ignored for ray r. counters (or NULL): [2] += nodes visited, [3] += quads tested. */
 int dst_debug_knearest(dst_handle* h, const float* ray_o, const float* ray_d, int64_t n_rays,
-                       unsigned long long* keys, int32_t* counts, int brute, void* stream);
+                       unsigned long long* keys, int32_t* counts, int brute, const float* t_cut,
+                       unsigned long long* counters, void* stream);
 /* Diagnostics: copies the per-quad plane frames (12 floats each, surfel order) to `out`. */
 int dst_debug_quad_frames(dst_handle* h, float* out, void* stream);
 
