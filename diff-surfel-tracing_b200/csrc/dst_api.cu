@@ -60,6 +60,7 @@ int dst_create(int device, dst_handle** out) {
     if (!h) { dst_global_error("dst_create: out of host memory"); return DST_E_NOMEM; }
     memset(h, 0, sizeof(*h));
     h->device = device;
+    h->wf_min_rays = 1 << 17;
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete h; dst_global_error("dst_create: cudaGetDeviceProperties failed"); return DST_E_CUDA; }
     h->sm_count = prop.multiProcessorCount;
@@ -80,6 +81,7 @@ int dst_destroy(dst_handle* h) {
     cudaFree(h->nodes); cudaFree(h->quads); cudaFree(h->leaf_gid); cudaFree(h->leaf_parent); cudaFree(h->arrive);
     cudaFree(h->keys); cudaFree(h->keys_alt); cudaFree(h->vals); cudaFree(h->vals_alt); cudaFree(h->block_hist);
     cudaFree(h->header); cudaFree(h->status); cudaFree(h->cache); cudaFree(h->arena);
+    cudaFree(h->wf_state); cudaFree(h->wf_req); cudaFree(h->wf_kbuf); cudaFree(h->wf_kcnt); cudaFree(h->wf_list[0]); cudaFree(h->wf_list[1]); cudaFree(h->wf_counts);
     for (int k = 0; k < 3; k++) {
         if (h->ev[k]) { for (int i = 0; i < 2 * DST_PROF_SLOTS; i++) cudaEventDestroy(h->ev[k][i]); delete[] h->ev[k]; }
     }
@@ -131,7 +133,8 @@ int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t*
     if (!h) return DST_E_ARG;
     if (surfels) *surfels = h->built ? h->P : 0;
     if (nodes) *nodes = h->built ? (h->P > 1 ? h->P - 1 : 1) : 0;
-    if (device_bytes) *device_bytes = h->cap * (64 + 48 + 4 + 4 + 4 + 16 + 8) + h->hist_cap * 1024 + h->cache_cap * 64 + h->arena_cap * 4 * DST_ARENA_FLOATS;
+    if (device_bytes) *device_bytes = h->cap * (64 + 48 + 4 + 4 + 4 + 16 + 8) + h->hist_cap * 1024 + h->cache_cap * 64 + h->arena_cap * 4 * DST_ARENA_FLOATS +
+                                      h->wf_cap * (long long)(h->wf_state_bytes + 32 + 8 * DST_CHUNK + 4 + 8);
     return DST_OK;
 }
 
@@ -141,6 +144,14 @@ int dst_debug_knearest(dst_handle* h, const float* ray_o, const float* ray_d, in
     if (!ray_o || !ray_d || !keys || !counts) return dst_set_error(h, DST_E_ARG, "null pointer");
     DeviceGuard g(h->device);
     return dst_knearest_impl(h, ray_o, ray_d, n_rays, keys, counts, brute, t_cut, counters, (cudaStream_t)stream);
+}
+
+int dst_set_option(dst_handle* h, int option, int64_t value) {
+    if (!h) return DST_E_ARG;
+    switch (option) {
+        case DST_OPT_WAVEFRONT_MIN_RAYS: h->wf_min_rays = value < 0 ? 0 : value; return DST_OK;
+        default: return dst_set_error(h, DST_E_ARG, "unknown option %d", option);
+    }
 }
 
 int dst_profile_enable(dst_handle* h, int on) {

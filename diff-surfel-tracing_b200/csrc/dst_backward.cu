@@ -2,9 +2,10 @@
 // traceRay 332-655 and its helpers) and the host launcher TraceSurfelsBackwardCUDA
 // (trace_surfels.cpp:307-464).
 //
-// One thread per ray. Bounces are visited last to first; each segment is re-traced front to back
-// with the forward kernel's exact decision code (eval_slot), and every contributing hit adds its
-// gradients. Per-surfel gradients go to a packed arena of 16-byte aligned rows with 4-float
+// Bounces are visited last to first; each segment is re-traced front to back with the forward
+// kernel's exact decision code (eval_slot), and every contributing hit adds its gradients. As in
+// the forward trace the per-ray loop is a state machine run as wavefront rounds (k_enum gathers,
+// k_bwd_shade composites and differentiates) with a one-thread-per-ray tail. Per-surfel gradients go to a packed arena of 16-byte aligned rows with 4-float
 // vector reductions (5 per contribution instead of 18 scalar atomics; SH rows 12 instead of 48),
 // and are unpacked into the caller's tensors by a streaming kernel afterwards.
 #include "dst_trace.cuh"
@@ -20,7 +21,33 @@ struct BwdParams {
     float* arena;
     unsigned int* status;
     int tiled;
+    // wavefront scratch
+    void* state;
+    EnumReq* req;
+    unsigned long long* kbuf;
+    int* kcnt;
+    int* list[2];
+    int* counts;
+    int min_count;
+    int rounds;
 };
+
+struct __align__(16) BwdState {
+    float sox, soy, soz, sdx;
+    float sdy, sdz, offset, dpt;
+    float T_prev, C0, C1, C2;
+    float D, Nx, Ny, Nz;
+    float O0, O1, s_prod, Cp0;
+    float Cp1, Cp2, cp0, cp1;
+    float cp2, t_rgb0, t_rgb1, t_rgb2;
+    float t_dpt, t_acc, t_aux0, t_aux1;
+    float t_nx, t_ny, t_nz, dir_g0;
+    float dir_g1, dir_g2, dro_x, dro_y;
+    float dro_z, drd_x, drd_y, drd_z;
+    int last_gidx, contributor, chunk, seg;
+    int dir_gidx, pad0, pad1, pad2;
+};
+static_assert(sizeof(BwdState) == 208, "ray state is thirteen 16-byte words");
 
 __device__ __forceinline__ void red4(float* addr, float a, float b, float c, float d) {
     atomicAdd(reinterpret_cast<float4*>(addr), make_float4(a, b, c, d));
@@ -78,252 +105,371 @@ __device__ __forceinline__ V3 sh_dir_grad(int deg, const float* s, float x, floa
     return v3(gx, gy, gz);
 }
 
-template <bool DIAG>
-__global__ void __launch_bounds__(BWD_THREADS) k_backward(const __grid_constant__ BwdParams p) {
-    __shared__ unsigned long long kbuf[DST_CHUNK * BWD_THREADS];
-    const dst_trace_inputs& in = p.a.in;
-    const long long ray = ray_of_thread(in.H, in.W, p.tiled != 0);
-    if (ray < 0) return;
-    unsigned long long* kb = kbuf + threadIdx.x;
-    TraceCounters tc = { 0, 0, 0, 0, 0, 0 };
 
+__device__ __forceinline__ void bwd_load_state(const void* base, int ray, BwdState& s) {
+    const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const BwdState*>(base) + ray);
+    float4* dst = reinterpret_cast<float4*>(&s);
+#pragma unroll
+    for (int i = 0; i < 13; i++) dst[i] = src[i];
+}
+__device__ __forceinline__ void bwd_store_state(void* base, int ray, const BwdState& s) {
+    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<BwdState*>(base) + ray);
+    const float4* src = reinterpret_cast<const float4*>(&s);
+#pragma unroll
+    for (int i = 0; i < 13; i++) dst[i] = src[i];
+}
+
+__device__ __forceinline__ void bwd_request(const BwdState& s, EnumReq& q) {
+    if (s.chunk == 0) { q.ox = s.sox; q.oy = s.soy; q.oz = s.soz; }
+    else { q.ox = xadd(s.sox, xmul(s.offset, s.sdx)); q.oy = xadd(s.soy, xmul(s.offset, s.sdy)); q.oz = xadd(s.soz, xmul(s.offset, s.sdz)); }
+    q.dx = s.sdx; q.dy = s.sdy; q.dz = s.sdz; q.kmax0 = DST_T_MAX; q.pad = 0.f;
+}
+
+// Finds the next segment to differentiate, from segment `start` downwards (backward.cu:706-802):
+// skips the ones the reference skips, derives the segment's upstream gradients and the reflection
+// chain, and resets the running sums. Writes the ray gradients and returns false when none is left.
+__device__ __forceinline__ bool bwd_next_segment(const BwdParams& p, int ray, BwdState& s, int start) {
+    const dst_trace_inputs& in = p.a.in;
     const int depth = in.max_trace_depth;
+    const float* mid = p.a.mid_val + (size_t)ray * in.mid_stride;
+    for (int i = start; i >= 0; i--) {
+        const float4* mp = reinterpret_cast<const float4*>(mid + i * DST_MID_CHANNELS);
+        const float4 m0 = __ldg(mp), m1 = __ldg(mp + 1), m2 = __ldg(mp + 2), m3 = __ldg(mp + 3);
+        const float sdx = m0.w, sdy = m1.x, sdz = m1.y;
+        const float tot_dpt = m1.z;
+        const V3 tot_n = v3(m2.x, m2.y, m2.z);
+        const float tot_o0 = m2.w, tot_c0 = m3.y, tot_c1 = m3.z, tot_c2 = m3.w;
+        const float s_prev = i > 0 ? __ldg(mid + (i - 1) * DST_MID_CHANNELS + 11) : 1.0f;
+        if (sqrtf(sdx * sdx + sdy * sdy + sdz * sdz) == 0.0f || s_prev <= in.specular_threshold) continue;    // :724
+
+        const float g_rgb0 = __ldg(p.a.dL_drgb + 3 * (size_t)ray), g_rgb1 = __ldg(p.a.dL_drgb + 3 * (size_t)ray + 1), g_rgb2 = __ldg(p.a.dL_drgb + 3 * (size_t)ray + 2);
+        const float f_this = (i == depth) ? 1.0f : 1.0f - tot_o0;
+        s.t_rgb0 = g_rgb0 * f_this * s.s_prod; s.t_rgb1 = g_rgb1 * f_this * s.s_prod; s.t_rgb2 = g_rgb2 * f_this * s.s_prod;   // :760
+        s.s_prod /= s_prev;                                                                                   // :762
+        s.t_dpt = 0.f; s.t_acc = 0.f; s.t_aux0 = 0.f; s.t_aux1 = 0.f;
+        V3 t_norm = v3(0.f, 0.f, 0.f);
+        V3 dro = v3(s.dro_x, s.dro_y, s.dro_z), drd = v3(s.drd_x, s.drd_y, s.drd_z);
+        if (i != depth) {
+            // :769-774
+            s.t_aux0 += g_rgb0 * (s.Cp0 / tot_o0) + g_rgb1 * (s.Cp1 / tot_o0) + g_rgb2 * (s.Cp2 / tot_o0);
+            if (i > 0) {
+                const float4 pm3 = __ldg(reinterpret_cast<const float4*>(mid + (i - 1) * DST_MID_CHANNELS) + 3);
+                s.cp0 = pm3.y; s.cp1 = pm3.z; s.cp2 = pm3.w;
+            } else { s.cp0 = s.cp1 = s.cp2 = 0.f; }
+            s.Cp0 -= s.s_prod * (s.cp0 - tot_c0); s.Cp1 -= s.s_prod * (s.cp1 - tot_c1); s.Cp2 -= s.s_prod * (s.cp2 - tot_c2);
+            const float nl = sqrtf(dot(tot_n, tot_n));
+            if (nl != 0.0f) {                                                                                 // :778-790
+                const V3 d = v3(sdx, sdy, sdz);
+                drd = drd + 0.00001f * dro;
+                const V3 n = (1.0f / nl) * tot_n;
+                s.t_dpt += dro.x * sdx + dro.y * sdy + dro.z * sdz;
+                const V3 gm2 = -2.0f * drd;
+                t_norm = t_norm + dnormvdv(tot_n, ddotndndn(n, d, gm2));
+                drd = tot_dpt * dro + drd + ddotndndd(n, gm2);
+            }
+        }
+        if (i == 0) {                                                                                         // :793-802
+            s.t_dpt += __ldg(p.a.dL_ddpt + ray); s.t_acc += __ldg(p.a.dL_dacc + ray);
+            t_norm = t_norm + v3(__ldg(p.a.dL_dnorm + 3 * (size_t)ray), __ldg(p.a.dL_dnorm + 3 * (size_t)ray + 1), __ldg(p.a.dL_dnorm + 3 * (size_t)ray + 2));
+            s.t_aux0 += __ldg(p.a.dL_daux + 2 * (size_t)ray); s.t_aux1 += __ldg(p.a.dL_daux + 2 * (size_t)ray + 1);
+        }
+        s.t_nx = t_norm.x; s.t_ny = t_norm.y; s.t_nz = t_norm.z;
+        s.drd_x = drd.x; s.drd_y = drd.y; s.drd_z = drd.z;
+        s.sox = m0.x; s.soy = m0.y; s.soz = m0.z; s.sdx = sdx; s.sdy = sdy; s.sdz = sdz;
+        s.offset = 0.f; s.dpt = 0.f; s.T_prev = 1.f;
+        s.C0 = s.C1 = s.C2 = 0.f; s.D = 0.f; s.Nx = s.Ny = s.Nz = 0.f; s.O0 = s.O1 = 0.f;
+        s.last_gidx = -1; s.contributor = 0; s.chunk = 0; s.seg = i; s.dir_gidx = -1;
+        return true;
+    }
+    p.a.dL_dray_o[3 * (size_t)ray] = s.dro_x; p.a.dL_dray_o[3 * (size_t)ray + 1] = s.dro_y; p.a.dL_dray_o[3 * (size_t)ray + 2] = s.dro_z;
+    p.a.dL_dray_d[3 * (size_t)ray] = s.drd_x; p.a.dL_dray_d[3 * (size_t)ray + 1] = s.drd_y; p.a.dL_dray_d[3 * (size_t)ray + 2] = s.drd_z;
+    return false;
+}
+
+// backward.cu:683-703 (specular product over all bounces and the colour "behind" each one), then the first segment
+__device__ __forceinline__ bool bwd_init_state(const BwdParams& p, int ray, BwdState& s) {
+    const dst_trace_inputs& in = p.a.in;
+    const float* mid = p.a.mid_val + (size_t)ray * in.mid_stride;
+    s.Cp0 = __ldg(p.a.out_rgb + 3 * (size_t)ray); s.Cp1 = __ldg(p.a.out_rgb + 3 * (size_t)ray + 1); s.Cp2 = __ldg(p.a.out_rgb + 3 * (size_t)ray + 2);
+    s.cp0 = s.cp1 = s.cp2 = 0.f;
+    s.s_prod = 1.0f;
+    for (int i = 0; i < in.max_trace_depth; i++) {
+        const float4 m3 = __ldg(reinterpret_cast<const float4*>(mid + i * DST_MID_CHANNELS) + 3);
+        const float4 m2 = __ldg(reinterpret_cast<const float4*>(mid + i * DST_MID_CHANNELS) + 2);
+        s.Cp0 += s.s_prod * (s.cp0 - m3.y); s.Cp1 += s.s_prod * (s.cp1 - m3.z); s.Cp2 += s.s_prod * (s.cp2 - m3.w);
+        s.cp0 = m3.y; s.cp1 = m3.z; s.cp2 = m3.w;
+        s.s_prod *= m2.w;
+    }
+    s.dro_x = s.dro_y = s.dro_z = 0.f; s.drd_x = s.drd_y = s.drd_z = 0.f;
+    s.dir_g0 = s.dir_g1 = s.dir_g2 = 0.f; s.pad0 = s.pad1 = s.pad2 = 0;
+    return bwd_next_segment(p, ray, s, in.max_trace_depth);
+}
+
+// Re-composites one gathered chunk of segment s.seg and accumulates the gradients of every
+// contributing hit (backward.cu:429-655). Returns true while the ray needs another enumeration.
+template <bool DIAG, int KS>
+__device__ __forceinline__ bool bwd_shade(const BwdParams& p, int ray, BwdState& s, const unsigned long long* kb, int cnt, TraceCounters& tc) {
+    const dst_trace_inputs& in = p.a.in;
     const bool use_sh = in.colors_precomp == nullptr;
     const bool has_aux = in.others_precomp != nullptr;
     const int ncoef = (in.sh_degree + 1) * (in.sh_degree + 1);
     const bool sh_aligned = ((in.sh_coeffs * 3) & 3) == 0 && ((reinterpret_cast<uintptr_t>(in.shs) & 15) == 0);
     const bool dsh_aligned = ((in.sh_coeffs * 3) & 3) == 0 && ((reinterpret_cast<uintptr_t>(p.a.dL_dshs) & 15) == 0);
     const float bg0 = __ldg(in.background), bg1 = __ldg(in.background + 1), bg2 = __ldg(in.background + 2);
-    const float* mid = p.a.mid_val + (size_t)ray * in.mid_stride;
+    const float4* mp = reinterpret_cast<const float4*>(p.a.mid_val + (size_t)ray * in.mid_stride + s.seg * DST_MID_CHANNELS);
+    const float4 m1 = __ldg(mp + 1), m2 = __ldg(mp + 2), m3 = __ldg(mp + 3);
+    const float tot_dpt = m1.z, tot_acc = m1.w;
+    const V3 tot_n = v3(m2.x, m2.y, m2.z);
+    const float tot_o0 = m2.w, tot_o1 = m3.x, tot_c0 = m3.y, tot_c1 = m3.z, tot_c2 = m3.w;
+    const float sox = s.sox, soy = s.soy, soz = s.soz, sdx = s.sdx, sdy = s.sdy, sdz = s.sdz;
+    const float t_rgb0 = s.t_rgb0, t_rgb1 = s.t_rgb1, t_rgb2 = s.t_rgb2, t_dpt = s.t_dpt, t_acc = s.t_acc, t_aux0 = s.t_aux0, t_aux1 = s.t_aux1;
+    const V3 t_norm = v3(s.t_nx, s.t_ny, s.t_nz);
+    const float min_depth = s.seg == 0 ? (in.start_from_first ? 0.2f : 0.0f) : 0.06f;
+    const float T_threshold = 0.0001f;
+    const float T_final = 1.0f - tot_acc;
+    float C0 = s.C0, C1 = s.C1, C2 = s.C2, D = s.D, O0 = s.O0, O1 = s.O1;
+    V3 N = v3(s.Nx, s.Ny, s.Nz);
+    float T_prev = s.T_prev, T_next = 1.0f, dpt = s.dpt;
+    const float offset = s.offset;
+    int last_gidx = s.last_gidx, contributor = s.contributor;
+    V3 dL_dray_o = v3(s.dro_x, s.dro_y, s.dro_z), dL_dray_d = v3(s.drd_x, s.drd_y, s.drd_z);
+    int dir_gidx = s.dir_gidx; float dir_g0 = s.dir_g0, dir_g1 = s.dir_g1, dir_g2 = s.dir_g2;
+    float sb[16];
+    if (use_sh) sh_basis(in.sh_degree, sdx, sdy, sdz, sb);
+    if (DIAG) { if (s.chunk == 0) tc.segs++; }
 
-    const float g_rgb0 = __ldg(p.a.dL_drgb + 3 * ray), g_rgb1 = __ldg(p.a.dL_drgb + 3 * ray + 1), g_rgb2 = __ldg(p.a.dL_drgb + 3 * ray + 2);
-    const float g_dpt = __ldg(p.a.dL_ddpt + ray), g_acc = __ldg(p.a.dL_dacc + ray);
-    const V3 g_norm = v3(__ldg(p.a.dL_dnorm + 3 * ray), __ldg(p.a.dL_dnorm + 3 * ray + 1), __ldg(p.a.dL_dnorm + 3 * ray + 2));
-    const float g_aux0 = __ldg(p.a.dL_daux + 2 * ray), g_aux1 = __ldg(p.a.dL_daux + 2 * ray + 1);
+    bool stop = false;
+    for (int sl = 0; sl < cnt; sl++) {
+        const unsigned long long key = kb[sl * KS];
+        const int pidx = (int)(unsigned int)key;
+        const int gidx = pidx >> 1;
+        if (gidx == last_gidx) continue;
+        if (DIAG) tc.evals++;
+        SlotEval e;
+        const bool ok = eval_slot(key, offset, sox, soy, soz, sdx, sdy, sdz, min_depth, p.cache, gidx, e);
+        dpt = e.dpt;
+        if (!ok) continue;
+        const float alpha = e.alpha;
+        T_next = xmul(T_prev, xsub(1.0f, alpha));
+        if (T_next < T_threshold) { stop = true; break; }
+        contributor++;
+        if (contributor > DST_MAX_INTERSECTION) { stop = true; break; }
+        last_gidx = gidx;
+        if (DIAG) tc.contribs++;
+        const float w = xmul(alpha, T_prev);
+        const V3 normal = v3(e.nsign * e.r2.x, e.nsign * e.r2.y, e.nsign * e.r2.z);
+        float c0, c1, c2, k0 = 1.f, k1 = 1.f, k2 = 1.f;       // colour and its clamp mask
+        float csh[48];
+        if (use_sh) {
+            load_sh_row(in.shs + 3 * (size_t)gidx * in.sh_coeffs, 3 * ncoef, sh_aligned, csh);
+            c0 = sh_channel(ncoef, sb, csh, 0); c1 = sh_channel(ncoef, sb, csh, 1); c2 = sh_channel(ncoef, sb, csh, 2);
+            k0 = c0 < 0.f ? 0.f : 1.f; k1 = c1 < 0.f ? 0.f : 1.f; k2 = c2 < 0.f ? 0.f : 1.f;
+            c0 = fmaxf(c0, 0.f); c1 = fmaxf(c1, 0.f); c2 = fmaxf(c2, 0.f);
+        } else {
+            const float* cp = in.colors_precomp + 3 * (size_t)gidx;
+            c0 = __ldg(cp); c1 = __ldg(cp + 1); c2 = __ldg(cp + 2);
+        }
+        C0 = xadd(C0, xmul(w, c0)); C1 = xadd(C1, xmul(w, c1)); C2 = xadd(C2, xmul(w, c2));
+        float ox0 = 0.f, ox1 = 0.f;
+        if (has_aux) {
+            const float2 ax = __ldg(reinterpret_cast<const float2*>(in.others_precomp) + gidx);
+            ox0 = ax.x; ox1 = ax.y;
+            O0 = xadd(O0, xmul(w, ox0)); O1 = xadd(O1, xmul(w, ox1));
+        }
+        D = xadd(D, xmul(w, dpt));
+        N.x = xadd(N.x, xmul(w, normal.x)); N.y = xadd(N.y, xmul(w, normal.y)); N.z = xadd(N.z, xmul(w, normal.z));
 
-    V3 dL_dray_o = v3(0.f, 0.f, 0.f), dL_dray_d = v3(0.f, 0.f, 0.f);
+        // gradient w.r.t. alpha from every composited quantity (backward.cu:529-568)
+        const float inv = 1.0f / (1.0f - alpha);
+        float dL_dalpha = t_rgb0 * (T_prev * c0 - (tot_c0 - C0) * inv) + t_rgb1 * (T_prev * c1 - (tot_c1 - C1) * inv) +
+                          t_rgb2 * (T_prev * c2 - (tot_c2 - C2) * inv);
+        dL_dalpha += (t_rgb0 * bg0 + t_rgb1 * bg1 + t_rgb2 * bg2) * (-T_final * inv);   // background counted a second time, as the reference does
+        if (has_aux) dL_dalpha += t_aux0 * (T_prev * ox0 - (tot_o0 - O0) * inv) + t_aux1 * (T_prev * ox1 - (tot_o1 - O1) * inv);
+        dL_dalpha += t_dpt * (T_prev * dpt - (tot_dpt - D) * inv);
+        dL_dalpha += t_norm.x * (T_prev * normal.x - (tot_n.x - N.x) * inv) + t_norm.y * (T_prev * normal.y - (tot_n.y - N.y) * inv) +
+                     t_norm.z * (T_prev * normal.z - (tot_n.z - N.z) * inv);
+        dL_dalpha += t_acc * (T_prev - tot_acc * inv);      // the reference's running weight sum stays 0 (backward.cu:359, 568)
 
-    // backward.cu:683-703: specular product over all bounces and the colour "behind" each one
-    float Cp0 = __ldg(p.a.out_rgb + 3 * ray), Cp1 = __ldg(p.a.out_rgb + 3 * ray + 1), Cp2 = __ldg(p.a.out_rgb + 3 * ray + 2);
-    float cp0 = 0.f, cp1 = 0.f, cp2 = 0.f;
-    float s_prod = 1.0f;
-    for (int i = 0; i < depth; i++) {
-        const float4 m3 = __ldg(reinterpret_cast<const float4*>(mid + i * DST_MID_CHANNELS) + 3);
-        const float4 m2 = __ldg(reinterpret_cast<const float4*>(mid + i * DST_MID_CHANNELS) + 2);
-        Cp0 += s_prod * (cp0 - m3.y); Cp1 += s_prod * (cp1 - m3.z); Cp2 += s_prod * (cp2 - m3.w);
-        cp0 = m3.y; cp1 = m3.z; cp2 = m3.w;
-        s_prod *= m2.w;
-    }
+        const float opac = e.r2.w, G = e.G;
+        const float dL_dG = dL_dalpha * opac;
+        const float pc = (opac * G) > 0.99f ? 0.0f : 1.0f;
+        const float dL_dopac = dL_dalpha * G * pc;
 
-    for (int i = depth; i >= 0; i--) {
-        const float4* mp = reinterpret_cast<const float4*>(mid + i * DST_MID_CHANNELS);
-        const float4 m0 = __ldg(mp), m1 = __ldg(mp + 1), m2 = __ldg(mp + 2), m3 = __ldg(mp + 3);
-        const float sox = m0.x, soy = m0.y, soz = m0.z, sdx = m0.w, sdy = m1.x, sdz = m1.y;
-        const float tot_dpt = m1.z, tot_acc = m1.w;
-        const V3 tot_n = v3(m2.x, m2.y, m2.z);
-        const float tot_o0 = m2.w, tot_o1 = m3.x, tot_c0 = m3.y, tot_c1 = m3.z, tot_c2 = m3.w;
-        const float s_prev = i > 0 ? __ldg(mid + (i - 1) * DST_MID_CHANNELS + 11) : 1.0f;
-        if (sqrtf(sdx * sdx + sdy * sdy + sdz * sdz) == 0.0f || s_prev <= in.specular_threshold) continue;    // :724
-
-        const float f_this = (i == depth) ? 1.0f : 1.0f - tot_o0;
-        const float t_rgb0 = g_rgb0 * f_this * s_prod, t_rgb1 = g_rgb1 * f_this * s_prod, t_rgb2 = g_rgb2 * f_this * s_prod;   // :760
-        s_prod /= s_prev;                                                                                     // :762
-        float t_dpt = 0.f, t_acc = 0.f, t_aux0 = 0.f, t_aux1 = 0.f;
-        V3 t_norm = v3(0.f, 0.f, 0.f);
-        if (i != depth) {
-            // :769-774
-            t_aux0 += g_rgb0 * (Cp0 / tot_o0) + g_rgb1 * (Cp1 / tot_o0) + g_rgb2 * (Cp2 / tot_o0);
-            if (i > 0) {
-                const float4 pm3 = __ldg(reinterpret_cast<const float4*>(mid + (i - 1) * DST_MID_CHANNELS) + 3);
-                cp0 = pm3.y; cp1 = pm3.z; cp2 = pm3.w;
-            } else { cp0 = cp1 = cp2 = 0.f; }
-            Cp0 -= s_prod * (cp0 - tot_c0); Cp1 -= s_prod * (cp1 - tot_c1); Cp2 -= s_prod * (cp2 - tot_c2);
-            const float nl = sqrtf(dot(tot_n, tot_n));
-            if (nl != 0.0f) {                                                                                 // :778-790
-                const V3 d = v3(sdx, sdy, sdz);
-                dL_dray_d = dL_dray_d + 0.00001f * dL_dray_o;
-                const V3 n = (1.0f / nl) * tot_n;
-                t_dpt += dL_dray_o.x * sdx + dL_dray_o.y * sdy + dL_dray_o.z * sdz;
-                const V3 gm2 = -2.0f * dL_dray_d;
-                t_norm = t_norm + dnormvdv(tot_n, ddotndndn(n, d, gm2));
-                dL_dray_d = tot_dpt * dL_dray_o + dL_dray_d + ddotndndd(n, gm2);
+        // geometry (backward.cu:201-287, 581-607)
+        const float sx = e.r3.x, sy = e.r3.y, u = e.u, v = e.v;
+        const V3 R0 = v3(e.r0.x, e.r0.y, e.r0.z), R1 = v3(e.r1.x, e.r1.y, e.r1.z);
+        const V3 pm = v3(__ldg(in.means3D + 3 * (size_t)gidx), __ldg(in.means3D + 3 * (size_t)gidx + 1), __ldg(in.means3D + 3 * (size_t)gidx + 2));
+        const V3 rel = v3(e.X - pm.x, e.Y - pm.y, e.Z - pm.z);
+        const float kk = dL_dG * pc;
+        const float dL_du = kk * -G * u, dL_dv = kk * -G * v;
+        V3 dR0 = (dL_du / sx) * rel, dR1 = (dL_dv / sy) * rel;
+        const V3 dR2 = v3(t_norm.x * w * e.nsign, t_norm.y * w * e.nsign, t_norm.z * w * e.nsign);
+        float dsx = kk * (G * u * u / sx), dsy = kk * (G * v * v / sy);
+        V3 dmean = (kk * G) * ((u / sx) * R0 + (v / sy) * R1);
+        const V3 dxyz = (dL_du / sx) * R0 + (dL_dv / sy) * R1;
+        const V3 rd = v3(sdx, sdy, sdz), ro = v3(sox, soy, soz);
+        const float dL_dd = t_dpt * w + dot(dxyz, rd);
+        V3 p1, p2, p3; float h1x, h1y, h2x, h2y, h3x, h3y;
+        {
+            const float4* vq = reinterpret_cast<const float4*>(in.vertices + 12 * (size_t)gidx);
+            const float4 va = __ldg(vq), vb = __ldg(vq + 1), vc = __ldg(vq + 2);
+            if ((pidx & 1) == 0) {
+                p1 = v3(va.x, va.y, va.z); p2 = v3(va.w, vb.x, vb.y); p3 = v3(vb.z, vb.w, vc.x);
+                h1x = -3.f; h1y = 3.f; h2x = -3.f; h2y = -3.f; h3x = 3.f; h3y = 3.f;
+            } else {
+                p1 = v3(va.w, vb.x, vb.y); p2 = v3(vb.z, vb.w, vc.x); p3 = v3(vc.y, vc.z, vc.w);
+                h1x = -3.f; h1y = -3.f; h2x = 3.f; h2y = 3.f; h3x = 3.f; h3y = -3.f;
             }
         }
-        if (i == 0) { t_dpt += g_dpt; t_acc += g_acc; t_norm = t_norm + g_norm; t_aux0 += g_aux0; t_aux1 += g_aux1; }   // :793-802
+        const V3 n = cross(p2 - p1, p3 - p1);
+        const V3 cvec = p1 - ro;
+        const float pp = dot(n, cvec), qq = dot(n, rd);
+        const float iq = 1.0f / qq;
+        const V3 dn = iq * (cvec - (pp * iq) * rd);
+        const V3 dv1 = dL_dd * cross(p2 - p3, dn) + (dL_dd * iq) * n;
+        const V3 dv2 = dL_dd * cross(p3 - p1, dn);
+        const V3 dv3 = dL_dd * cross(p1 - p2, dn);
+        dL_dray_o = dL_dray_o + dxyz - (dL_dd * iq) * n;
+        if (!use_sh) dL_dray_d = dL_dray_d + dpt * dxyz - (dL_dd * pp * iq * iq) * n;   // with SH the value is replaced below
+        const V3 shx = h1x * dv1 + h2x * dv2 + h3x * dv3, shy = h1y * dv1 + h2y * dv2 + h3y * dv3;
+        dR0 = dR0 + sx * shx; dR1 = dR1 + sy * shy;
+        dsx += dot(R0, shx); dsy += dot(R1, shy);
+        dmean = dmean + dv1 + dv2 + dv3;
+        // quaternion (auxiliary.h:433-477; no gradient through the normalisation)
+        const float4 q = __ldg(reinterpret_cast<const float4*>(in.rotations) + gidx);
+        const float qs = rsqrtf(q.w * q.w + q.x * q.x + q.y * q.y + q.z * q.z);
+        const float qw = q.x * qs, qx = q.y * qs, qy = q.z * qs, qz = q.w * qs;
+        const float dq0 = 2.f * (qx * (dR1.z - dR2.y) + qy * (dR2.x - dR0.z) + qz * (dR0.y - dR1.x));
+        const float dq1 = 2.f * (-2.f * qx * (dR1.y + dR2.z) + qy * (dR0.y + dR1.x) + qz * (dR0.z + dR2.x) + qw * (dR1.z - dR2.y));
+        const float dq2 = 2.f * (qx * (dR0.y + dR1.x) - 2.f * qy * (dR0.x + dR2.z) + qz * (dR1.z + dR2.y) + qw * (dR2.x - dR0.z));
+        const float dq3 = 2.f * (qx * (dR0.z + dR2.x) + qy * (dR1.z + dR2.y) - 2.f * qz * (dR0.x + dR1.y) + qw * (dR0.y - dR1.x));
 
-        // ---- re-trace of segment i with gradients (backward.cu:332-655) ----
-        const float min_depth = i == 0 ? (in.start_from_first ? 0.2f : 0.0f) : 0.06f;
-        const float T_threshold = 0.0001f;
-        const float T_final = 1.0f - tot_acc;
-        float C0 = 0.f, C1 = 0.f, C2 = 0.f, D = 0.f, O0 = 0.f, O1 = 0.f;
-        V3 N = v3(0.f, 0.f, 0.f);
-        float T_prev = 1.0f, T_next = 1.0f, dpt = 0.0f, offset = 0.0f;
-        int last_gidx = -1, contributor = 0;
-        float tox = sox, toy = soy, toz = soz;
-        float sb[16];
-        if (use_sh) sh_basis(in.sh_degree, sdx, sdy, sdz, sb);
-        int dir_gidx = -1; float dir_g0 = 0.f, dir_g1 = 0.f, dir_g2 = 0.f;     // last SH contribution, for the direction gradient
-        if (DIAG) tc.segs++;
+        // per-surfel accumulation (backward.cu:543, 557, 578, 610-626)
+        float* row = p.arena + (size_t)gidx * DST_ARENA_FLOATS;
+        red4(row, dq0, dq1, dq2, dq3);
+        red4(row + 4, dmean.x, dmean.y, dmean.z, dL_dopac);
+        const float hd = 0.5f * dpt;
+        red4(row + 8, dmean.x * hd, dmean.y * hd, dmean.z * hd, 0.f);
+        red4(row + 12, dsx, dsy, has_aux ? t_aux0 * w : 0.f, has_aux ? t_aux1 * w : 0.f);
+        const float dc0 = t_rgb0 * w, dc1 = t_rgb1 * w, dc2 = t_rgb2 * w;
+        red4(row + 16, dc0, dc1, dc2, 0.f);
+        if (use_sh) {
+            const float m0c = dc0 * k0, m1c = dc1 * k1, m2c = dc2 * k2;
+            float* dsh = p.a.dL_dshs + 3 * (size_t)gidx * in.sh_coeffs;
+            if (dsh_aligned) {
+                // 3*ncoef floats as 4-float reductions (ncoef = 4, 16 -> 3, 12 vectors; 1, 9 leave a scalar tail)
+                const int nf = 3 * ncoef, nv = nf >> 2;
+#pragma unroll
+                for (int q4 = 0; q4 < 12; q4++) {
+                    if (q4 < nv) {
+                        float o4[4];
+#pragma unroll
+                        for (int l = 0; l < 4; l++) { const int f = 4 * q4 + l; const int j = f / 3, ch = f - 3 * j; o4[l] = sb[j] * (ch == 0 ? m0c : ch == 1 ? m1c : m2c); }
+                        red4(dsh + 4 * q4, o4[0], o4[1], o4[2], o4[3]);
+                    }
+                }
+                for (int f = nv << 2; f < nf; f++) { const int j = f / 3, ch = f - 3 * j; atomicAdd(dsh + f, sb[j] * (ch == 0 ? m0c : ch == 1 ? m1c : m2c)); }
+            } else {
+                for (int j = 0; j < ncoef; j++) { atomicAdd(dsh + 3 * j, sb[j] * m0c); atomicAdd(dsh + 3 * j + 1, sb[j] * m1c); atomicAdd(dsh + 3 * j + 2, sb[j] * m2c); }
+            }
+            dir_gidx = gidx; dir_g0 = m0c; dir_g1 = m1c; dir_g2 = m2c;
+        }
+        T_prev = T_next;
+    }
+    s.C0 = C0; s.C1 = C1; s.C2 = C2; s.D = D; s.O0 = O0; s.O1 = O1; s.Nx = N.x; s.Ny = N.y; s.Nz = N.z;
+    s.T_prev = T_prev; s.dpt = dpt; s.last_gidx = last_gidx; s.contributor = contributor;
+    s.dro_x = dL_dray_o.x; s.dro_y = dL_dray_o.y; s.dro_z = dL_dray_o.z;
+    s.drd_x = dL_dray_d.x; s.drd_y = dL_dray_d.y; s.drd_z = dL_dray_d.z;
+    s.dir_gidx = dir_gidx; s.dir_g0 = dir_g0; s.dir_g1 = dir_g1; s.dir_g2 = dir_g2;
+    s.chunk++;
+    bool seg_done = stop || T_next < T_threshold || cnt < DST_CHUNK || contributor > DST_MAX_INTERSECTION;
+    if (!seg_done && s.chunk >= DST_MAX_CHUNKS) { atomicOr(p.status, DST_STATUS_CHUNK_LIMIT); seg_done = true; }
+    if (!seg_done) {
+        s.offset = (float)((double)dpt + 0.00001);
+        return true;
+    }
+    // With SH colours the reference ASSIGNS the SH direction gradient to the ray-direction
+    // accumulator at every contribution (backward.cu:165, 631-632), so what survives a segment
+    // is the value of its last contribution.
+    if (use_sh && dir_gidx >= 0) {
+        float csh[48], sj[16];
+        load_sh_row(in.shs + 3 * (size_t)dir_gidx * in.sh_coeffs, 3 * ncoef, sh_aligned, csh);
+#pragma unroll
+        for (int j = 0; j < 16; j++) sj[j] = j < ncoef ? csh[3 * j] * dir_g0 + csh[3 * j + 1] * dir_g1 + csh[3 * j + 2] * dir_g2 : 0.f;
+        const V3 g = sh_dir_grad(in.sh_degree, sj, sdx, sdy, sdz);
+        s.drd_x = g.x; s.drd_y = g.y; s.drd_z = g.z;
+    }
+    return bwd_next_segment(p, ray, s, s.seg - 1);
+}
 
-        for (int chunk = 0;; chunk++) {
-            if (chunk >= DST_MAX_CHUNKS) { atomicOr(p.status, DST_STATUS_CHUNK_LIMIT); break; }
-            const int cnt = knearest<false, DIAG, BWD_THREADS>(p.bvh, tox, toy, toz, sdx, sdy, sdz, kb, p.status, tc);
+__global__ void __launch_bounds__(256) k_bwd_init(const __grid_constant__ BwdParams p, long long slots) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= slots) return;
+    if (i == 0) p.counts[0] = (int)slots;
+    int ray = ray_of_slot(i, p.a.in.H, p.a.in.W, p.tiled != 0);
+    if (ray >= 0) {
+        BwdState s;
+        if (bwd_init_state(p, ray, s)) {
+            bwd_store_state(p.state, ray, s);
+            EnumReq q;
+            bwd_request(s, q);
+            p.req[ray] = q;
+        } else ray = -1;       // no segment to differentiate: the (zero) ray gradients are already written
+    }
+    p.list[0][i] = ray;
+}
+
+template <bool DIAG>
+__global__ void __launch_bounds__(BWD_THREADS) k_bwd_shade(const __grid_constant__ BwdParams p, int round) {
+    const int n = p.counts[round];
+    if (n < p.min_count) return;
+    const int* list = p.list[round & 1];
+    int* next_list = p.list[(round + 1) & 1];
+    TraceCounters tc = { 0, 0, 0, 0, 0, 0 };
+    const int n_pad = (n + 31) & ~31;
+    for (int i = blockIdx.x * BWD_THREADS + threadIdx.x; i < n_pad; i += gridDim.x * BWD_THREADS) {
+        const int ray = i < n ? list[i] : -1;
+        bool alive = false;
+        if (ray >= 0) {
+            BwdState s;
+            bwd_load_state(p.state, ray, s);
+            alive = bwd_shade<DIAG, 1>(p, ray, s, p.kbuf + (size_t)ray * DST_CHUNK, p.kcnt[ray], tc);
+            if (alive) {
+                bwd_store_state(p.state, ray, s);
+                EnumReq q;
+                bwd_request(s, q);
+                p.req[ray] = q;
+            }
+        }
+        append_alive(alive, ray, next_list, p.counts + round + 1);
+    }
+    if (DIAG && p.a.counters) {
+        atomicAdd(p.a.counters + 0, tc.segs); atomicAdd(p.a.counters + 4, tc.evals); atomicAdd(p.a.counters + 5, tc.contribs);
+    }
+}
+
+template <bool DIAG>
+__global__ void __launch_bounds__(BWD_THREADS) k_bwd_tail(const __grid_constant__ BwdParams p) {
+    __shared__ unsigned long long kshared[DST_CHUNK * BWD_THREADS];
+    const int round = first_skipped_round(p.counts, p.rounds, p.min_count);
+    const int n = p.counts[round];
+    const int* list = p.list[round & 1];
+    unsigned long long* kb = kshared + threadIdx.x;
+    TraceCounters tc = { 0, 0, 0, 0, 0, 0 };
+    for (int i = blockIdx.x * BWD_THREADS + threadIdx.x; i < n; i += gridDim.x * BWD_THREADS) {
+        const int ray = list[i];
+        if (ray < 0) continue;
+        BwdState s;
+        bwd_load_state(p.state, ray, s);
+        bool alive = true;
+        while (alive) {
+            EnumReq q;
+            bwd_request(s, q);
+            const int cnt = knearest<false, DIAG, BWD_THREADS>(p.bvh, q.ox, q.oy, q.oz, q.dx, q.dy, q.dz, kb, p.status, tc, q.kmax0);
             if (DIAG) tc.enums++;
-            bool stop = false;
-            for (int s = 0; s < cnt; s++) {
-                const unsigned long long key = kb[s * BWD_THREADS];
-                const int pidx = (int)(unsigned int)key;
-                const int gidx = pidx >> 1;
-                if (gidx == last_gidx) continue;
-                if (DIAG) tc.evals++;
-                SlotEval e;
-                const bool ok = eval_slot(key, offset, sox, soy, soz, sdx, sdy, sdz, min_depth, p.cache, gidx, e);
-                dpt = e.dpt;
-                if (!ok) continue;
-                const float alpha = e.alpha;
-                T_next = xmul(T_prev, xsub(1.0f, alpha));
-                if (T_next < T_threshold) { stop = true; break; }
-                contributor++;
-                if (contributor > DST_MAX_INTERSECTION) { stop = true; break; }
-                last_gidx = gidx;
-                if (DIAG) tc.contribs++;
-                const float w = xmul(alpha, T_prev);
-                const V3 normal = v3(e.nsign * e.r2.x, e.nsign * e.r2.y, e.nsign * e.r2.z);
-                float c0, c1, c2, k0 = 1.f, k1 = 1.f, k2 = 1.f;       // colour and its clamp mask
-                float csh[48];
-                if (use_sh) {
-                    load_sh_row(in.shs + 3 * (size_t)gidx * in.sh_coeffs, 3 * ncoef, sh_aligned, csh);
-                    c0 = sh_channel(ncoef, sb, csh, 0); c1 = sh_channel(ncoef, sb, csh, 1); c2 = sh_channel(ncoef, sb, csh, 2);
-                    k0 = c0 < 0.f ? 0.f : 1.f; k1 = c1 < 0.f ? 0.f : 1.f; k2 = c2 < 0.f ? 0.f : 1.f;
-                    c0 = fmaxf(c0, 0.f); c1 = fmaxf(c1, 0.f); c2 = fmaxf(c2, 0.f);
-                } else {
-                    const float* cp = in.colors_precomp + 3 * (size_t)gidx;
-                    c0 = __ldg(cp); c1 = __ldg(cp + 1); c2 = __ldg(cp + 2);
-                }
-                C0 = xadd(C0, xmul(w, c0)); C1 = xadd(C1, xmul(w, c1)); C2 = xadd(C2, xmul(w, c2));
-                float ox0 = 0.f, ox1 = 0.f;
-                if (has_aux) {
-                    const float2 ax = __ldg(reinterpret_cast<const float2*>(in.others_precomp) + gidx);
-                    ox0 = ax.x; ox1 = ax.y;
-                    O0 = xadd(O0, xmul(w, ox0)); O1 = xadd(O1, xmul(w, ox1));
-                }
-                D = xadd(D, xmul(w, dpt));
-                N.x = xadd(N.x, xmul(w, normal.x)); N.y = xadd(N.y, xmul(w, normal.y)); N.z = xadd(N.z, xmul(w, normal.z));
-
-                // gradient w.r.t. alpha from every composited quantity (backward.cu:529-568)
-                const float inv = 1.0f / (1.0f - alpha);
-                float dL_dalpha = t_rgb0 * (T_prev * c0 - (tot_c0 - C0) * inv) + t_rgb1 * (T_prev * c1 - (tot_c1 - C1) * inv) +
-                                  t_rgb2 * (T_prev * c2 - (tot_c2 - C2) * inv);
-                dL_dalpha += (t_rgb0 * bg0 + t_rgb1 * bg1 + t_rgb2 * bg2) * (-T_final * inv);   // background counted a second time, as the reference does
-                if (has_aux) dL_dalpha += t_aux0 * (T_prev * ox0 - (tot_o0 - O0) * inv) + t_aux1 * (T_prev * ox1 - (tot_o1 - O1) * inv);
-                dL_dalpha += t_dpt * (T_prev * dpt - (tot_dpt - D) * inv);
-                dL_dalpha += t_norm.x * (T_prev * normal.x - (tot_n.x - N.x) * inv) + t_norm.y * (T_prev * normal.y - (tot_n.y - N.y) * inv) +
-                             t_norm.z * (T_prev * normal.z - (tot_n.z - N.z) * inv);
-                dL_dalpha += t_acc * (T_prev - tot_acc * inv);      // the reference's running weight sum stays 0 (backward.cu:359, 568)
-
-                const float opac = e.r2.w, G = e.G;
-                const float dL_dG = dL_dalpha * opac;
-                const float pc = (opac * G) > 0.99f ? 0.0f : 1.0f;
-                const float dL_dopac = dL_dalpha * G * pc;
-
-                // geometry (backward.cu:201-287, 581-607)
-                const float sx = e.r3.x, sy = e.r3.y, u = e.u, v = e.v;
-                const V3 R0 = v3(e.r0.x, e.r0.y, e.r0.z), R1 = v3(e.r1.x, e.r1.y, e.r1.z);
-                const V3 pm = v3(__ldg(in.means3D + 3 * (size_t)gidx), __ldg(in.means3D + 3 * (size_t)gidx + 1), __ldg(in.means3D + 3 * (size_t)gidx + 2));
-                const V3 rel = v3(e.X - pm.x, e.Y - pm.y, e.Z - pm.z);
-                const float kk = dL_dG * pc;
-                const float dL_du = kk * -G * u, dL_dv = kk * -G * v;
-                V3 dR0 = (dL_du / sx) * rel, dR1 = (dL_dv / sy) * rel;
-                const V3 dR2 = v3(t_norm.x * w * e.nsign, t_norm.y * w * e.nsign, t_norm.z * w * e.nsign);
-                float dsx = kk * (G * u * u / sx), dsy = kk * (G * v * v / sy);
-                V3 dmean = (kk * G) * ((u / sx) * R0 + (v / sy) * R1);
-                const V3 dxyz = (dL_du / sx) * R0 + (dL_dv / sy) * R1;
-                const V3 rd = v3(sdx, sdy, sdz), ro = v3(sox, soy, soz);
-                const float dL_dd = t_dpt * w + dot(dxyz, rd);
-                V3 p1, p2, p3; float h1x, h1y, h2x, h2y, h3x, h3y;
-                {
-                    const float4* vq = reinterpret_cast<const float4*>(in.vertices + 12 * (size_t)gidx);
-                    const float4 va = __ldg(vq), vb = __ldg(vq + 1), vc = __ldg(vq + 2);
-                    if ((pidx & 1) == 0) {
-                        p1 = v3(va.x, va.y, va.z); p2 = v3(va.w, vb.x, vb.y); p3 = v3(vb.z, vb.w, vc.x);
-                        h1x = -3.f; h1y = 3.f; h2x = -3.f; h2y = -3.f; h3x = 3.f; h3y = 3.f;
-                    } else {
-                        p1 = v3(va.w, vb.x, vb.y); p2 = v3(vb.z, vb.w, vc.x); p3 = v3(vc.y, vc.z, vc.w);
-                        h1x = -3.f; h1y = -3.f; h2x = 3.f; h2y = 3.f; h3x = 3.f; h3y = -3.f;
-                    }
-                }
-                const V3 n = cross(p2 - p1, p3 - p1);
-                const V3 cvec = p1 - ro;
-                const float pp = dot(n, cvec), qq = dot(n, rd);
-                const float iq = 1.0f / qq;
-                const V3 dn = iq * (cvec - (pp * iq) * rd);
-                const V3 dv1 = dL_dd * cross(p2 - p3, dn) + (dL_dd * iq) * n;
-                const V3 dv2 = dL_dd * cross(p3 - p1, dn);
-                const V3 dv3 = dL_dd * cross(p1 - p2, dn);
-                dL_dray_o = dL_dray_o + dxyz - (dL_dd * iq) * n;
-                if (!use_sh) dL_dray_d = dL_dray_d + dpt * dxyz - (dL_dd * pp * iq * iq) * n;   // with SH the value is replaced below
-                const V3 shx = h1x * dv1 + h2x * dv2 + h3x * dv3, shy = h1y * dv1 + h2y * dv2 + h3y * dv3;
-                dR0 = dR0 + sx * shx; dR1 = dR1 + sy * shy;
-                dsx += dot(R0, shx); dsy += dot(R1, shy);
-                dmean = dmean + dv1 + dv2 + dv3;
-                // quaternion (auxiliary.h:433-477; no gradient through the normalisation)
-                const float4 q = __ldg(reinterpret_cast<const float4*>(in.rotations) + gidx);
-                const float qs = rsqrtf(q.w * q.w + q.x * q.x + q.y * q.y + q.z * q.z);
-                const float qw = q.x * qs, qx = q.y * qs, qy = q.z * qs, qz = q.w * qs;
-                const float dq0 = 2.f * (qx * (dR1.z - dR2.y) + qy * (dR2.x - dR0.z) + qz * (dR0.y - dR1.x));
-                const float dq1 = 2.f * (-2.f * qx * (dR1.y + dR2.z) + qy * (dR0.y + dR1.x) + qz * (dR0.z + dR2.x) + qw * (dR1.z - dR2.y));
-                const float dq2 = 2.f * (qx * (dR0.y + dR1.x) - 2.f * qy * (dR0.x + dR2.z) + qz * (dR1.z + dR2.y) + qw * (dR2.x - dR0.z));
-                const float dq3 = 2.f * (qx * (dR0.z + dR2.x) + qy * (dR1.z + dR2.y) - 2.f * qz * (dR0.x + dR1.y) + qw * (dR0.y - dR1.x));
-
-                // per-surfel accumulation (backward.cu:543, 557, 578, 610-626)
-                float* row = p.arena + (size_t)gidx * DST_ARENA_FLOATS;
-                red4(row, dq0, dq1, dq2, dq3);
-                red4(row + 4, dmean.x, dmean.y, dmean.z, dL_dopac);
-                const float hd = 0.5f * dpt;
-                red4(row + 8, dmean.x * hd, dmean.y * hd, dmean.z * hd, 0.f);
-                red4(row + 12, dsx, dsy, has_aux ? t_aux0 * w : 0.f, has_aux ? t_aux1 * w : 0.f);
-                const float dc0 = t_rgb0 * w, dc1 = t_rgb1 * w, dc2 = t_rgb2 * w;
-                red4(row + 16, dc0, dc1, dc2, 0.f);
-                if (use_sh) {
-                    const float m0c = dc0 * k0, m1c = dc1 * k1, m2c = dc2 * k2;
-                    float* dsh = p.a.dL_dshs + 3 * (size_t)gidx * in.sh_coeffs;
-                    if (dsh_aligned) {
-                        // 3*ncoef floats as 4-float reductions (ncoef = 4, 16 -> 3, 12 vectors; 1, 9 leave a scalar tail)
-                        const int nf = 3 * ncoef, nv = nf >> 2;
-#pragma unroll
-                        for (int q4 = 0; q4 < 12; q4++) {
-                            if (q4 < nv) {
-                                float o4[4];
-#pragma unroll
-                                for (int l = 0; l < 4; l++) { const int f = 4 * q4 + l; const int j = f / 3, ch = f - 3 * j; o4[l] = sb[j] * (ch == 0 ? m0c : ch == 1 ? m1c : m2c); }
-                                red4(dsh + 4 * q4, o4[0], o4[1], o4[2], o4[3]);
-                            }
-                        }
-                        for (int f = nv << 2; f < nf; f++) { const int j = f / 3, ch = f - 3 * j; atomicAdd(dsh + f, sb[j] * (ch == 0 ? m0c : ch == 1 ? m1c : m2c)); }
-                    } else {
-                        for (int j = 0; j < ncoef; j++) { atomicAdd(dsh + 3 * j, sb[j] * m0c); atomicAdd(dsh + 3 * j + 1, sb[j] * m1c); atomicAdd(dsh + 3 * j + 2, sb[j] * m2c); }
-                    }
-                    dir_gidx = gidx; dir_g0 = m0c; dir_g1 = m1c; dir_g2 = m2c;
-                }
-                T_prev = T_next;
-            }
-            if (stop || T_next < T_threshold || cnt < DST_CHUNK || contributor > DST_MAX_INTERSECTION) break;
-            offset = (float)((double)dpt + 0.00001);
-            tox = xadd(sox, xmul(offset, sdx)); toy = xadd(soy, xmul(offset, sdy)); toz = xadd(soz, xmul(offset, sdz));
-        }
-        // With SH colours the reference ASSIGNS the SH direction gradient to the ray-direction
-        // accumulator at every contribution (backward.cu:165, 631-632), so what survives a segment
-        // is the value of its last contribution.
-        if (use_sh && dir_gidx >= 0) {
-            float csh[48], sj[16];
-            load_sh_row(in.shs + 3 * (size_t)dir_gidx * in.sh_coeffs, 3 * ncoef, sh_aligned, csh);
-#pragma unroll
-            for (int j = 0; j < 16; j++) sj[j] = j < ncoef ? csh[3 * j] * dir_g0 + csh[3 * j + 1] * dir_g1 + csh[3 * j + 2] * dir_g2 : 0.f;
-            dL_dray_d = sh_dir_grad(in.sh_degree, sj, sdx, sdy, sdz);
+            alive = bwd_shade<DIAG, BWD_THREADS>(p, ray, s, kb, cnt, tc);
         }
     }
-    p.a.dL_dray_o[3 * ray] = dL_dray_o.x; p.a.dL_dray_o[3 * ray + 1] = dL_dray_o.y; p.a.dL_dray_o[3 * ray + 2] = dL_dray_o.z;
-    p.a.dL_dray_d[3 * ray] = dL_dray_d.x; p.a.dL_dray_d[3 * ray + 1] = dL_dray_d.y; p.a.dL_dray_d[3 * ray + 2] = dL_dray_d.z;
     if (DIAG && p.a.counters) {
         atomicAdd(p.a.counters + 0, tc.segs); atomicAdd(p.a.counters + 1, tc.enums); atomicAdd(p.a.counters + 2, tc.nodes);
         atomicAdd(p.a.counters + 3, tc.quads); atomicAdd(p.a.counters + 4, tc.evals); atomicAdd(p.a.counters + 5, tc.contribs);
@@ -378,11 +524,31 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
     BwdParams p;
     p.a = *a; p.bvh = dst_bvh_view(h); p.cache = h->cache; p.arena = h->arena; p.status = h->status;
     p.tiled = a->in.H >= 16;
-    const long long R = (long long)a->in.H * a->in.W;
-    const long long blocks = p.tiled ? (long long)((a->in.W + 15) / 16) * ((a->in.H + 7) / 8) : (R + BWD_THREADS - 1) / BWD_THREADS;
+    const long long slots = slots_of_grid(a->in.H, a->in.W, p.tiled != 0);
+    rc = dst_ensure_wavefront(h, slots, sizeof(BwdState));
+    if (rc != DST_OK) return rc;
+    p.state = h->wf_state; p.req = static_cast<EnumReq*>(h->wf_req); p.kbuf = h->wf_kbuf; p.kcnt = h->wf_kcnt;
+    p.list[0] = h->wf_list[0]; p.list[1] = h->wf_list[1]; p.counts = h->wf_counts;
+    const bool wave = slots >= h->wf_min_rays;
+    p.rounds = wave ? DST_WF_ROUNDS : 0;
+    p.min_count = wave ? (int)(slots / 64 > 4096 ? slots / 64 : 4096) : 1;
+    const bool diag = a->counters != nullptr;
+    DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * (DST_WF_ROUNDS + 2), st));
     dst_prof_mark(h, 2, 0, st);
-    if (a->counters) k_backward<true><<<(unsigned int)blocks, BWD_THREADS, 0, st>>>(p);
-    else k_backward<false><<<(unsigned int)blocks, BWD_THREADS, 0, st>>>(p);
+    k_bwd_init<<<(unsigned int)((slots + 255) / 256), 256, 0, st>>>(p, slots);
+    const int g_enum = dst_wavefront_grid(h, slots, ENUM_THREADS, 10), g_shade = dst_wavefront_grid(h, slots, BWD_THREADS, 4);
+    for (int r = 0; r < p.rounds; r++) {
+        if (diag) {
+            k_enum<true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters);
+            k_bwd_shade<true><<<g_shade, BWD_THREADS, 0, st>>>(p, r);
+        } else {
+            k_enum<false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr);
+            k_bwd_shade<false><<<g_shade, BWD_THREADS, 0, st>>>(p, r);
+        }
+    }
+    const int g_tail = dst_wavefront_grid(h, wave ? p.min_count : slots, BWD_THREADS, 4);
+    if (diag) k_bwd_tail<true><<<g_tail, BWD_THREADS, 0, st>>>(p);
+    else k_bwd_tail<false><<<g_tail, BWD_THREADS, 0, st>>>(p);
     dst_prof_mark(h, 2, 1, st);
     DST_CUDA_TRY(h, cudaGetLastError());
     k_unpack<<<(unsigned int)((P + 255) / 256), 256, 0, st>>>((int)P, h->arena, a->dL_drotations, a->dL_dmeans3D, a->dL_dopacities,

@@ -261,7 +261,7 @@ __global__ void __launch_bounds__(256) k_refit(const float* __restrict__ verts, 
     quads[3 * (size_t)pos + 0] = make_float4(q.p0x, q.p0y, q.p0z, q.nx);
     quads[3 * (size_t)pos + 1] = make_float4(q.ny, q.nz, q.wux, q.wuy);
     quads[3 * (size_t)pos + 2] = make_float4(q.wuz, q.wvx, q.wvy, q.wvz);
-    leaf_gid[pos] = gid;
+    leaf_gid[pos] = gid << 4;       // reference = surfel id << 4 | sub-rectangle
     float lo[3], hi[3];
     quad_box(v, lo, hi);
     int child = ~pos;
@@ -300,7 +300,7 @@ __global__ void __launch_bounds__(256) k_export_frames(int P, const float4* __re
     const int pos = blockIdx.x * blockDim.x + threadIdx.x;
     if (pos >= P) return;
     const float4 a = quads[3 * (size_t)pos], b = quads[3 * (size_t)pos + 1], c = quads[3 * (size_t)pos + 2];
-    float* o = out + 12 * (size_t)leaf_gid[pos];
+    float* o = out + 12 * (size_t)(leaf_gid[pos] >> 4);
     o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
     o[8] = c.x; o[9] = c.y; o[10] = c.z; o[11] = c.w;
 }
@@ -372,7 +372,7 @@ int dst_bvh_build_impl(dst_handle* h, const float* v, int64_t P, int rebuild, cu
         }
         // 8 passes: the sorted data is back in keys / vals
         if (n > 1) k_karras<<<(n - 1 + tpb - 1) / tpb, tpb, 0, st>>>(h->keys, n, h->nodes, h->leaf_parent);
-        h->P = P;
+        h->P = P; h->nrefs = P;
     }
     DST_CUDA_TRY(h, cudaMemsetAsync(h->arrive, 0, 4 * (size_t)(n > 1 ? n - 1 : 1), st));
     if (n == 1) k_single_leaf<<<1, 1, 0, st>>>(h->nodes, h->leaf_parent, h->arrive);

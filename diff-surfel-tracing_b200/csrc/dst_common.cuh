@@ -29,7 +29,8 @@ struct BvhView {
     const float4* quads;
     const int* leaf_gid;
     const float* header;
-    int P;
+    int P;          // surfels
+    int nrefs;      // leaves (>= P when large quads are split into several references)
 };
 
 // Per-surfel shading record rebuilt at the start of every trace call (parameters change each
@@ -47,6 +48,7 @@ struct dst_handle {
     char err[512];
     bool built;
     int64_t P;            // surfels of the current hierarchy
+    int64_t nrefs;        // leaves of the current hierarchy
     int64_t cap;          // surfels the build buffers can hold
     BvhNode* nodes;
     float4* quads;
@@ -62,6 +64,10 @@ struct dst_handle {
     float4* cache; int64_t cache_cap;
     float* arena;  int64_t arena_cap;
     int sm_count;
+    // ray scratch of the wavefront trace (grow-only): state records, enumeration requests, hit buffers, live lists
+    void* wf_state; size_t wf_state_bytes; void* wf_req; unsigned long long* wf_kbuf; int* wf_kcnt; int* wf_list[2]; int* wf_counts;
+    long long wf_cap;
+    long long wf_min_rays;        // launches with fewer rays skip the wavefront rounds
     // optional event timing (dst_profile_enable)
     int profiling;
     cudaEvent_t* ev[3];           // per kind: 2 * DST_PROF_SLOTS events (start, stop pairs)
@@ -92,6 +98,8 @@ int dst_knearest_impl(dst_handle* h, const float* ro, const float* rd, int64_t n
                       int32_t* counts, int brute, const float* t_cut, unsigned long long* counters, cudaStream_t st);
 int dst_prepare_cache(dst_handle* h, const dst_trace_inputs* in, cudaStream_t st);
 int dst_export_frames_impl(dst_handle* h, float* out, cudaStream_t st);
+int dst_ensure_wavefront(dst_handle* h, long long slots, size_t state_bytes);
+int dst_wavefront_grid(const dst_handle* h, long long slots, int threads, int per_sm);
 
 #ifdef __CUDACC__
 // ---------------------------------------------------------------------------------------------

@@ -2,15 +2,18 @@
 // (__raygen__ot 428-477, tracePath 318-424, traceRay 136-315, __anyhit__ot 481-525) and their
 // host launcher TraceSurfelsCUDA (trace_surfels.cpp:162-304).
 //
-// One thread per ray. Per ray segment: repeat { gather the 16 nearest quad hits with a pruned
-// hierarchy walk into a shared-memory k-buffer; composite them front to back } until the
-// transmittance threshold, the contribution cap or the end of the ray. Bounces re-enter the same
-// loop from the reflected ray.
+// The per-ray loop of the reference (bounces { enumerations { gather 16 hits; composite } }) is
+// flattened into a state machine: a ray's state is {segment, running sums, depth bookkeeping}, and
+// one step is "gather the 16 nearest hits from the moved origin" followed by "composite them and
+// decide": continue the segment, start the reflected segment, or finish. Large launches run the
+// steps as a wavefront (k_enum / k_fwd_shade rounds over the list of live rays, state in scratch
+// memory); the stragglers and small launches run in k_fwd_tail, one thread per ray to completion.
 #include "dst_trace.cuh"
 
 namespace {
 
-constexpr int FWD_THREADS = 128;
+constexpr int SHADE_THREADS = 128;
+constexpr int TAIL_THREADS = 128;
 
 struct FwdParams {
     dst_fwd_args a;
@@ -18,7 +21,28 @@ struct FwdParams {
     const float4* cache;
     unsigned int* status;
     int tiled;
+    // wavefront scratch
+    void* state;
+    EnumReq* req;
+    unsigned long long* kbuf;
+    int* kcnt;
+    int* list[2];
+    int* counts;
+    int min_count;
+    int rounds;
 };
+
+struct __align__(16) FwdState {
+    float sox, soy, soz, sdx;
+    float sdy, sdz, offset, dpt;
+    float T_prev, C0, C1, C2;
+    float D, Nx, Ny, Nz;
+    float O0, O1, s_prod, rgb0;
+    float rgb1, rgb2; int last_gidx, contributor;
+    int bounce, chunk, hit_count, pad0;
+    float pad1[4];
+};
+static_assert(sizeof(FwdState) == 128, "ray state is one 128-byte record");
 
 // Per-surfel shading record: tangent-frame rows from the quaternion exactly as
 // quat_to_rotmat_transpose does on an IEEE host (optix_tracer/auxiliary.h:403-429, with rsqrtf
@@ -49,153 +73,244 @@ __global__ void __launch_bounds__(256) k_prepare_cache(int P, const float* __res
     o[3] = make_float4(scales[2 * (size_t)g], scales[2 * (size_t)g + 1], 0.f, 0.f);
 }
 
-template <bool BRUTE, bool DIAG>
-__global__ void __launch_bounds__(FWD_THREADS) k_forward(const __grid_constant__ FwdParams p) {
-    __shared__ unsigned long long kbuf[DST_CHUNK * FWD_THREADS];
-    const dst_trace_inputs& in = p.a.in;
-    const long long ray = ray_of_thread(in.H, in.W, p.tiled != 0);
-    if (ray < 0) return;
-    unsigned long long* kb = kbuf + threadIdx.x;
-    TraceCounters tc = { 0, 0, 0, 0, 0, 0 };
+__device__ __forceinline__ void fwd_begin_segment(FwdState& s) {
+    s.offset = 0.f; s.dpt = 0.f; s.T_prev = 1.f;
+    s.C0 = s.C1 = s.C2 = 0.f; s.D = 0.f; s.Nx = s.Ny = s.Nz = 0.f; s.O0 = s.O1 = 0.f;
+    s.last_gidx = -1; s.contributor = 0; s.chunk = 0;
+}
 
-    const float rox = __ldg(in.ray_o + 3 * ray), roy = __ldg(in.ray_o + 3 * ray + 1), roz = __ldg(in.ray_o + 3 * ray + 2);
-    const float rdx = __ldg(in.ray_d + 3 * ray), rdy = __ldg(in.ray_d + 3 * ray + 1), rdz = __ldg(in.ray_d + 3 * ray + 2);
-    const float bg0 = __ldg(in.background), bg1 = __ldg(in.background + 1), bg2 = __ldg(in.background + 2);
+__device__ __forceinline__ void fwd_init_state(const FwdParams& p, int ray, FwdState& s) {
+    const dst_trace_inputs& in = p.a.in;
+    s.sox = __ldg(in.ray_o + 3 * (size_t)ray); s.soy = __ldg(in.ray_o + 3 * (size_t)ray + 1); s.soz = __ldg(in.ray_o + 3 * (size_t)ray + 2);
+    s.sdx = __ldg(in.ray_d + 3 * (size_t)ray); s.sdy = __ldg(in.ray_d + 3 * (size_t)ray + 1); s.sdz = __ldg(in.ray_d + 3 * (size_t)ray + 2);
+    s.s_prod = 1.f; s.rgb0 = s.rgb1 = s.rgb2 = 0.f; s.bounce = 0; s.hit_count = 0; s.pad0 = 0;
+    fwd_begin_segment(s);
+}
+
+// origin of the next enumeration: the segment origin, moved along the ray past the last evaluated hit (forward.cu:303-306)
+__device__ __forceinline__ void fwd_request(const FwdState& s, EnumReq& q) {
+    if (s.chunk == 0) { q.ox = s.sox; q.oy = s.soy; q.oz = s.soz; }
+    else { q.ox = xadd(s.sox, xmul(s.offset, s.sdx)); q.oy = xadd(s.soy, xmul(s.offset, s.sdy)); q.oz = xadd(s.soz, xmul(s.offset, s.sdz)); }
+    q.dx = s.sdx; q.dy = s.sdy; q.dz = s.sdz; q.kmax0 = DST_T_MAX; q.pad = 0.f;
+}
+
+// Composites one gathered chunk (forward.cu:197-306) and, when the segment ends, finishes it
+// (forward.cu:309-314, tracePath 378-422). Returns true while the ray needs another enumeration.
+// kb: the chunk's keys with stride KS; cnt: how many.
+template <bool DIAG, int KS>
+__device__ __forceinline__ bool fwd_shade(const FwdParams& p, int ray, FwdState& s, const unsigned long long* kb, int cnt, TraceCounters& tc) {
+    const dst_trace_inputs& in = p.a.in;
     const bool use_sh = in.colors_precomp == nullptr;
     const bool has_aux = in.others_precomp != nullptr;
     const int ncoef = (in.sh_degree + 1) * (in.sh_degree + 1);
     const bool sh_aligned = ((in.sh_coeffs * 3) & 3) == 0 && ((reinterpret_cast<uintptr_t>(in.shs) & 15) == 0);
+    const float min_depth = s.bounce == 0 ? (in.start_from_first ? 0.2f : 0.0f) : 0.06f;       // forward.cu:353
+    const float T_threshold = 0.0001f;
+    float sb[16];
+    if (use_sh) sh_basis(in.sh_degree, s.sdx, s.sdy, s.sdz, sb);
+    if (DIAG) { if (s.chunk == 0) tc.segs++; }
 
-    float out_rgb0 = 0.f, out_rgb1 = 0.f, out_rgb2 = 0.f, out_dpt = 0.f, out_acc = 0.f;
-    float out_nx = 0.f, out_ny = 0.f, out_nz = 0.f, out_aux0 = 0.f, out_aux1 = 0.f;
+    float T_next = 1.0f;
+    bool stop = false;
+    for (int i = 0; i < cnt; i++) {
+        const unsigned long long key = kb[i * KS];
+        const int pidx = (int)(unsigned int)key;
+        const int gidx = pidx >> 1;
+        if (gidx == s.last_gidx) continue;                                // forward.cu:207
+        if (DIAG) tc.evals++;
+        SlotEval e;
+        const bool ok = eval_slot(key, s.offset, s.sox, s.soy, s.soz, s.sdx, s.sdy, s.sdz, min_depth, p.cache, gidx, e);
+        s.dpt = e.dpt;                                                    // :211 (kept even when the slot is skipped)
+        if (!ok) continue;
+        const float alpha = e.alpha, nsign = e.nsign;
+        const float4 r2 = e.r2;
+        T_next = xmul(s.T_prev, xsub(1.0f, alpha));
+        if (T_next < T_threshold) { stop = true; break; }
+        s.contributor++;
+        if (s.contributor > DST_MAX_INTERSECTION) { stop = true; break; }
+        s.last_gidx = gidx;
+        const float w = xmul(alpha, s.T_prev);
+        if (use_sh) {
+            float c[48];
+            load_sh_row(in.shs + 3 * (size_t)gidx * in.sh_coeffs, 3 * ncoef, sh_aligned, c);
+            s.C0 = xadd(s.C0, xmul(w, fmaxf(sh_channel(ncoef, sb, c, 0), 0.f)));
+            s.C1 = xadd(s.C1, xmul(w, fmaxf(sh_channel(ncoef, sb, c, 1), 0.f)));
+            s.C2 = xadd(s.C2, xmul(w, fmaxf(sh_channel(ncoef, sb, c, 2), 0.f)));
+        } else {
+            const float* cp = in.colors_precomp + 3 * (size_t)gidx;
+            s.C0 = xadd(s.C0, xmul(w, __ldg(cp))); s.C1 = xadd(s.C1, xmul(w, __ldg(cp + 1))); s.C2 = xadd(s.C2, xmul(w, __ldg(cp + 2)));
+        }
+        if (has_aux) {
+            const float2 ax = __ldg(reinterpret_cast<const float2*>(in.others_precomp) + gidx);
+            s.O0 = xadd(s.O0, xmul(w, ax.x)); s.O1 = xadd(s.O1, xmul(w, ax.y));
+        }
+        s.D = xadd(s.D, xmul(w, s.dpt));
+        s.Nx = xadd(s.Nx, xmul(w, nsign * r2.x)); s.Ny = xadd(s.Ny, xmul(w, nsign * r2.y)); s.Nz = xadd(s.Nz, xmul(w, nsign * r2.z));
+        s.T_prev = T_next;
+        if (p.a.training && p.a.a_weights) atomicAdd(p.a.a_weights + gidx, w);          // forward.cu:295
+        if (DIAG) {
+            tc.contribs++;
+            if (p.a.hit_log && s.hit_count < p.a.hit_cap) p.a.hit_log[(size_t)ray * p.a.hit_cap + s.hit_count] = pidx;
+            s.hit_count++;
+        }
+    }
+    s.chunk++;
+    bool seg_done = stop || T_next < T_threshold || cnt < DST_CHUNK || s.contributor > DST_MAX_INTERSECTION;   // :299
+    if (!seg_done && s.chunk >= DST_MAX_CHUNKS) { atomicOr(p.status, DST_STATUS_CHUNK_LIMIT); seg_done = true; }
+    if (!seg_done) {
+        s.offset = (float)((double)s.dpt + 0.00001);                                     // :303
+        return true;
+    }
+    // ---- end of the segment (forward.cu:309-314) ----
+    const float bg0 = __ldg(in.background), bg1 = __ldg(in.background + 1), bg2 = __ldg(in.background + 2);
+    const float C0 = xadd(s.C0, xmul(s.T_prev, bg0)), C1 = xadd(s.C1, xmul(s.T_prev, bg1)), C2 = xadd(s.C2, xmul(s.T_prev, bg2));
+    const float A = xsub(1.0f, s.T_prev);
+    // tracePath, forward.cu:378-412
+    if (s.bounce == 0) {
+        p.a.out_dpt[ray] = s.D; p.a.out_acc[ray] = A;
+        p.a.out_norm[3 * (size_t)ray] = s.Nx; p.a.out_norm[3 * (size_t)ray + 1] = s.Ny; p.a.out_norm[3 * (size_t)ray + 2] = s.Nz;
+        p.a.out_aux[2 * (size_t)ray] = s.O0; p.a.out_aux[2 * (size_t)ray + 1] = s.O1;
+        p.a.out_dist[3 * (size_t)ray] = 0.f; p.a.out_dist[3 * (size_t)ray + 1] = 0.f; p.a.out_dist[3 * (size_t)ray + 2] = 0.f;
+    }
+    const float f_this = (s.bounce == in.max_trace_depth) ? 1.0f : xsub(1.0f, s.O0);
+    s.rgb0 = xadd(s.rgb0, xmul(xmul(C0, f_this), s.s_prod));
+    s.rgb1 = xadd(s.rgb1, xmul(xmul(C1, f_this), s.s_prod));
+    s.rgb2 = xadd(s.rgb2, xmul(xmul(C2, f_this), s.s_prod));
+    s.s_prod = xmul(s.s_prod, s.O0);
     float* mid = p.a.mid_val + (size_t)ray * in.mid_stride;
-    int hit_count = 0;
+    float4* m4 = reinterpret_cast<float4*>(mid + s.bounce * DST_MID_CHANNELS);
+    m4[0] = make_float4(s.sox, s.soy, s.soz, s.sdx);
+    m4[1] = make_float4(s.sdy, s.sdz, s.D, A);
+    m4[2] = make_float4(s.Nx, s.Ny, s.Nz, s.O0);
+    m4[3] = make_float4(s.O1, C0, C1, C2);
+    const float nlen = xsqrt(rdot3(s.Nx, s.Ny, s.Nz, s.Nx, s.Ny, s.Nz));
+    if (nlen == 0.0f || s.O0 <= in.specular_threshold || s.bounce == in.max_trace_depth) {        // :416
+        // the ray is finished; bounces that were never traced read as zeros (the reference leaves them uninitialised, forward.cu:446)
+        for (int k = (s.bounce + 1) * DST_MID_CHANNELS; k < in.mid_stride; k += 4)
+            *reinterpret_cast<float4*>(mid + k) = make_float4(0.f, 0.f, 0.f, 0.f);
+        p.a.out_rgb[3 * (size_t)ray] = s.rgb0; p.a.out_rgb[3 * (size_t)ray + 1] = s.rgb1; p.a.out_rgb[3 * (size_t)ray + 2] = s.rgb2;
+        if (DIAG && p.a.hit_cnt) p.a.hit_cnt[ray] = s.hit_count;
+        return false;
+    }
+    // reflect about the accumulated normal, restart 0.06 along the new direction (:420-422);
+    // exactly rounded, because the bounce ray decides which quads the next segment sees
+    const float nx = xdiv(s.Nx, nlen), ny = xdiv(s.Ny, nlen), nz = xdiv(s.Nz, nlen);
+    const float k = xmul(2.0f, rdot3(nx, ny, nz, s.sdx, s.sdy, s.sdz));
+    const float Ex = xadd(s.sox, xmul(s.D, s.sdx)), Ey = xadd(s.soy, xmul(s.D, s.sdy)), Ez = xadd(s.soz, xmul(s.D, s.sdz));
+    s.sdx = xsub(s.sdx, xmul(k, nx)); s.sdy = xsub(s.sdy, xmul(k, ny)); s.sdz = xsub(s.sdz, xmul(k, nz));
+    s.sox = xadd(Ex, xmul(0.06f, s.sdx)); s.soy = xadd(Ey, xmul(0.06f, s.sdy)); s.soz = xadd(Ez, xmul(0.06f, s.sdz));
+    s.bounce++;
+    fwd_begin_segment(s);
+    return true;
+}
 
-    float sox = rox, soy = roy, soz = roz, sdx = rdx, sdy = rdy, sdz = rdz;    // segment origin / direction
-    float s_prod = 1.0f;
-    int bounce = 0;
-    for (; bounce <= in.max_trace_depth; bounce++) {
-        // forward.cu:353
-        const float min_depth = bounce == 0 ? (in.start_from_first ? 0.2f : 0.0f) : 0.06f;
-        const float T_threshold = 0.0001f;
-        float C0 = 0.f, C1 = 0.f, C2 = 0.f, D = 0.f, Nx = 0.f, Ny = 0.f, Nz = 0.f, O0 = 0.f, O1 = 0.f;
-        float T_prev = 1.0f, T_next = 1.0f, dpt = 0.0f, offset = 0.0f;
-        int last_gidx = -1, contributor = 0;
-        float tox = sox, toy = soy, toz = soz;                                 // moved origin of the current enumeration
-        float sb[16];
-        if (use_sh) sh_basis(in.sh_degree, sdx, sdy, sdz, sb);
-        if (DIAG) tc.segs++;
+__device__ __forceinline__ void load_state(const void* base, int ray, FwdState& s) {
+    const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const FwdState*>(base) + ray);
+    float4* dst = reinterpret_cast<float4*>(&s);
+#pragma unroll
+    for (int i = 0; i < 7; i++) dst[i] = src[i];
+}
+__device__ __forceinline__ void store_state(void* base, int ray, const FwdState& s) {
+    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<FwdState*>(base) + ray);
+    const float4* src = reinterpret_cast<const float4*>(&s);
+#pragma unroll
+    for (int i = 0; i < 7; i++) dst[i] = src[i];
+}
 
-        for (int chunk = 0;; chunk++) {
-            if (chunk >= DST_MAX_CHUNKS) { atomicOr(p.status, DST_STATUS_CHUNK_LIMIT); break; }
-            const int cnt = knearest<BRUTE, DIAG, FWD_THREADS>(p.bvh, tox, toy, toz, sdx, sdy, sdz, kb, p.status, tc);
-            if (DIAG) tc.enums++;
-            bool stop = false;
-            for (int i = 0; i < cnt; i++) {
-                const unsigned long long key = kb[i * FWD_THREADS];
-                const int pidx = (int)(unsigned int)key;
-                const int gidx = pidx >> 1;
-                if (gidx == last_gidx) continue;                                // forward.cu:207
-                if (DIAG) tc.evals++;
-                SlotEval e;
-                const bool ok = eval_slot(key, offset, sox, soy, soz, sdx, sdy, sdz, min_depth, p.cache, gidx, e);
-                dpt = e.dpt;                                                    // :211 (kept even when the slot is skipped)
-                if (!ok) continue;
-                const float alpha = e.alpha, nsign = e.nsign;
-                const float4 r2 = e.r2;
-                T_next = xmul(T_prev, xsub(1.0f, alpha));
-                if (T_next < T_threshold) { stop = true; break; }
-                contributor++;
-                if (contributor > DST_MAX_INTERSECTION) { stop = true; break; }
-                last_gidx = gidx;
-                const float w = xmul(alpha, T_prev);
-                if (use_sh) {
-                    float c[48];
-                    load_sh_row(in.shs + 3 * (size_t)gidx * in.sh_coeffs, 3 * ncoef, sh_aligned, c);
-                    C0 = xadd(C0, xmul(w, fmaxf(sh_channel(ncoef, sb, c, 0), 0.f)));
-                    C1 = xadd(C1, xmul(w, fmaxf(sh_channel(ncoef, sb, c, 1), 0.f)));
-                    C2 = xadd(C2, xmul(w, fmaxf(sh_channel(ncoef, sb, c, 2), 0.f)));
-                } else {
-                    const float* cp = in.colors_precomp + 3 * (size_t)gidx;
-                    C0 = xadd(C0, xmul(w, __ldg(cp))); C1 = xadd(C1, xmul(w, __ldg(cp + 1))); C2 = xadd(C2, xmul(w, __ldg(cp + 2)));
-                }
-                if (has_aux) {
-                    const float2 ax = __ldg(reinterpret_cast<const float2*>(in.others_precomp) + gidx);
-                    O0 = xadd(O0, xmul(w, ax.x)); O1 = xadd(O1, xmul(w, ax.y));
-                }
-                D = xadd(D, xmul(w, dpt));
-                Nx = xadd(Nx, xmul(w, nsign * r2.x)); Ny = xadd(Ny, xmul(w, nsign * r2.y)); Nz = xadd(Nz, xmul(w, nsign * r2.z));
-                T_prev = T_next;
-                if (p.a.training && p.a.a_weights) atomicAdd(p.a.a_weights + gidx, w);          // forward.cu:295
-                if (DIAG) {
-                    tc.contribs++;
-                    if (p.a.hit_log && hit_count < p.a.hit_cap) p.a.hit_log[(size_t)ray * p.a.hit_cap + hit_count] = pidx;
-                    hit_count++;
-                }
+__device__ __forceinline__ void flush_counters(unsigned long long* counters, const TraceCounters& tc) {
+    if (!counters) return;
+    if (tc.segs) atomicAdd(counters + 0, tc.segs);
+    if (tc.enums) atomicAdd(counters + 1, tc.enums);
+    if (tc.nodes) atomicAdd(counters + 2, tc.nodes);
+    if (tc.quads) atomicAdd(counters + 3, tc.quads);
+    if (tc.evals) atomicAdd(counters + 4, tc.evals);
+    if (tc.contribs) atomicAdd(counters + 5, tc.contribs);
+}
+
+// round 0: list of all rays in tile order, initial state and first enumeration request
+__global__ void __launch_bounds__(256) k_fwd_init(const __grid_constant__ FwdParams p, long long slots) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= slots) return;
+    if (i == 0) p.counts[0] = (int)slots;
+    const int ray = ray_of_slot(i, p.a.in.H, p.a.in.W, p.tiled != 0);
+    p.list[0][i] = ray;
+    if (ray < 0) return;
+    FwdState s;
+    fwd_init_state(p, ray, s);
+    store_state(p.state, ray, s);
+    EnumReq q;
+    fwd_request(s, q);
+    p.req[ray] = q;
+}
+
+template <bool DIAG>
+__global__ void __launch_bounds__(SHADE_THREADS) k_fwd_shade(const __grid_constant__ FwdParams p, int round) {
+    const int n = p.counts[round];
+    if (n < p.min_count) return;
+    const int* list = p.list[round & 1];
+    int* next_list = p.list[(round + 1) & 1];
+    TraceCounters tc = { 0, 0, 0, 0, 0, 0 };
+    const int n_pad = (n + 31) & ~31;
+    for (int i = blockIdx.x * SHADE_THREADS + threadIdx.x; i < n_pad; i += gridDim.x * SHADE_THREADS) {
+        const int ray = i < n ? list[i] : -1;
+        bool alive = false;
+        if (ray >= 0) {
+            FwdState s;
+            load_state(p.state, ray, s);
+            alive = fwd_shade<DIAG, 1>(p, ray, s, p.kbuf + (size_t)ray * DST_CHUNK, p.kcnt[ray], tc);
+            if (alive) {
+                store_state(p.state, ray, s);
+                EnumReq q;
+                fwd_request(s, q);
+                p.req[ray] = q;
             }
-            if (stop || T_next < T_threshold || cnt < DST_CHUNK || contributor > DST_MAX_INTERSECTION) break;   // :299
-            offset = (float)((double)dpt + 0.00001);                                               // :303
-            tox = xadd(sox, xmul(offset, sdx)); toy = xadd(soy, xmul(offset, sdy)); toz = xadd(soz, xmul(offset, sdz));
         }
-        // forward.cu:309-314
-        C0 = xadd(C0, xmul(T_prev, bg0)); C1 = xadd(C1, xmul(T_prev, bg1)); C2 = xadd(C2, xmul(T_prev, bg2));
-        const float A = xsub(1.0f, T_prev);
-        // tracePath, forward.cu:378-412
-        if (bounce == 0) { out_dpt = D; out_acc = A; out_nx = Nx; out_ny = Ny; out_nz = Nz; out_aux0 = O0; out_aux1 = O1; }
-        const float f_this = (bounce == in.max_trace_depth) ? 1.0f : xsub(1.0f, O0);
-        out_rgb0 = xadd(out_rgb0, xmul(xmul(C0, f_this), s_prod));
-        out_rgb1 = xadd(out_rgb1, xmul(xmul(C1, f_this), s_prod));
-        out_rgb2 = xadd(out_rgb2, xmul(xmul(C2, f_this), s_prod));
-        s_prod = xmul(s_prod, O0);
-        float4* m4 = reinterpret_cast<float4*>(mid + bounce * DST_MID_CHANNELS);
-        m4[0] = make_float4(sox, soy, soz, sdx);
-        m4[1] = make_float4(sdy, sdz, D, A);
-        m4[2] = make_float4(Nx, Ny, Nz, O0);
-        m4[3] = make_float4(O1, C0, C1, C2);
-        const float nlen = xsqrt(rdot3(Nx, Ny, Nz, Nx, Ny, Nz));
-        if (nlen == 0.0f || O0 <= in.specular_threshold) { bounce++; break; }                      // :416
-        if (bounce == in.max_trace_depth) { bounce++; break; }
-        // reflect about the accumulated normal, restart 0.06 along the new direction (:420-422);
-        // exactly rounded, because the bounce ray decides which quads the next segment sees
-        const float nx = xdiv(Nx, nlen), ny = xdiv(Ny, nlen), nz = xdiv(Nz, nlen);
-        const float k = xmul(2.0f, rdot3(nx, ny, nz, sdx, sdy, sdz));
-        const float Ex = xadd(sox, xmul(D, sdx)), Ey = xadd(soy, xmul(D, sdy)), Ez = xadd(soz, xmul(D, sdz));
-        sdx = xsub(sdx, xmul(k, nx)); sdy = xsub(sdy, xmul(k, ny)); sdz = xsub(sdz, xmul(k, nz));
-        sox = xadd(Ex, xmul(0.06f, sdx)); soy = xadd(Ey, xmul(0.06f, sdy)); soz = xadd(Ez, xmul(0.06f, sdz));
+        append_alive(alive, ray, next_list, p.counts + round + 1);
     }
-    // bounces that were never traced read as zeros (the reference leaves them uninitialised, forward.cu:446)
-    for (int k = bounce * DST_MID_CHANNELS; k < in.mid_stride; k += 4)
-        *reinterpret_cast<float4*>(mid + k) = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (DIAG) flush_counters(p.a.counters, tc);
+}
 
-    p.a.out_rgb[3 * ray] = out_rgb0; p.a.out_rgb[3 * ray + 1] = out_rgb1; p.a.out_rgb[3 * ray + 2] = out_rgb2;
-    p.a.out_dpt[ray] = out_dpt; p.a.out_acc[ray] = out_acc;
-    p.a.out_norm[3 * ray] = out_nx; p.a.out_norm[3 * ray + 1] = out_ny; p.a.out_norm[3 * ray + 2] = out_nz;
-    p.a.out_dist[3 * ray] = 0.f; p.a.out_dist[3 * ray + 1] = 0.f; p.a.out_dist[3 * ray + 2] = 0.f;
-    p.a.out_aux[2 * ray] = out_aux0; p.a.out_aux[2 * ray + 1] = out_aux1;
-    if (DIAG) {
-        if (p.a.hit_cnt) p.a.hit_cnt[ray] = hit_count;
-        if (p.a.counters) {
-            atomicAdd(p.a.counters + 0, tc.segs); atomicAdd(p.a.counters + 1, tc.enums); atomicAdd(p.a.counters + 2, tc.nodes);
-            atomicAdd(p.a.counters + 3, tc.quads); atomicAdd(p.a.counters + 4, tc.evals); atomicAdd(p.a.counters + 5, tc.contribs);
+// runs every ray of the first list the wavefront left alone to completion, one thread per ray
+template <bool BRUTE, bool DIAG>
+__global__ void __launch_bounds__(TAIL_THREADS) k_fwd_tail(const __grid_constant__ FwdParams p) {
+    __shared__ unsigned long long kshared[DST_CHUNK * TAIL_THREADS];
+    const int round = first_skipped_round(p.counts, p.rounds, p.min_count);
+    const int n = p.counts[round];
+    const int* list = p.list[round & 1];
+    unsigned long long* kb = kshared + threadIdx.x;
+    TraceCounters tc = { 0, 0, 0, 0, 0, 0 };
+    for (int i = blockIdx.x * TAIL_THREADS + threadIdx.x; i < n; i += gridDim.x * TAIL_THREADS) {
+        const int ray = list[i];
+        if (ray < 0) continue;
+        FwdState s;
+        load_state(p.state, ray, s);
+        bool alive = true;
+        while (alive) {
+            EnumReq q;
+            fwd_request(s, q);
+            const int cnt = knearest<BRUTE, DIAG, TAIL_THREADS>(p.bvh, q.ox, q.oy, q.oz, q.dx, q.dy, q.dz, kb, p.status, tc, q.kmax0);
+            if (DIAG) tc.enums++;
+            alive = fwd_shade<DIAG, TAIL_THREADS>(p, ray, s, kb, cnt, tc);
         }
     }
+    if (DIAG) flush_counters(p.a.counters, tc);
 }
 
 // one enumeration per ray, for tests of the hierarchy walk against exhaustive testing
 template <bool BRUTE>
-__global__ void __launch_bounds__(FWD_THREADS) k_knearest(BvhView bvh, const float* __restrict__ ro, const float* __restrict__ rd,
-                                                          long long n, unsigned long long* keys, int* counts, unsigned int* status,
-                                                          const float* __restrict__ t_cut, unsigned long long* counters) {
-    __shared__ unsigned long long kbuf[DST_CHUNK * FWD_THREADS];
+__global__ void __launch_bounds__(TAIL_THREADS) k_knearest(BvhView bvh, const float* __restrict__ ro, const float* __restrict__ rd,
+                                                           long long n, unsigned long long* keys, int* counts, unsigned int* status,
+                                                           const float* __restrict__ t_cut, unsigned long long* counters) {
+    __shared__ unsigned long long kbuf[DST_CHUNK * TAIL_THREADS];
     const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= n) return;
     unsigned long long* kb = kbuf + threadIdx.x;
     TraceCounters tc = { 0, 0, 0, 0, 0, 0 };
-    const int c = knearest<BRUTE, true, FWD_THREADS>(bvh, ro[3 * r], ro[3 * r + 1], ro[3 * r + 2], rd[3 * r], rd[3 * r + 1], rd[3 * r + 2],
-                                                    kb, status, tc, t_cut ? t_cut[r] : DST_T_MAX);
+    const int c = knearest<BRUTE, true, TAIL_THREADS>(bvh, ro[3 * r], ro[3 * r + 1], ro[3 * r + 2], rd[3 * r], rd[3 * r + 1], rd[3 * r + 2],
+                                                     kb, status, tc, t_cut ? t_cut[r] : DST_T_MAX);
     if (counters) { atomicAdd(counters + 2, tc.nodes); atomicAdd(counters + 3, tc.quads); }
     counts[r] = c;
-    for (int i = 0; i < DST_CHUNK; i++) keys[r * DST_CHUNK + i] = i < c ? kb[i * FWD_THREADS] : 0ull;
+    for (int i = 0; i < DST_CHUNK; i++) keys[r * DST_CHUNK + i] = i < c ? kb[i * TAIL_THREADS] : 0ull;
 }
 
 }  // namespace
@@ -203,7 +318,7 @@ __global__ void __launch_bounds__(FWD_THREADS) k_knearest(BvhView bvh, const flo
 BvhView dst_bvh_view(const dst_handle* h) {
     BvhView b;
     b.nodes = reinterpret_cast<const float4*>(h->nodes);
-    b.quads = h->quads; b.leaf_gid = h->leaf_gid; b.header = h->header; b.P = (int)h->P;
+    b.quads = h->quads; b.leaf_gid = h->leaf_gid; b.header = h->header; b.P = (int)h->P; b.nrefs = (int)h->nrefs;
     return b;
 }
 
@@ -211,7 +326,7 @@ int dst_check_inputs(dst_handle* h, const dst_trace_inputs* in) {
     if (!h->built) return dst_set_error(h, DST_E_STATE, "trace requested before build_acceleration_structure");
     if (in->P != h->P) return dst_set_error(h, DST_E_ARG, "means3D has %d surfels but the hierarchy was built over %lld", in->P, (long long)h->P);
     if (in->H <= 0 || in->W <= 0) return dst_set_error(h, DST_E_ARG, "ray grid must be non-empty, got %d x %d", in->H, in->W);
-    if ((long long)in->H * in->W > 0x7fffffffll) return dst_set_error(h, DST_E_ARG, "too many rays");
+    if ((long long)in->H * in->W > 0x3fffffffll) return dst_set_error(h, DST_E_ARG, "too many rays");
     if (!in->ray_o || !in->ray_d || !in->means3D || !in->opacities || !in->scales || !in->rotations || !in->background || !in->vertices)
         return dst_set_error(h, DST_E_ARG, "a required input pointer is null");
     if ((in->shs == nullptr) == (in->colors_precomp == nullptr))
@@ -236,24 +351,72 @@ int dst_prepare_cache(dst_handle* h, const dst_trace_inputs* in, cudaStream_t st
     return DST_OK;
 }
 
+// scratch for `slots` list entries / rays of `state_bytes` each (grow-only)
+int dst_ensure_wavefront(dst_handle* h, long long slots, size_t state_bytes) {
+    if (slots <= h->wf_cap && state_bytes <= h->wf_state_bytes) return DST_OK;
+    cudaFree(h->wf_state); cudaFree(h->wf_req); cudaFree(h->wf_kbuf); cudaFree(h->wf_kcnt); cudaFree(h->wf_list[0]); cudaFree(h->wf_list[1]);
+    cudaFree(h->wf_counts);
+    h->wf_state = nullptr; h->wf_req = nullptr; h->wf_kbuf = nullptr; h->wf_kcnt = nullptr; h->wf_list[0] = h->wf_list[1] = nullptr; h->wf_counts = nullptr;
+    h->wf_cap = 0; h->wf_state_bytes = 0;
+    const long long cap = slots > h->wf_cap ? slots + slots / 16 + 1024 : h->wf_cap;
+    const size_t sb = state_bytes > h->wf_state_bytes ? state_bytes : h->wf_state_bytes;
+    cudaError_t e = cudaMalloc(&h->wf_state, sb * (size_t)cap);
+    if (e == cudaSuccess) e = cudaMalloc(&h->wf_req, 32 * (size_t)cap);
+    if (e == cudaSuccess) e = cudaMalloc(&h->wf_kbuf, 8 * DST_CHUNK * (size_t)cap);
+    if (e == cudaSuccess) e = cudaMalloc(&h->wf_kcnt, 4 * (size_t)cap);
+    if (e == cudaSuccess) e = cudaMalloc(&h->wf_list[0], 4 * (size_t)cap);
+    if (e == cudaSuccess) e = cudaMalloc(&h->wf_list[1], 4 * (size_t)cap);
+    if (e == cudaSuccess) e = cudaMalloc(&h->wf_counts, 4 * (DST_WF_ROUNDS + 2));
+    if (e != cudaSuccess) { cudaGetLastError(); return dst_set_error(h, DST_E_NOMEM, "ray scratch allocation for %lld rays failed: %s", slots, cudaGetErrorString(e)); }
+    h->wf_cap = cap; h->wf_state_bytes = sb;
+    return DST_OK;
+}
+
+int dst_wavefront_grid(const dst_handle* h, long long slots, int threads, int per_sm) {
+    const long long want = (slots + threads - 1) / threads;
+    const long long cap = (long long)h->sm_count * per_sm;
+    return (int)(want < cap ? (want > 0 ? want : 1) : cap);
+}
+
 int dst_forward_impl(dst_handle* h, const dst_fwd_args* a, cudaStream_t st) {
     int rc = dst_check_inputs(h, &a->in);
     if (rc != DST_OK) return rc;
     if (!a->out_rgb || !a->out_dpt || !a->out_acc || !a->out_norm || !a->out_dist || !a->out_aux || !a->mid_val)
         return dst_set_error(h, DST_E_ARG, "a forward output pointer is null");
     if ((reinterpret_cast<uintptr_t>(a->mid_val) & 15) != 0) return dst_set_error(h, DST_E_ARG, "mid_val must be 16-byte aligned");
-    rc = dst_prepare_cache(h, &a->in, st);
-    if (rc != DST_OK) return rc;
-    if (a->training && a->a_weights) DST_CUDA_TRY(h, cudaMemsetAsync(a->a_weights, 0, 4 * (size_t)a->in.P, st));
     FwdParams p;
     p.a = *a; p.bvh = dst_bvh_view(h); p.cache = h->cache; p.status = h->status;
     p.tiled = a->in.H >= 16;
-    const long long R = (long long)a->in.H * a->in.W;
-    long long blocks = p.tiled ? (long long)((a->in.W + 15) / 16) * ((a->in.H + 7) / 8) : (R + FWD_THREADS - 1) / FWD_THREADS;
+    const long long slots = slots_of_grid(a->in.H, a->in.W, p.tiled != 0);
+    rc = dst_ensure_wavefront(h, slots, sizeof(FwdState));
+    if (rc != DST_OK) return rc;
+    rc = dst_prepare_cache(h, &a->in, st);
+    if (rc != DST_OK) return rc;
+    p.cache = h->cache;
+    if (a->training && a->a_weights) DST_CUDA_TRY(h, cudaMemsetAsync(a->a_weights, 0, 4 * (size_t)a->in.P, st));
+    p.state = h->wf_state; p.req = static_cast<EnumReq*>(h->wf_req); p.kbuf = h->wf_kbuf; p.kcnt = h->wf_kcnt;
+    p.list[0] = h->wf_list[0]; p.list[1] = h->wf_list[1]; p.counts = h->wf_counts;
+    // small launches go straight to the per-ray kernel; large ones run wavefront rounds until few rays are left
+    const bool wave = slots >= h->wf_min_rays;
+    p.rounds = wave ? DST_WF_ROUNDS : 0;
+    p.min_count = wave ? (int)(slots / 64 > 4096 ? slots / 64 : 4096) : 1;
     const bool diag = a->hit_log || a->hit_cnt || a->counters;
+    DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * (DST_WF_ROUNDS + 2), st));
     dst_prof_mark(h, 1, 0, st);
-    if (diag) k_forward<false, true><<<(unsigned int)blocks, FWD_THREADS, 0, st>>>(p);
-    else k_forward<false, false><<<(unsigned int)blocks, FWD_THREADS, 0, st>>>(p);
+    k_fwd_init<<<(unsigned int)((slots + 255) / 256), 256, 0, st>>>(p, slots);
+    const int g_enum = dst_wavefront_grid(h, slots, ENUM_THREADS, 12), g_shade = dst_wavefront_grid(h, slots, SHADE_THREADS, 8);
+    for (int r = 0; r < p.rounds; r++) {
+        if (diag) {
+            k_enum<true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters);
+            k_fwd_shade<true><<<g_shade, SHADE_THREADS, 0, st>>>(p, r);
+        } else {
+            k_enum<false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr);
+            k_fwd_shade<false><<<g_shade, SHADE_THREADS, 0, st>>>(p, r);
+        }
+    }
+    const int g_tail = dst_wavefront_grid(h, wave ? p.min_count : slots, TAIL_THREADS, 8);
+    if (diag) k_fwd_tail<false, true><<<g_tail, TAIL_THREADS, 0, st>>>(p);
+    else k_fwd_tail<false, false><<<g_tail, TAIL_THREADS, 0, st>>>(p);
     dst_prof_mark(h, 1, 1, st);
     DST_CUDA_TRY(h, cudaGetLastError());
     return DST_OK;
@@ -263,9 +426,9 @@ int dst_knearest_impl(dst_handle* h, const float* ro, const float* rd, int64_t n
                       int brute, const float* t_cut, unsigned long long* counters, cudaStream_t st) {
     if (!h->built) return dst_set_error(h, DST_E_STATE, "no hierarchy has been built");
     if (n <= 0) return DST_OK;
-    const unsigned int blocks = (unsigned int)((n + FWD_THREADS - 1) / FWD_THREADS);
-    if (brute) k_knearest<true><<<blocks, FWD_THREADS, 0, st>>>(dst_bvh_view(h), ro, rd, n, keys, counts, h->status, t_cut, counters);
-    else k_knearest<false><<<blocks, FWD_THREADS, 0, st>>>(dst_bvh_view(h), ro, rd, n, keys, counts, h->status, t_cut, counters);
+    const unsigned int blocks = (unsigned int)((n + TAIL_THREADS - 1) / TAIL_THREADS);
+    if (brute) k_knearest<true><<<blocks, TAIL_THREADS, 0, st>>>(dst_bvh_view(h), ro, rd, n, keys, counts, h->status, t_cut, counters);
+    else k_knearest<false><<<blocks, TAIL_THREADS, 0, st>>>(dst_bvh_view(h), ro, rd, n, keys, counts, h->status, t_cut, counters);
     DST_CUDA_TRY(h, cudaGetLastError());
     return DST_OK;
 }

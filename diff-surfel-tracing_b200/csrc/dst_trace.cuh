@@ -7,6 +7,7 @@
 #define DST_STACK 96                 // >= depth bound of a Karras tree over 63-bit keys + 32-bit index tie-breaks
 #define DST_MAX_CHUNKS 4096          // bound on enumerations per ray segment (the reference loops without one)
 #define DST_MAX_INTERSECTION 256     // optix_tracer/config.h:23
+#define DST_REF_SHIFT 4                // leaf reference = surfel id << 4 | sub-rectangle (iu << 2 | iv)
 #define DST_PAD_FACTOR 4e-6f         // box padding per unit of coordinate magnitude, see knearest()
 
 struct TraceCounters { unsigned long long segs, enums, nodes, quads, evals, contribs; };
@@ -42,22 +43,21 @@ __device__ __forceinline__ int knearest(const BvhView& bvh, float ox, float oy, 
         if (COUNT) tc.quads++;
         float t; int tri;
         if (!ray_quad(qa, qb, qc, ox, oy, oz, dx, dy, dz, kmax, t, tri)) return;
-        const unsigned int gid = (unsigned int)__ldg(bvh.leaf_gid + pos);
+        const unsigned int gid = (unsigned int)__ldg(bvh.leaf_gid + pos) >> DST_REF_SHIFT;
         const unsigned long long key = make_key(t, 2u * gid + (unsigned int)tri);
-        if (n == DST_CHUNK) { if (key >= kb[(DST_CHUNK - 1) * KS]) return; n = DST_CHUNK - 1; }
+        if (n == DST_CHUNK && key >= kb[(DST_CHUNK - 1) * KS]) return;
         int j = n;
-        while (j > 0) {
-            const unsigned long long prev = kb[(j - 1) * KS];
-            if (prev <= key) break;
-            kb[j * KS] = prev; j--;
-        }
+        while (j > 0 && kb[(j - 1) * KS] > key) j--;
+        if (j > 0 && kb[(j - 1) * KS] == key) return;       // the same hit reached through another leaf of a split quad
+        if (n == DST_CHUNK) n = DST_CHUNK - 1;
+        for (int i = n; i > j; i--) kb[i * KS] = kb[(i - 1) * KS];
         kb[j * KS] = key;
         n++;
         if (n == DST_CHUNK) kmax = hitkey_t(kb[(DST_CHUNK - 1) * KS]);
     };
 
     if (BRUTE) {
-        for (int pos = 0; pos < bvh.P; pos++) offer(pos);
+        for (int pos = 0; pos < bvh.nrefs; pos++) offer(pos);
         return n;
     }
 
@@ -76,9 +76,19 @@ __device__ __forceinline__ int knearest(const BvhView& bvh, float ox, float oy, 
 
     unsigned long long stack[DST_STACK];
     int sp = 0;
+    constexpr int DONE = 0x7fffffff;
+    // pops the next subtree that can still hold a hit nearer than the 16th
+    auto pop = [&]() -> int {
+        while (sp > 0) {
+            const unsigned long long e = stack[--sp];
+            if (__uint_as_float((unsigned int)(e >> 32)) <= kmax) return (int)(unsigned int)e;
+        }
+        return DONE;
+    };
     int cur = 0;
-    while (true) {
-        if (cur >= 0) {
+    for (;;) {
+        // "while-while": lanes walk internal nodes until each holds a leaf (or is done), then test leaves together
+        while ((unsigned int)cur < (unsigned int)DONE) {
             const float4* np = bvh.nodes + 4 * (size_t)cur;
             const float4 a = __ldg(np), b = __ldg(np + 1), c = __ldg(np + 2);
             const int4 lk = __ldg(reinterpret_cast<const int4*>(np + 3));
@@ -98,25 +108,18 @@ __device__ __forceinline__ int knearest(const BvhView& bvh, float ox, float oy, 
             const bool h1 = (tn1 <= tf1) && (tn1 <= kmax);
             if (h0 && h1) {
                 const bool swap = tn1 < tn0;
-                const int cn = swap ? lk.y : lk.x, cf = swap ? lk.x : lk.y;
+                const int cf = swap ? lk.x : lk.y;
                 const float tfar = swap ? tn0 : tn1;
                 if (sp < DST_STACK) stack[sp++] = ((unsigned long long)__float_as_uint(tfar) << 32) | (unsigned int)cf;
                 else atomicOr(status, DST_STATUS_STACK_OVERFLOW);
-                cur = cn;
-                continue;
-            }
-            if (h0) { cur = lk.x; continue; }
-            if (h1) { cur = lk.y; continue; }
-        } else {
-            offer(~cur);
+                cur = swap ? lk.y : lk.x;
+            } else if (h0) cur = lk.x;
+            else if (h1) cur = lk.y;
+            else cur = pop();
         }
-        // pop the next subtree that can still hold a hit nearer than the 16th
-        bool found = false;
-        while (sp > 0) {
-            const unsigned long long e = stack[--sp];
-            if (__uint_as_float((unsigned int)(e >> 32)) <= kmax) { cur = (int)(unsigned int)e; found = true; break; }
-        }
-        if (!found) break;
+        if (cur == DONE) break;
+        offer(~cur);
+        cur = pop();
     }
     return n;
 }
@@ -259,4 +262,80 @@ __device__ __forceinline__ bool eval_slot(unsigned long long key, float offset, 
     e.alpha = fminf(0.99f, xmul(e.r2.w, e.G));
     if (e.alpha < 1.0f / 255.0f) return false;
     return true;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Wavefront plumbing. A trace call runs as rounds of two kernels over the list of rays that are
+// still alive: k_enum gathers the 16 nearest hits of each ray's current enumeration (small
+// register footprint, every lane busy), a shade kernel composites them and decides what the ray
+// does next. Ray state, hit buffers and the lists live in scratch memory owned by the handle.
+// counts[r] is the length of list[r & 1] in round r; a round whose list is shorter than
+// `min_count` is skipped by both kernels and left to the tail kernel, which runs the remaining
+// rays to completion one thread per ray.
+// ---------------------------------------------------------------------------------------------
+struct __align__(16) EnumReq { float ox, oy, oz, dx, dy, dz, kmax0, pad; };
+
+constexpr int ENUM_THREADS = 128;
+#define DST_WF_ROUNDS 48
+
+template <bool COUNT>
+__global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumReq* __restrict__ req, const int* __restrict__ list,
+                                                       const int* __restrict__ count_ptr, int min_count,
+                                                       unsigned long long* __restrict__ kbuf, int* __restrict__ kcnt,
+                                                       unsigned int* status, unsigned long long* counters) {
+    __shared__ unsigned long long kshared[DST_CHUNK * ENUM_THREADS];
+    const int n = *count_ptr;
+    if (n < min_count) return;
+    unsigned long long* kb = kshared + threadIdx.x;
+    TraceCounters tc = { 0, 0, 0, 0, 0, 0 };
+    for (int i = blockIdx.x * ENUM_THREADS + threadIdx.x; i < n; i += gridDim.x * ENUM_THREADS) {
+        const int ray = list[i];
+        if (ray < 0) continue;
+        const float4 r0 = __ldg(reinterpret_cast<const float4*>(req + ray)), r1 = __ldg(reinterpret_cast<const float4*>(req + ray) + 1);
+        const int c = knearest<false, COUNT, ENUM_THREADS>(bvh, r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, kb, status, tc, r1.z);
+        if (COUNT) tc.enums++;
+        kcnt[ray] = c;
+        ulonglong2* out = reinterpret_cast<ulonglong2*>(kbuf + (size_t)ray * DST_CHUNK);
+#pragma unroll
+        for (int k = 0; k < DST_CHUNK / 2; k++) {
+            if (2 * k < c) out[k] = make_ulonglong2(kb[(2 * k) * ENUM_THREADS], kb[(2 * k + 1) * ENUM_THREADS]);
+        }
+    }
+    if (COUNT && counters) { atomicAdd(counters + 1, tc.enums); atomicAdd(counters + 2, tc.nodes); atomicAdd(counters + 3, tc.quads); }
+}
+
+// list entry i of round 0 -> ray index (or -1): image-like grids are walked in 8x4 pixel tiles so
+// that the rays of a warp stay close in the hierarchy, batched ray lists linearly
+__device__ __forceinline__ int ray_of_slot(long long i, int H, int W, bool tiled) {
+    if (!tiled) return i < (long long)H * W ? (int)i : -1;
+    const int tiles_x = (W + 7) >> 3;
+    const long long tile = i >> 5;
+    const int lane = (int)(i & 31);
+    const int x = (int)(tile % tiles_x) * 8 + (lane & 7);
+    const int y = (int)(tile / tiles_x) * 4 + (lane >> 3);
+    if (x >= W || y >= H) return -1;
+    return y * W + x;
+}
+__host__ __device__ __forceinline__ long long slots_of_grid(int H, int W, bool tiled) {
+    if (!tiled) return (long long)H * W;
+    return (long long)((W + 7) >> 3) * ((H + 3) >> 2) * 32;
+}
+
+// appends `ray` to the next round's list when `alive`; one atomic per warp, order kept within a warp
+__device__ __forceinline__ void append_alive(bool alive, int ray, int* __restrict__ next_list, int* next_count) {
+    __syncwarp();
+    const unsigned int m = __ballot_sync(__activemask(), alive);
+    if (!alive) return;
+    const int lane = threadIdx.x & 31;
+    const int leader = __ffs(m) - 1;
+    int base = 0;
+    if (lane == leader) base = atomicAdd(next_count, __popc(m));
+    base = __shfl_sync(m, base, leader);
+    next_list[base + __popc(m & ((1u << lane) - 1u))] = ray;
+}
+
+// first round the wavefront kernels left alone (list shorter than min_count)
+__device__ __forceinline__ int first_skipped_round(const int* __restrict__ counts, int rounds, int min_count) {
+    for (int r = 0; r < rounds; r++) if (counts[r] < min_count) return r;
+    return rounds;
 }

@@ -62,6 +62,7 @@ def lib():
         l.dst_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), C.c_void_p]
         l.dst_bvh_info.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
         l.dst_debug_knearest.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+        l.dst_set_option.argtypes = [C.c_void_p, C.c_int, C.c_int64]
         l.dst_profile_enable.argtypes = [C.c_void_p, C.c_int]
         l.dst_profile_read.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_int32)]
         l.dst_debug_quad_frames.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
@@ -127,6 +128,11 @@ class OptiXStateWrapper:
         f = C.c_uint32(0)
         _check(self, lib().dst_status(self.handle, C.byref(f), _stream()))
         return f.value
+
+    def set_wavefront_min_rays(self, n):
+        """Trace calls with at least `n` rays run as rounds of gather / composite kernels over the
+        live rays; smaller calls use one thread per ray for the whole path (same results)."""
+        _check(self, lib().dst_set_option(self.handle, 1, int(n)))
 
     def profile(self, on=True):
         """Records CUDA events around the build, forward and backward kernels of later calls."""

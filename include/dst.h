@@ -126,6 +126,12 @@ int dst_status(dst_handle* h, uint32_t* flags, void* stream);
 /* Hierarchy facts for tests and reports: surfels, internal nodes, bytes held on the device. */
 int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t* device_bytes);
 
+/* Tunables. DST_OPT_WAVEFRONT_MIN_RAYS: trace calls with at least this many rays run as rounds of
+ * separate gather / composite kernels over the live rays (default 131072); smaller calls use one
+ * thread per ray for the whole path. Results do not depend on the setting. */
+#define DST_OPT_WAVEFRONT_MIN_RAYS 1
+int dst_set_option(dst_handle* h, int option, int64_t value);
+
 /* Timing of the main kernels with CUDA events on the launching stream. While enabled, every
  * dst_build / dst_forward / dst_backward call records an event pair around its dominant kernel
  * (which = 0: the whole build or refit sequence, 1: the forward trace kernel, 2: the backward trace

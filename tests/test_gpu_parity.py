@@ -24,8 +24,10 @@ def C():
     return _C
 
 
-def _build(C, wc):
+def _build(C, wc, wave=False):
     st = C.OptiXStateWrapper("")
+    if wave:
+        st.set_wavefront_min_rays(0)      # run the wavefront rounds even on these small ray counts
     C.build_acceleration_structure(st, wc["v"], wc["f"], 1)
     return st
 
@@ -66,10 +68,10 @@ def test_knearest_walk_equals_exhaustive(C, oracle_mod, config):
     assert int(cw.max()) > 0
 
 
-def _forward_pair(C, oracle_mod, config, hit_cap=320):
+def _forward_pair(C, oracle_mod, config, hit_cap=320, wave=False):
     w = hp.reduced_workload(config)
     wc = hp.to_cuda(w)
-    st = _build(C, wc)
+    st = _build(C, wc, wave)
     diag = dict(hit_cap=hit_cap)
     got = hp.cuda_forward(C, st, wc, training=True, diag=diag)
     torch.cuda.synchronize()
@@ -80,9 +82,10 @@ def _forward_pair(C, oracle_mod, config, hit_cap=320):
     return w, wc, st, got, want, diag, orc
 
 
+@pytest.mark.parametrize("wave", [False, True], ids=["per-ray", "wavefront"])
 @pytest.mark.parametrize("config", [1, 2, 3, 4, 5])
-def test_forward_parity(C, oracle_mod, config):
-    w, wc, st, got, want, diag, _ = _forward_pair(C, oracle_mod, config)
+def test_forward_parity(C, oracle_mod, config, wave):
+    w, wc, st, got, want, diag, _ = _forward_pair(C, oracle_mod, config, wave=wave)
     H, W = w["ray_o"].shape[:2]
     # contributing hit sequences: exact, on every ray, over all bounces
     cnt = diag["hit_cnt"].cpu().numpy()
@@ -103,9 +106,10 @@ def test_forward_parity(C, oracle_mod, config):
     assert c[5] == want["stats"][3] and c[4] == want["stats"][2] and c[1] == want["stats"][0]
 
 
+@pytest.mark.parametrize("wave", [False, True], ids=["per-ray", "wavefront"])
 @pytest.mark.parametrize("config", [1, 2, 3, 4, 5])
-def test_backward_parity(C, oracle_mod, config):
-    w, wc, st, got, want, diag, orc = _forward_pair(C, oracle_mod, config, hit_cap=0)
+def test_backward_parity(C, oracle_mod, config, wave):
+    w, wc, st, got, want, diag, orc = _forward_pair(C, oracle_mod, config, hit_cap=0, wave=wave)
     gen = torch.Generator().manual_seed(100 + config)
     H, W = w["ray_o"].shape[:2]
     # unit upstream gradients on the outputs the configuration names, plus a seeded random run on all of them
