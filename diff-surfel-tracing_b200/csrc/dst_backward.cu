@@ -533,16 +533,16 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
     p.rounds = wave ? DST_WF_ROUNDS : 0;
     p.min_count = wave ? (int)(slots / 64 > 4096 ? slots / 64 : 4096) : 1;
     const bool diag = a->counters != nullptr;
-    DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * (DST_WF_ROUNDS + 2), st));
+    DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 2 * (DST_WF_ROUNDS + 2), st));
     dst_prof_mark(h, 2, 0, st);
     k_bwd_init<<<(unsigned int)((slots + 255) / 256), 256, 0, st>>>(p, slots);
     const int g_enum = dst_wavefront_grid(h, slots, ENUM_THREADS, 10), g_shade = dst_wavefront_grid(h, slots, BWD_THREADS, 4);
     for (int r = 0; r < p.rounds; r++) {
         if (diag) {
-            k_enum<true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters);
+            k_enum<true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters);
             k_bwd_shade<true><<<g_shade, BWD_THREADS, 0, st>>>(p, r);
         } else {
-            k_enum<false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr);
+            k_enum<false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr);
             k_bwd_shade<false><<<g_shade, BWD_THREADS, 0, st>>>(p, r);
         }
     }

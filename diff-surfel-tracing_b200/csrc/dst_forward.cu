@@ -366,7 +366,7 @@ int dst_ensure_wavefront(dst_handle* h, long long slots, size_t state_bytes) {
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_kcnt, 4 * (size_t)cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_list[0], 4 * (size_t)cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_list[1], 4 * (size_t)cap);
-    if (e == cudaSuccess) e = cudaMalloc(&h->wf_counts, 4 * (DST_WF_ROUNDS + 2));
+    if (e == cudaSuccess) e = cudaMalloc(&h->wf_counts, 4 * 2 * (DST_WF_ROUNDS + 2));
     if (e != cudaSuccess) { cudaGetLastError(); return dst_set_error(h, DST_E_NOMEM, "ray scratch allocation for %lld rays failed: %s", slots, cudaGetErrorString(e)); }
     h->wf_cap = cap; h->wf_state_bytes = sb;
     return DST_OK;
@@ -401,16 +401,16 @@ int dst_forward_impl(dst_handle* h, const dst_fwd_args* a, cudaStream_t st) {
     p.rounds = wave ? DST_WF_ROUNDS : 0;
     p.min_count = wave ? (int)(slots / 64 > 4096 ? slots / 64 : 4096) : 1;
     const bool diag = a->hit_log || a->hit_cnt || a->counters;
-    DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * (DST_WF_ROUNDS + 2), st));
+    DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 2 * (DST_WF_ROUNDS + 2), st));
     dst_prof_mark(h, 1, 0, st);
     k_fwd_init<<<(unsigned int)((slots + 255) / 256), 256, 0, st>>>(p, slots);
     const int g_enum = dst_wavefront_grid(h, slots, ENUM_THREADS, 12), g_shade = dst_wavefront_grid(h, slots, SHADE_THREADS, 8);
     for (int r = 0; r < p.rounds; r++) {
         if (diag) {
-            k_enum<true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters);
+            k_enum<true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters);
             k_fwd_shade<true><<<g_shade, SHADE_THREADS, 0, st>>>(p, r);
         } else {
-            k_enum<false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr);
+            k_enum<false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr);
             k_fwd_shade<false><<<g_shade, SHADE_THREADS, 0, st>>>(p, r);
         }
     }

@@ -8,6 +8,7 @@
 #define DST_MAX_CHUNKS 4096          // bound on enumerations per ray segment (the reference loops without one)
 #define DST_MAX_INTERSECTION 256     // optix_tracer/config.h:23
 #define DST_REF_SHIFT 4                // leaf reference = surfel id << 4 | sub-rectangle (iu << 2 | iv)
+#define DST_NODE_VOTE 16               // lanes with node work needed to stay in the node phase of k_enum
 #define DST_PAD_FACTOR 4e-6f         // box padding per unit of coordinate magnitude, see knearest()
 
 struct TraceCounters { unsigned long long segs, enums, nodes, quads, evals, contribs; };
@@ -278,27 +279,152 @@ struct __align__(16) EnumReq { float ox, oy, oz, dx, dy, dz, kmax0, pad; };
 constexpr int ENUM_THREADS = 128;
 #define DST_WF_ROUNDS 48
 
+// Slab constants of one ray for the padded child-box test (see knearest()).
+struct RaySlab {
+    float ix, iy, iz, onx, ony, onz, ofx, ofy, ofz;
+    bool px, py, pz, valid;
+};
+__device__ __forceinline__ RaySlab make_slab(float ox, float oy, float oz, float dx, float dy, float dz, float absmax) {
+    RaySlab r;
+    const float omax = fmaxf(fabsf(ox), fmaxf(fabsf(oy), fabsf(oz)));
+    r.valid = omax < INFINITY;
+    const float pad = DST_PAD_FACTOR * (omax + absmax) + 1e-30f;
+    const float sdx = fabsf(dx) < 1e-20f ? copysignf(1e-20f, dx) : dx;
+    const float sdy = fabsf(dy) < 1e-20f ? copysignf(1e-20f, dy) : dy;
+    const float sdz = fabsf(dz) < 1e-20f ? copysignf(1e-20f, dz) : dz;
+    r.ix = 1.0f / sdx; r.iy = 1.0f / sdy; r.iz = 1.0f / sdz;
+    r.px = !(sdx < 0.0f); r.py = !(sdy < 0.0f); r.pz = !(sdz < 0.0f);
+    r.onx = fmaf(ox, r.ix, pad * fabsf(r.ix)); r.ofx = fmaf(ox, r.ix, -pad * fabsf(r.ix));
+    r.ony = fmaf(oy, r.iy, pad * fabsf(r.iy)); r.ofy = fmaf(oy, r.iy, -pad * fabsf(r.iy));
+    r.onz = fmaf(oz, r.iz, pad * fabsf(r.iz)); r.ofz = fmaf(oz, r.iz, -pad * fabsf(r.iz));
+    return r;
+}
+
+// Persistent enumeration kernel: every lane walks the hierarchy for one ray at a time and, as soon
+// as its ray is done, takes the next entry of the live list from a shared cursor, so a warp stays
+// full until the list is exhausted however uneven the rays are. Same result as knearest().
 template <bool COUNT>
 __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumReq* __restrict__ req, const int* __restrict__ list,
-                                                       const int* __restrict__ count_ptr, int min_count,
+                                                       const int* __restrict__ count_ptr, int* cursor, int min_count,
                                                        unsigned long long* __restrict__ kbuf, int* __restrict__ kcnt,
                                                        unsigned int* status, unsigned long long* counters) {
     __shared__ unsigned long long kshared[DST_CHUNK * ENUM_THREADS];
-    const int n = *count_ptr;
-    if (n < min_count) return;
+    const int total = *count_ptr;
+    if (total < min_count || bvh.nrefs <= 0) return;
+    constexpr int KS = ENUM_THREADS;
+    constexpr int DONE = 0x7fffffff;
     unsigned long long* kb = kshared + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const float absmax = __ldg(bvh.header + 6);
     TraceCounters tc = { 0, 0, 0, 0, 0, 0 };
-    for (int i = blockIdx.x * ENUM_THREADS + threadIdx.x; i < n; i += gridDim.x * ENUM_THREADS) {
-        const int ray = list[i];
-        if (ray < 0) continue;
-        const float4 r0 = __ldg(reinterpret_cast<const float4*>(req + ray)), r1 = __ldg(reinterpret_cast<const float4*>(req + ray) + 1);
-        const int c = knearest<false, COUNT, ENUM_THREADS>(bvh, r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, kb, status, tc, r1.z);
-        if (COUNT) tc.enums++;
-        kcnt[ray] = c;
-        ulonglong2* out = reinterpret_cast<ulonglong2*>(kbuf + (size_t)ray * DST_CHUNK);
+    unsigned long long stack[DST_STACK];
+    int sp = 0, n = 0, cur = DONE, ray = -1;
+    float kmax = DST_T_MAX;
+    float ox = 0.f, oy = 0.f, oz = 0.f, dx = 0.f, dy = 0.f, dz = 0.f;
+    RaySlab sl = make_slab(0.f, 0.f, 0.f, 1.f, 1.f, 1.f, 0.f);
+    bool exhausted = false;            // warp-uniform: the list has no more entries
+
+    auto pop = [&]() -> int {
+        while (sp > 0) {
+            const unsigned long long e = stack[--sp];
+            if (__uint_as_float((unsigned int)(e >> 32)) <= kmax) return (int)(unsigned int)e;
+        }
+        return DONE;
+    };
+
+    for (;;) {
+        // ---- hand finished lanes their next ray ----
+        const unsigned int idle = __ballot_sync(0xffffffffu, ray < 0);
+        if (idle && !exhausted) {
+            int base = 0;
+            const int leader = __ffs(idle) - 1;
+            if (lane == leader) base = atomicAdd(cursor, __popc(idle));
+            base = __shfl_sync(0xffffffffu, base, leader);
+            if (base + __popc(idle) >= total) exhausted = true;
+            if (ray < 0) {
+                const int idx = base + __popc(idle & ((1u << lane) - 1u));
+                const int r = idx < total ? list[idx] : -1;
+                if (r >= 0) {
+                    const float4 r0 = __ldg(reinterpret_cast<const float4*>(req + r)), r1 = __ldg(reinterpret_cast<const float4*>(req + r) + 1);
+                    ox = r0.x; oy = r0.y; oz = r0.z; dx = r0.w; dy = r1.x; dz = r1.y; kmax = r1.z;
+                    sl = make_slab(ox, oy, oz, dx, dy, dz, absmax);
+                    ray = r; n = 0; sp = 0;
+                    cur = sl.valid ? 0 : DONE;
+                    if (COUNT) tc.enums++;
+                }
+            }
+        }
+        if (__all_sync(0xffffffffu, ray < 0)) { if (exhausted) break; else continue; }
+
+        // ---- node phase: lanes holding an internal node step through it; the phase lasts while at
+        //      least DST_NODE_VOTE lanes have node work (or nobody has anything else to do), so that
+        //      lanes waiting with a leaf are not starved and node steps run with most lanes busy ----
+        for (;;) {
+            const bool is_node = (unsigned int)cur < (unsigned int)DONE;
+            const unsigned int m = __ballot_sync(0xffffffffu, is_node);
+            if (m == 0u) break;
+            if (__popc(m) < DST_NODE_VOTE && __any_sync(0xffffffffu, cur < 0 || (cur == DONE && ray >= 0))) break;
+            if (!is_node) continue;
+            const float4* np = bvh.nodes + 4 * (size_t)cur;
+            const float4 a = __ldg(np), b = __ldg(np + 1), c = __ldg(np + 2);
+            const int4 lk = __ldg(reinterpret_cast<const int4*>(np + 3));
+            if (COUNT) tc.nodes++;
+            const float n0x = sl.px ? a.x : a.w, f0x = sl.px ? a.w : a.x;
+            const float n0y = sl.py ? a.y : b.x, f0y = sl.py ? b.x : a.y;
+            const float n0z = sl.pz ? a.z : b.y, f0z = sl.pz ? b.y : a.z;
+            const float n1x = sl.px ? b.z : c.y, f1x = sl.px ? c.y : b.z;
+            const float n1y = sl.py ? b.w : c.z, f1y = sl.py ? c.z : b.w;
+            const float n1z = sl.pz ? c.x : c.w, f1z = sl.pz ? c.w : c.x;
+            const float tn0 = fmaxf(fmaxf(fmaf(n0x, sl.ix, -sl.onx), fmaf(n0y, sl.iy, -sl.ony)), fmaxf(fmaf(n0z, sl.iz, -sl.onz), 0.0f));
+            const float tf0 = fminf(fminf(fmaf(f0x, sl.ix, -sl.ofx), fmaf(f0y, sl.iy, -sl.ofy)), fmaf(f0z, sl.iz, -sl.ofz));
+            const float tn1 = fmaxf(fmaxf(fmaf(n1x, sl.ix, -sl.onx), fmaf(n1y, sl.iy, -sl.ony)), fmaxf(fmaf(n1z, sl.iz, -sl.onz), 0.0f));
+            const float tf1 = fminf(fminf(fmaf(f1x, sl.ix, -sl.ofx), fmaf(f1y, sl.iy, -sl.ofy)), fmaf(f1z, sl.iz, -sl.ofz));
+            const bool h0 = (tn0 <= tf0) && (tn0 <= kmax);
+            const bool h1 = (tn1 <= tf1) && (tn1 <= kmax);
+            if (h0 && h1) {
+                const bool swap = tn1 < tn0;
+                const int cf = swap ? lk.x : lk.y;
+                const float tfar = swap ? tn0 : tn1;
+                if (sp < DST_STACK) stack[sp++] = ((unsigned long long)__float_as_uint(tfar) << 32) | (unsigned int)cf;
+                else atomicOr(status, DST_STATUS_STACK_OVERFLOW);
+                cur = swap ? lk.y : lk.x;
+            } else if (h0) cur = lk.x;
+            else if (h1) cur = lk.y;
+            else cur = pop();
+        }
+        // ---- leaf: exact quad test and k-buffer insertion ----
+        if (cur < 0) {
+            const int pos = ~cur;
+            const float4* qp = bvh.quads + 3 * (size_t)pos;
+            const float4 qa = __ldg(qp), qb = __ldg(qp + 1), qc = __ldg(qp + 2);
+            if (COUNT) tc.quads++;
+            float t; int tri;
+            if (ray_quad(qa, qb, qc, ox, oy, oz, dx, dy, dz, kmax, t, tri)) {
+                const unsigned int gid = (unsigned int)__ldg(bvh.leaf_gid + pos) >> DST_REF_SHIFT;
+                const unsigned long long key = make_key(t, 2u * gid + (unsigned int)tri);
+                if (!(n == DST_CHUNK && key >= kb[(DST_CHUNK - 1) * KS])) {
+                    int j = n;
+                    while (j > 0 && kb[(j - 1) * KS] > key) j--;
+                    if (!(j > 0 && kb[(j - 1) * KS] == key)) {
+                        if (n == DST_CHUNK) n = DST_CHUNK - 1;
+                        for (int i = n; i > j; i--) kb[i * KS] = kb[(i - 1) * KS];
+                        kb[j * KS] = key;
+                        n++;
+                        if (n == DST_CHUNK) kmax = hitkey_t(kb[(DST_CHUNK - 1) * KS]);
+                    }
+                }
+            }
+            cur = pop();
+        }
+        // ---- done: publish the chunk ----
+        if (cur == DONE && ray >= 0) {
+            kcnt[ray] = n;
+            ulonglong2* out = reinterpret_cast<ulonglong2*>(kbuf + (size_t)ray * DST_CHUNK);
 #pragma unroll
-        for (int k = 0; k < DST_CHUNK / 2; k++) {
-            if (2 * k < c) out[k] = make_ulonglong2(kb[(2 * k) * ENUM_THREADS], kb[(2 * k + 1) * ENUM_THREADS]);
+            for (int k = 0; k < DST_CHUNK / 2; k++) {
+                if (2 * k < n) out[k] = make_ulonglong2(kb[(2 * k) * KS], kb[(2 * k + 1) * KS]);
+            }
+            ray = -1;
         }
     }
     if (COUNT && counters) { atomicAdd(counters + 1, tc.enums); atomicAdd(counters + 2, tc.nodes); atomicAdd(counters + 3, tc.quads); }
