@@ -79,6 +79,7 @@ int dst_destroy(dst_handle* h) {
     if (!h) return DST_OK;
     DeviceGuard g(h->device);
     cudaFree(h->nodes); cudaFree(h->quads); cudaFree(h->leaf_gid); cudaFree(h->leaf_parent); cudaFree(h->arrive);
+    cudaFree(h->node_parent); cudaFree(h->node_first); cudaFree(h->node_count); cudaFree(h->child_cost);
     cudaFree(h->keys); cudaFree(h->keys_alt); cudaFree(h->vals); cudaFree(h->vals_alt); cudaFree(h->block_hist);
     cudaFree(h->header); cudaFree(h->status); cudaFree(h->cache); cudaFree(h->arena);
     cudaFree(h->wf_state); cudaFree(h->wf_req); cudaFree(h->wf_kbuf); cudaFree(h->wf_kcnt); cudaFree(h->wf_list[0]); cudaFree(h->wf_list[1]); cudaFree(h->wf_counts);
@@ -133,7 +134,7 @@ int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t*
     if (!h) return DST_E_ARG;
     if (surfels) *surfels = h->built ? h->P : 0;
     if (nodes) *nodes = h->built ? (h->P > 1 ? h->P - 1 : 1) : 0;
-    if (device_bytes) *device_bytes = h->cap * (64 + 48 + 4 + 4 + 4 + 16 + 8) + h->hist_cap * 1024 + h->cache_cap * 64 + h->arena_cap * 4 * DST_ARENA_FLOATS +
+    if (device_bytes) *device_bytes = h->cap * (64 + 48 + 4 + 4 + 4 + 16 + 8 + 20) + h->hist_cap * 1024 + h->cache_cap * 64 + h->arena_cap * 4 * DST_ARENA_FLOATS +
                                       h->wf_cap * (long long)(h->wf_state_bytes + 32 + 8 * DST_CHUNK + 4 + 8);
     return DST_OK;
 }

@@ -208,7 +208,8 @@ __device__ __forceinline__ int key_delta(const unsigned long long* __restrict__ 
 }
 
 __global__ void __launch_bounds__(256) k_karras(const unsigned long long* __restrict__ keys, int n, BvhNode* __restrict__ nodes,
-                                                int* __restrict__ leaf_parent) {
+                                                int* __restrict__ leaf_parent, int* __restrict__ node_parent,
+                                                int* __restrict__ node_first, int* __restrict__ node_count) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n - 1) return;
     const unsigned long long ki = keys[i];
@@ -229,23 +230,38 @@ __global__ void __launch_bounds__(256) k_karras(const unsigned long long* __rest
     const int gamma = i + s * d + min(d, 0);
     const int lo = min(i, j), hi = max(i, j);
     int c0, c1;
-    if (lo == gamma) { c0 = ~gamma; leaf_parent[gamma] = i; } else { c0 = gamma; nodes[gamma].parent = i; }
-    if (hi == gamma + 1) { c1 = ~(gamma + 1); leaf_parent[gamma + 1] = i; } else { c1 = gamma + 1; nodes[gamma + 1].parent = i; }
+    if (lo == gamma) { c0 = ~gamma; leaf_parent[gamma] = i; } else { c0 = gamma; node_parent[gamma] = i; }
+    if (hi == gamma + 1) { c1 = ~(gamma + 1); leaf_parent[gamma + 1] = i; } else { c1 = gamma + 1; node_parent[gamma + 1] = i; }
     nodes[i].c0 = c0; nodes[i].c1 = c1;
-    if (i == 0) nodes[0].parent = -1;
+    node_first[i] = lo; node_count[i] = hi - lo + 1;
+    if (i == 0) node_parent[0] = -1;
 }
 
 // single-surfel scene: one node whose second child is an empty box
-__global__ void k_single_leaf(BvhNode* nodes, int* leaf_parent, unsigned int* arrive) {
-    nodes[0].c0 = ~0; nodes[0].c1 = ~0; nodes[0].parent = -1;
+__global__ void k_single_leaf(BvhNode* nodes, int* leaf_parent, int* node_parent, int* node_first, int* node_count, unsigned int* arrive) {
+    nodes[0].c0 = ~0; nodes[0].c1 = ~0; node_parent[0] = -1; node_first[0] = 0; node_count[0] = 1;
+    nodes[0].t0 = DST_LEAF_LINK(0, 1); nodes[0].t1 = DST_LEAF_LINK(0, 1);
     for (int a = 0; a < 3; a++) { nodes[0].box[6 + a] = INFINITY; nodes[0].box[9 + a] = -INFINITY; }
     leaf_parent[0] = 0;
     arrive[0] = 1;      // the lone leaf acts as the second arrival
 }
 
 // ---- bottom-up pass: quad frames + leaf boxes, then boxes of all ancestors ----------------------
+// On the way up every node also gets the expected cost of walking its subtree (surface-area
+// heuristic) and decides whether the walk should treat it as ONE run of leaves: where boxes overlap
+// almost completely (large quads crossing each other) descending costs more than testing every quad.
+#define DST_COST_NODE 1.2f
+#define DST_COST_QUAD 1.0f
+__device__ __forceinline__ float box_area(const float* lo, const float* hi) {
+    const float dx = hi[0] - lo[0], dy = hi[1] - lo[1], dz = hi[2] - lo[2];
+    const float a = dx * dy + dy * dz + dz * dx;
+    return (a > 0.0f && a < INFINITY) ? a : 0.0f;
+}
+
 __global__ void __launch_bounds__(256) k_refit(const float* __restrict__ verts, int P, const unsigned int* __restrict__ vals,
-                                               BvhNode* nodes, const int* __restrict__ leaf_parent, unsigned int* arrive,
+                                               BvhNode* nodes, const int* __restrict__ leaf_parent, const int* __restrict__ node_parent,
+                                               const int* __restrict__ node_first, const int* __restrict__ node_count,
+                                               float* child_cost, unsigned int* arrive,
                                                float4* __restrict__ quads, int* __restrict__ leaf_gid, float* header) {
     const int pos = blockIdx.x * blockDim.x + threadIdx.x;
     if (pos >= P) return;
@@ -264,7 +280,9 @@ __global__ void __launch_bounds__(256) k_refit(const float* __restrict__ verts, 
     leaf_gid[pos] = gid << 4;       // reference = surfel id << 4 | sub-rectangle
     float lo[3], hi[3];
     quad_box(v, lo, hi);
-    int child = ~pos;
+    int child = ~pos;                           // topology id of the subtree being carried up
+    int link = DST_LEAF_LINK(pos, 1);           // how the walk reaches it
+    float cost = DST_COST_QUAD;
     int parent = leaf_parent[pos];
     // the depth of a Karras tree over 64-bit keys with index tie-breaks is below 128
     for (int guard = 0; guard < 128; guard++) {
@@ -272,10 +290,15 @@ __global__ void __launch_bounds__(256) k_refit(const float* __restrict__ verts, 
         const int slot = (nd->c0 == child) ? 0 : 1;
         float2* dst = reinterpret_cast<float2*>(nd->box + 6 * slot);
         dst[0] = make_float2(lo[0], lo[1]); dst[1] = make_float2(lo[2], hi[0]); dst[2] = make_float2(hi[1], hi[2]);
+        (&nd->t0)[slot] = link;
+        child_cost[2 * (size_t)parent + slot] = cost;
         __threadfence();
         if (atomicAdd(&arrive[parent], 1u) == 0u) return;      // the sibling subtree is not done yet
         const float2* src = reinterpret_cast<const float2*>(nd->box + 6 * (1 - slot));
         const float2 s0 = __ldcg(src), s1 = __ldcg(src + 1), s2 = __ldcg(src + 2);
+        const float sib_cost = __ldcg(child_cost + 2 * (size_t)parent + (1 - slot));
+        float slo[3] = { s0.x, s0.y, s1.x }, shi[3] = { s1.y, s2.x, s2.y };
+        const float a_me = box_area(lo, hi), a_sib = box_area(slo, shi);
         lo[0] = fminf(lo[0], s0.x); lo[1] = fminf(lo[1], s0.y); lo[2] = fminf(lo[2], s1.x);
         hi[0] = fmaxf(hi[0], s1.y); hi[1] = fmaxf(hi[1], s2.x); hi[2] = fmaxf(hi[2], s2.y);
         if (parent == 0) {
@@ -289,8 +312,15 @@ __global__ void __launch_bounds__(256) k_refit(const float* __restrict__ verts, 
             header[6] = am;
             return;
         }
+        const float a_all = box_area(lo, hi);
+        const float p_me = a_all > 0.0f ? fminf(a_me / a_all, 1.0f) : 1.0f, p_sib = a_all > 0.0f ? fminf(a_sib / a_all, 1.0f) : 1.0f;
+        const float cost_split = DST_COST_NODE + p_me * cost + p_sib * sib_cost;
+        const int count = node_count[parent];
+        const float cost_run = DST_COST_QUAD * (float)count;
+        if (count <= DST_LEAF_MAX && cost_run <= cost_split) { link = DST_LEAF_LINK(node_first[parent], count); cost = cost_run; }
+        else { link = parent; cost = cost_split; }
         child = parent;
-        parent = nd->parent;
+        parent = node_parent[parent];
     }
 }
 
@@ -309,6 +339,8 @@ int ensure_capacity(dst_handle* h, int64_t P) {
     if (P <= h->cap) return DST_OK;
     // grow-only arena; the old buffers are released first (a rebuild does not need them)
     cudaFree(h->nodes); cudaFree(h->quads); cudaFree(h->leaf_gid); cudaFree(h->leaf_parent); cudaFree(h->arrive);
+    cudaFree(h->node_parent); cudaFree(h->node_first); cudaFree(h->node_count); cudaFree(h->child_cost);
+    h->node_parent = h->node_first = h->node_count = nullptr; h->child_cost = nullptr;
     cudaFree(h->keys); cudaFree(h->keys_alt); cudaFree(h->vals); cudaFree(h->vals_alt); cudaFree(h->block_hist);
     h->nodes = nullptr; h->quads = nullptr; h->leaf_gid = nullptr; h->leaf_parent = nullptr; h->arrive = nullptr;
     h->keys = h->keys_alt = nullptr; h->vals = h->vals_alt = nullptr; h->block_hist = nullptr;
@@ -321,6 +353,10 @@ int ensure_capacity(dst_handle* h, int64_t P) {
     if (e == cudaSuccess) e = cudaMalloc(&h->leaf_gid, 4 * cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->leaf_parent, 4 * cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->arrive, 4 * cap);
+    if (e == cudaSuccess) e = cudaMalloc(&h->node_parent, 4 * cap);
+    if (e == cudaSuccess) e = cudaMalloc(&h->node_first, 4 * cap);
+    if (e == cudaSuccess) e = cudaMalloc(&h->node_count, 4 * cap);
+    if (e == cudaSuccess) e = cudaMalloc(&h->child_cost, 8 * cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->keys, 8 * cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->keys_alt, 8 * cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->vals, 4 * cap);
@@ -338,7 +374,7 @@ int ensure_capacity(dst_handle* h, int64_t P) {
 
 int dst_bvh_build_impl(dst_handle* h, const float* v, int64_t P, int rebuild, cudaStream_t st) {
     if (P <= 0) return dst_set_error(h, DST_E_ARG, "vertices must hold at least one surfel (4 vertices)");
-    if (P > (1ll << 27)) return dst_set_error(h, DST_E_ARG, "at most 2^27 surfels are supported");
+    if (P > (1ll << DST_LEAF_POS_BITS)) return dst_set_error(h, DST_E_ARG, "at most 2^26 surfels are supported");
     if ((reinterpret_cast<uintptr_t>(v) & 15) != 0) return dst_set_error(h, DST_E_ARG, "vertices must be 16-byte aligned");
     if (!rebuild) {
         if (!h->built) return dst_set_error(h, DST_E_STATE, "refit (rebuild=0) requested before any build");
@@ -371,12 +407,13 @@ int dst_bvh_build_impl(dst_handle* h, const float* v, int64_t P, int rebuild, cu
             unsigned int* tv = vin; vin = vout; vout = tv;
         }
         // 8 passes: the sorted data is back in keys / vals
-        if (n > 1) k_karras<<<(n - 1 + tpb - 1) / tpb, tpb, 0, st>>>(h->keys, n, h->nodes, h->leaf_parent);
+        if (n > 1) k_karras<<<(n - 1 + tpb - 1) / tpb, tpb, 0, st>>>(h->keys, n, h->nodes, h->leaf_parent, h->node_parent, h->node_first, h->node_count);
         h->P = P; h->nrefs = P;
     }
     DST_CUDA_TRY(h, cudaMemsetAsync(h->arrive, 0, 4 * (size_t)(n > 1 ? n - 1 : 1), st));
-    if (n == 1) k_single_leaf<<<1, 1, 0, st>>>(h->nodes, h->leaf_parent, h->arrive);
-    k_refit<<<grid, tpb, 0, st>>>(v, n, h->vals, h->nodes, h->leaf_parent, h->arrive, h->quads, h->leaf_gid, h->header);
+    if (n == 1) k_single_leaf<<<1, 1, 0, st>>>(h->nodes, h->leaf_parent, h->node_parent, h->node_first, h->node_count, h->arrive);
+    k_refit<<<grid, tpb, 0, st>>>(v, n, h->vals, h->nodes, h->leaf_parent, h->node_parent, h->node_first, h->node_count, h->child_cost,
+                                  h->arrive, h->quads, h->leaf_gid, h->header);
     dst_prof_mark(h, 0, 1, st);
     DST_CUDA_TRY(h, cudaGetLastError());
     h->built = true;

@@ -7,7 +7,7 @@
 
 // ---------------------------------------------------------------------------------------------
 // Hierarchy layout in HBM
-//   nodes      (P-1) x 64 B : boxes of both children + child links + parent (Aila-Laine style,
+//   nodes      (P-1) x 64 B : boxes of both children + child links (Aila-Laine style,
 //                             one 64-byte fetch = four 16-byte vector loads per visited node)
 //   quads      P x 48 B     : plane frame of each quad in LEAF ORDER (three 16-byte loads per test)
 //   leaf_gid   P x 4 B      : leaf position -> surfel id
@@ -15,10 +15,16 @@
 // ---------------------------------------------------------------------------------------------
 struct __align__(16) BvhNode {
     float box[12];      // [0..2] lo of child 0, [3..5] hi of child 0, [6..8] lo of child 1, [9..11] hi of child 1
-    int c0, c1;
-    int parent;         // -1 for the root
-    int pad;
+    int c0, c1;         // topology of the Karras tree: child >= 0 internal node, < 0 leaf position ~c
+    int t0, t1;         // links the walk follows: >= 0 internal node, < 0 a run of leaves (DST_LEAF_* below);
+                        // a subtree whose boxes overlap so much that testing all its quads is cheaper is one run
 };
+#define DST_LEAF_FLAG 0x80000000u
+#define DST_LEAF_POS_BITS 26
+#define DST_LEAF_MAX 16               // most quads in one run
+#define DST_LEAF_LINK(first, count) ((int)(DST_LEAF_FLAG | ((unsigned int)((count) - 1) << DST_LEAF_POS_BITS) | (unsigned int)(first)))
+#define DST_LEAF_FIRST(link) ((int)((unsigned int)(link) & ((1u << DST_LEAF_POS_BITS) - 1u)))
+#define DST_LEAF_COUNT(link) ((int)(((unsigned int)(link) >> DST_LEAF_POS_BITS) & 31u) + 1)
 static_assert(sizeof(BvhNode) == 64, "node must be one 64-byte record");
 
 // header floats: [0..2] scene lo, [3..5] scene hi, [6] largest |coordinate|
@@ -54,6 +60,10 @@ struct dst_handle {
     float4* quads;
     int* leaf_gid;
     int* leaf_parent;
+    int* node_parent;             // -1 for the root
+    int* node_first;              // first leaf position under each node
+    int* node_count;              // leaves under each node
+    float* child_cost;            // 2 per node: expected walk cost of each child subtree (bottom-up pass)
     unsigned int* arrive;         // per-node arrival counters of the bottom-up pass
     unsigned long long *keys, *keys_alt;
     unsigned int *vals, *vals_alt;

@@ -109,17 +109,20 @@ __device__ __forceinline__ int knearest(const BvhView& bvh, float ox, float oy, 
             const bool h1 = (tn1 <= tf1) && (tn1 <= kmax);
             if (h0 && h1) {
                 const bool swap = tn1 < tn0;
-                const int cf = swap ? lk.x : lk.y;
+                const int cf = swap ? lk.z : lk.w;
                 const float tfar = swap ? tn0 : tn1;
                 if (sp < DST_STACK) stack[sp++] = ((unsigned long long)__float_as_uint(tfar) << 32) | (unsigned int)cf;
                 else atomicOr(status, DST_STATUS_STACK_OVERFLOW);
-                cur = swap ? lk.y : lk.x;
-            } else if (h0) cur = lk.x;
-            else if (h1) cur = lk.y;
+                cur = swap ? lk.w : lk.z;
+            } else if (h0) cur = lk.z;
+            else if (h1) cur = lk.w;
             else cur = pop();
         }
         if (cur == DONE) break;
-        offer(~cur);
+        {   // a run of leaves: test every quad of it
+            const int first = DST_LEAF_FIRST(cur), count = DST_LEAF_COUNT(cur);
+            for (int q = 0; q < count; q++) offer(first + q);
+        }
         cur = pop();
     }
     return n;
@@ -383,36 +386,36 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
             const bool h1 = (tn1 <= tf1) && (tn1 <= kmax);
             if (h0 && h1) {
                 const bool swap = tn1 < tn0;
-                const int cf = swap ? lk.x : lk.y;
+                const int cf = swap ? lk.z : lk.w;
                 const float tfar = swap ? tn0 : tn1;
                 if (sp < DST_STACK) stack[sp++] = ((unsigned long long)__float_as_uint(tfar) << 32) | (unsigned int)cf;
                 else atomicOr(status, DST_STATUS_STACK_OVERFLOW);
-                cur = swap ? lk.y : lk.x;
-            } else if (h0) cur = lk.x;
-            else if (h1) cur = lk.y;
+                cur = swap ? lk.w : lk.z;
+            } else if (h0) cur = lk.z;
+            else if (h1) cur = lk.w;
             else cur = pop();
         }
-        // ---- leaf: exact quad test and k-buffer insertion ----
+        // ---- leaf run: exact quad tests and k-buffer insertion ----
         if (cur < 0) {
-            const int pos = ~cur;
-            const float4* qp = bvh.quads + 3 * (size_t)pos;
-            const float4 qa = __ldg(qp), qb = __ldg(qp + 1), qc = __ldg(qp + 2);
-            if (COUNT) tc.quads++;
-            float t; int tri;
-            if (ray_quad(qa, qb, qc, ox, oy, oz, dx, dy, dz, kmax, t, tri)) {
+            const int first = DST_LEAF_FIRST(cur), count = DST_LEAF_COUNT(cur);
+            for (int lq = 0; lq < count; lq++) {
+                const int pos = first + lq;
+                const float4* qp = bvh.quads + 3 * (size_t)pos;
+                const float4 qa = __ldg(qp), qb = __ldg(qp + 1), qc = __ldg(qp + 2);
+                if (COUNT) tc.quads++;
+                float t; int tri;
+                if (!ray_quad(qa, qb, qc, ox, oy, oz, dx, dy, dz, kmax, t, tri)) continue;
                 const unsigned int gid = (unsigned int)__ldg(bvh.leaf_gid + pos) >> DST_REF_SHIFT;
                 const unsigned long long key = make_key(t, 2u * gid + (unsigned int)tri);
-                if (!(n == DST_CHUNK && key >= kb[(DST_CHUNK - 1) * KS])) {
-                    int j = n;
-                    while (j > 0 && kb[(j - 1) * KS] > key) j--;
-                    if (!(j > 0 && kb[(j - 1) * KS] == key)) {
-                        if (n == DST_CHUNK) n = DST_CHUNK - 1;
-                        for (int i = n; i > j; i--) kb[i * KS] = kb[(i - 1) * KS];
-                        kb[j * KS] = key;
-                        n++;
-                        if (n == DST_CHUNK) kmax = hitkey_t(kb[(DST_CHUNK - 1) * KS]);
-                    }
-                }
+                if (n == DST_CHUNK && key >= kb[(DST_CHUNK - 1) * KS]) continue;
+                int j = n;
+                while (j > 0 && kb[(j - 1) * KS] > key) j--;
+                if (j > 0 && kb[(j - 1) * KS] == key) continue;
+                if (n == DST_CHUNK) n = DST_CHUNK - 1;
+                for (int i = n; i > j; i--) kb[i * KS] = kb[(i - 1) * KS];
+                kb[j * KS] = key;
+                n++;
+                if (n == DST_CHUNK) kmax = hitkey_t(kb[(DST_CHUNK - 1) * KS]);
             }
             cur = pop();
         }
