@@ -432,3 +432,77 @@ int dst_knearest_impl(dst_handle* h, const float* ro, const float* rd, int64_t n
     DST_CUDA_TRY(h, cudaGetLastError());
     return DST_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free forward trace (dst_forward_static, include/dst.h): the per-call scratch lives in
+// a file-scope device array instead of handle-owned cudaMalloc buffers.
+// ---------------------------------------------------------------------------------------------
+namespace {
+constexpr long long ST_SLOTS = 98304;                        // list entries: rays rounded up to whole 8x4 tiles
+constexpr size_t ST_OFF_CACHE = 0;                                                        // 64 B per surfel
+constexpr size_t ST_OFF_STATE = ST_OFF_CACHE + 64ull * DST_STATIC_MAX_SURFELS;            // 128 B per ray
+constexpr size_t ST_OFF_REQ = ST_OFF_STATE + sizeof(FwdState) * (size_t)DST_STATIC_MAX_RAYS;  // 32 B per ray
+constexpr size_t ST_OFF_LIST = ST_OFF_REQ + sizeof(EnumReq) * (size_t)DST_STATIC_MAX_RAYS;    // 4 B per slot
+constexpr size_t ST_OFF_COUNTS = ST_OFF_LIST + 4ull * ST_SLOTS;                               // round counters
+constexpr size_t ST_BYTES = ST_OFF_COUNTS + 4ull * 2 * (DST_WF_ROUNDS + 2) + 256;
+}
+// In host code this name is only a handle for cudaGetSymbolAddress; kernels get the looked-up device pointer.
+static __device__ __align__(256) unsigned char g_static_scratch[ST_BYTES];
+static unsigned char* g_static_ptr[64] = { nullptr };        // per device, filled on the first call there
+
+extern "C" int dst_forward_static(dst_handle* h, const dst_fwd_args* a, void* stream) {
+    if (!h) return DST_E_ARG;
+    if (!a) return dst_set_error(h, DST_E_ARG, "args is null");
+    cudaStream_t st = (cudaStream_t)stream;
+    int prev = -1;
+    if (cudaGetDevice(&prev) != cudaSuccess) return dst_set_error(h, DST_E_CUDA, "cudaGetDevice failed");
+    if (prev != h->device && cudaSetDevice(h->device) != cudaSuccess) return dst_set_error(h, DST_E_CUDA, "cudaSetDevice(%d) failed", h->device);
+    struct Restore { int prev, cur; ~Restore() { if (prev >= 0 && prev != cur) cudaSetDevice(prev); } } restore{ prev, h->device };
+
+    int rc = dst_check_inputs(h, &a->in);
+    if (rc != DST_OK) return rc;
+    if (!a->out_rgb || !a->out_dpt || !a->out_acc || !a->out_norm || !a->out_dist || !a->out_aux || !a->mid_val)
+        return dst_set_error(h, DST_E_ARG, "a forward output pointer is null");
+    if ((reinterpret_cast<uintptr_t>(a->mid_val) & 15) != 0) return dst_set_error(h, DST_E_ARG, "mid_val must be 16-byte aligned");
+    const long long R = (long long)a->in.H * a->in.W;
+    const bool tiled = a->in.H >= 16;
+    const long long slots = slots_of_grid(a->in.H, a->in.W, tiled);
+    if (a->in.P > DST_STATIC_MAX_SURFELS)
+        return dst_set_error(h, DST_E_ARG, "dst_forward_static handles at most %d surfels per call, got %d (use dst_forward)", DST_STATIC_MAX_SURFELS, a->in.P);
+    if (R > DST_STATIC_MAX_RAYS || slots > ST_SLOTS)
+        return dst_set_error(h, DST_E_ARG, "dst_forward_static handles at most %d rays per call, got %lld (use dst_forward)", DST_STATIC_MAX_RAYS, R);
+    if (h->device < 0 || h->device >= 64) return dst_set_error(h, DST_E_ARG, "device index %d out of range", h->device);
+    // one-time set-up per device, with that device current: the device address of the scratch array
+    if (!g_static_ptr[h->device]) {
+        unsigned char* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_static_scratch);
+        if (e != cudaSuccess || !ptr) {
+            cudaGetLastError();
+            return dst_set_error(h, DST_E_CUDA, "cudaGetSymbolAddress for the static scratch failed: %s", cudaGetErrorString(e));
+        }
+        g_static_ptr[h->device] = ptr;
+    }
+    unsigned char* base = g_static_ptr[h->device];
+
+    FwdParams p;
+    p.a = *a; p.bvh = dst_bvh_view(h); p.status = h->status; p.tiled = tiled;
+    p.cache = reinterpret_cast<const float4*>(base + ST_OFF_CACHE);
+    p.state = base + ST_OFF_STATE;
+    p.req = reinterpret_cast<EnumReq*>(base + ST_OFF_REQ);
+    p.kbuf = nullptr; p.kcnt = nullptr;                          // only the per-ray kernel runs: no round buffers
+    p.list[0] = reinterpret_cast<int*>(base + ST_OFF_LIST); p.list[1] = p.list[0];
+    p.counts = reinterpret_cast<int*>(base + ST_OFF_COUNTS);
+    p.rounds = 0; p.min_count = 1;
+    // the array keeps the previous call's contents: the round counters must start at zero, everything else is rewritten
+    DST_CUDA_TRY(h, cudaMemsetAsync(p.counts, 0, 4 * 2 * (DST_WF_ROUNDS + 2), st));
+    if (a->training && a->a_weights) DST_CUDA_TRY(h, cudaMemsetAsync(a->a_weights, 0, 4 * (size_t)a->in.P, st));
+    k_prepare_cache<<<(a->in.P + 255) / 256, 256, 0, st>>>(a->in.P, a->in.means3D, a->in.scales, a->in.rotations, a->in.opacities,
+                                                             reinterpret_cast<float4*>(base + ST_OFF_CACHE));
+    k_fwd_init<<<(unsigned int)((slots + 255) / 256), 256, 0, st>>>(p, slots);
+    const bool diag = a->hit_log || a->hit_cnt || a->counters;
+    const int g_tail = dst_wavefront_grid(h, slots, TAIL_THREADS, 8);
+    if (diag) k_fwd_tail<false, true><<<g_tail, TAIL_THREADS, 0, st>>>(p);
+    else k_fwd_tail<false, false><<<g_tail, TAIL_THREADS, 0, st>>>(p);
+    DST_CUDA_TRY(h, cudaGetLastError());
+    return DST_OK;
+}

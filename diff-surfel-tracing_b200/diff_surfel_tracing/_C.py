@@ -59,6 +59,7 @@ def lib():
         l.dst_build.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]
         l.dst_forward.argtypes = [C.c_void_p, C.POINTER(_FwdArgs), C.c_void_p]
         l.dst_backward.argtypes = [C.c_void_p, C.POINTER(_BwdArgs), C.c_void_p]
+        l.dst_forward_static.argtypes = [C.c_void_p, C.POINTER(_FwdArgs), C.c_void_p]
         l.dst_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), C.c_void_p]
         l.dst_bvh_info.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
         l.dst_debug_knearest.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
@@ -321,3 +322,32 @@ def debug_quad_frames(state):
     out = torch.zeros((info["surfels"], 12), dtype=torch.float32, device=f"cuda:{state.device}")
     _check(state, lib().dst_debug_quad_frames(state.handle, out.data_ptr(), _stream()))
     return out
+
+
+STATIC_MAX_SURFELS = 65536
+STATIC_MAX_RAYS = 65536
+
+
+def trace_surfels_static(state, training, start_from_first, ray_o, ray_d, vertices, background, means3D, shs, degree,
+                         colors_precomp, others_precomp, opacities, scales, scale_modifier, rotations,
+                         max_trace_depth, specular_threshold):
+    """Forward trace through dst_forward_static: same outputs as trace_surfels, but the library call
+    allocates nothing (its scratch is a fixed array inside the library, at most STATIC_MAX_SURFELS
+    surfels and STATIC_MAX_RAYS rays per call). For callers that may not allocate device memory at
+    the point of the call, e.g. under a memory pool that owns the whole device or inside a loop
+    that cannot take an allocation's synchronisation; the output tensors here are still allocated
+    by torch before the call.
+    Concurrent calls on one device share the array and must be serialised."""
+    i, keep = _inputs(state, start_from_first, ray_o, ray_d, vertices, background, means3D, shs, degree, colors_precomp,
+                      others_precomp, opacities, scales, scale_modifier, rotations, max_trace_depth, specular_threshold)
+    H, W, P = i.H, i.W, i.P
+    f32 = dict(dtype=torch.float32, device=means3D.device)
+    outs = [torch.empty((H, W, c), **f32) for c in (NUM_CHANNELS, 1, 1, 3, 3, AUX_CHANNELS, i.mid_stride)]
+    a_weights = torch.empty((P, 1), **f32) if training else None
+    a = _FwdArgs()
+    a.inp = i
+    a.training = int(bool(training))
+    (a.out_rgb, a.out_dpt, a.out_acc, a.out_norm, a.out_dist, a.out_aux, a.mid_val) = [t.data_ptr() for t in outs]
+    a.a_weights = _ptr(a_weights)
+    _check(state, lib().dst_forward_static(state.handle, C.byref(a), _stream()))
+    return (*outs, a_weights)

@@ -120,6 +120,30 @@ int dst_forward(dst_handle* h, const dst_fwd_args* args, void* stream);
 /* Backward trace (trace_surfels.cpp:307-464 + optix_tracer/backward.cu). */
 int dst_backward(dst_handle* h, const dst_bwd_args* args, void* stream);
 
+/* Forward trace that allocates nothing. It has no counterpart in the reference.
+ *
+ * dst_forward grows handle-owned scratch buffers with cudaMalloc whenever a call is larger than
+ * any before it. Some callers must not do that: a host application that has given all device
+ * memory to its own pool and forbids driver allocations, a plug-in that only ever receives
+ * buffers lent by its host, a latency-bound render or control loop that cannot afford the
+ * device-wide synchronisation a driver allocation implies.
+ * For them this variant keeps its scratch (per-surfel shading records, per-ray state, the ray
+ * list) in a fixed array that is part of the loaded library image: about 15 MB of device memory
+ * per GPU that loads the library, held until the process exits. Limits: at most
+ * DST_STATIC_MAX_SURFELS surfels and DST_STATIC_MAX_RAYS rays per call (a larger call is
+ * rejected with DST_E_ARG and an explanatory message; nothing runs). The hierarchy must have been
+ * built before with dst_build on the same handle (that call does allocate). Results are those
+ * of dst_forward on the same arguments.
+ *
+ * The first call on each device looks up the array's device address (a one-time set-up that
+ * should happen before any stream capture begins); later calls only enqueue kernels and
+ * memsets on `stream`. All calls on one device share the one array and it keeps the last call's
+ * contents, so two calls whose GPU work overlaps (different streams, or different handles, on the
+ * same device) race: serialise them. */
+#define DST_STATIC_MAX_SURFELS 65536
+#define DST_STATIC_MAX_RAYS    65536
+int dst_forward_static(dst_handle* h, const dst_fwd_args* args, void* stream);
+
 /* Synchronises `stream`, returns and clears the device status word (DST_STATUS_* bits). */
 int dst_status(dst_handle* h, uint32_t* flags, void* stream);
 
