@@ -324,8 +324,15 @@ def main():
     dom = "backward" if bwd_ms >= fwd_ms else "forward"
     dom_bytes, dom_ms = (bytes_b, bwd_ms) if dom == "backward" else (bytes_f, fwd_ms)
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9 if dom_ms > 0 else 0.0
-    roofline = {"bound": "hbm", "kernel": f"k_{dom}", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "peak_source": peak_src, "algorithmic_bytes_per_launch": int(dom_bytes),
+    # DRAM bytes of one trace sequence from the ncu launch list (profiles/launch_list_config3_step.md: quarter of the
+    # rays, per-ray part scaled to the ray count, per-surfel part kept); only quoted for the workload it was measured on
+    traffic = None
+    if args.config == 3 and P == 3_000_000:
+        per_ray_q, per_surfel = (2.96e9 - 0.6e9, 0.6e9) if dom == "forward" else (3.91e9 - 1.0e9, 1.0e9)
+        traffic = int(per_ray_q * R / 518400 + per_surfel)
+    roofline = {"bound": "hbm", "kernel": f"{dom} trace sequence (k_enum gather rounds + k_{'bwd' if dom == 'backward' else 'fwd'}_shade + tail)",
+                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": traffic, "peak_source": peak_src, "algorithmic_bytes_per_launch": int(dom_bytes),
                 "kernel_ms": {"forward": fwd_ms, "backward": bwd_ms},
                 "other_kernel": {"algorithmic_bytes_per_launch": int(bytes_f if dom == "backward" else bytes_b),
                                  "achieved": (bytes_f if dom == "backward" else bytes_b) / ((fwd_ms if dom == "backward" else bwd_ms) * 1e-3) / 1e9}}
