@@ -224,7 +224,8 @@ def main():
         return _C.trace_surfels_backward(st, w["start_from_first"], wc["ray_o"], wc["ray_d"], wc["v"], wc["bg"], wc["means3D"], shs,
                                          w["sh_degree"], cols, oth, wc["opacities"], wc["scales"], 1.0, wc["rotations"], e, e, e, e,
                                          False, False, w["max_trace_depth"], w["specular_threshold"],
-                                         f[0], f[1], f[2], f[3], f[4], f[5], f[6], ones, z1, z1, z3, z1, z2, _diag=diag)
+                                         f[0], f[1], f[2], f[3], f[4], f[5], f[6], ones, z1, z1, z3, z1, z2, _diag=diag,
+                                         _forward_serial=st.last_forward_serial)
 
     def step():
         f = fwd()

@@ -61,6 +61,7 @@ int dst_create(int device, dst_handle** out) {
     memset(h, 0, sizeof(*h));
     h->device = device;
     h->wf_min_rays = 1 << 17;
+    h->log_enabled = 1;
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete h; dst_global_error("dst_create: cudaGetDeviceProperties failed"); return DST_E_CUDA; }
     h->sm_count = prop.multiProcessorCount;
@@ -82,6 +83,7 @@ int dst_destroy(dst_handle* h) {
     cudaFree(h->node_parent); cudaFree(h->node_first); cudaFree(h->node_count); cudaFree(h->child_cost);
     cudaFree(h->keys); cudaFree(h->keys_alt); cudaFree(h->vals); cudaFree(h->vals_alt); cudaFree(h->block_hist);
     cudaFree(h->header); cudaFree(h->status); cudaFree(h->cache); cudaFree(h->arena);
+    cudaFree(h->log_keys); cudaFree(h->log_hdr); cudaFree(h->log_count); cudaFree(h->log_seg_head); cudaFree(h->log_ray_ok);
     cudaFree(h->wf_state); cudaFree(h->wf_req); cudaFree(h->wf_kbuf); cudaFree(h->wf_kcnt); cudaFree(h->wf_list[0]); cudaFree(h->wf_list[1]); cudaFree(h->wf_counts);
     for (int k = 0; k < 3; k++) {
         if (h->ev[k]) { for (int i = 0; i < 2 * DST_PROF_SLOTS; i++) cudaEventDestroy(h->ev[k][i]); delete[] h->ev[k]; }
@@ -101,6 +103,7 @@ int dst_build(dst_handle* h, const float* vertices, int64_t n_vertices, const in
         return dst_set_error(h, DST_E_ARG, "triangles must hold 2 per surfel: %lld triangles for %lld vertices", (long long)n_triangles, (long long)n_vertices);
     DeviceGuard g(h->device);
     if (!g.ok) return dst_set_error(h, DST_E_CUDA, "cudaSetDevice(%d) failed", h->device);
+    h->log_serial = 0;      // the logged chunks refer to the hierarchy that is about to change
     return dst_bvh_build_impl(h, vertices, n_vertices / 4, rebuild, (cudaStream_t)stream);
 }
 
@@ -151,8 +154,15 @@ int dst_set_option(dst_handle* h, int option, int64_t value) {
     if (!h) return DST_E_ARG;
     switch (option) {
         case DST_OPT_WAVEFRONT_MIN_RAYS: h->wf_min_rays = value < 0 ? 0 : value; return DST_OK;
+        case DST_OPT_CHUNK_LOG: h->log_enabled = value != 0; if (!h->log_enabled) h->log_serial = 0; return DST_OK;
         default: return dst_set_error(h, DST_E_ARG, "unknown option %d", option);
     }
+}
+
+int dst_forward_serial(const dst_handle* h, unsigned long long* serial) {
+    if (!h || !serial) return DST_E_ARG;
+    *serial = h->log_serial;
+    return DST_OK;
 }
 
 int dst_profile_enable(dst_handle* h, int on) {

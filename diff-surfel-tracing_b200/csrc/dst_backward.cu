@@ -30,6 +30,9 @@ struct BwdParams {
     int* counts;
     int min_count;
     int rounds;
+    // chunk log of the matching forward call (null: not available)
+    const unsigned long long* log_keys; const int2* log_hdr; const int* log_seg_head; const unsigned char* log_ray_ok;
+    int log_seg_stride;
 };
 
 struct __align__(16) BwdState {
@@ -476,6 +479,52 @@ __global__ void __launch_bounds__(BWD_THREADS) k_bwd_tail(const __grid_constant_
     }
 }
 
+__device__ __forceinline__ void bwd_flush_counters(unsigned long long* counters, const TraceCounters& tc) {
+    if (!counters) return;
+    if (tc.segs) atomicAdd(counters + 0, tc.segs);
+    if (tc.enums) atomicAdd(counters + 1, tc.enums);
+    if (tc.nodes) atomicAdd(counters + 2, tc.nodes);
+    if (tc.quads) atomicAdd(counters + 3, tc.quads);
+    if (tc.evals) atomicAdd(counters + 4, tc.evals);
+    if (tc.contribs) atomicAdd(counters + 5, tc.contribs);
+}
+
+// Backward over the chunk log of the matching forward call: every ray re-composites the chunks the
+// forward composited (chained per segment), so no hierarchy walk is needed; one thread per ray, all
+// segments. Rays whose log is incomplete (log full during the forward) are initialised and queued
+// for k_bwd_tail, which re-traces them.
+template <bool DIAG>
+__global__ void __launch_bounds__(BWD_THREADS) k_bwd_logged(const __grid_constant__ BwdParams p, long long slots) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int ray = i < slots ? ray_of_slot(i, p.a.in.H, p.a.in.W, p.tiled != 0) : -1;
+    TraceCounters tc = { 0, 0, 0, 0, 0, 0 };
+    bool requeue = false;
+    if (ray >= 0) {
+        BwdState s;
+        if (bwd_init_state(p, ray, s)) {
+            if (!p.log_ray_ok[ray]) {
+                bwd_store_state(p.state, ray, s);
+                EnumReq q;
+                bwd_request(s, q);
+                p.req[ray] = q;
+                requeue = true;
+            } else {
+                const int* heads = p.log_seg_head + (size_t)ray * p.log_seg_stride;
+                int idx = heads[s.seg];
+                for (;;) {
+                    if (idx < 0) { atomicOr(p.status, DST_STATUS_LOG_MISMATCH); break; }
+                    const int2 hdr = __ldg(p.log_hdr + idx);
+                    if (DIAG) tc.enums++;
+                    if (!bwd_shade<DIAG, 1>(p, ray, s, p.log_keys + (size_t)idx * DST_CHUNK, hdr.y, tc)) break;
+                    idx = (s.chunk == 0) ? heads[s.seg] : hdr.x;      // chunk == 0: an earlier segment has begun
+                }
+            }
+        }
+    }
+    append_alive(requeue, ray, p.list[0], p.counts);
+    if (DIAG) bwd_flush_counters(p.a.counters, tc);
+}
+
 // arena rows -> the caller's gradient tensors
 __global__ void __launch_bounds__(256) k_unpack(int P, const float* __restrict__ arena, float* __restrict__ d_rot, float* __restrict__ d_mean,
                                                 float* __restrict__ d_opac, float* __restrict__ d_g3d, float* __restrict__ d_scale,
@@ -529,11 +578,32 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
     if (rc != DST_OK) return rc;
     p.state = h->wf_state; p.req = static_cast<EnumReq*>(h->wf_req); p.kbuf = h->wf_kbuf; p.kcnt = h->wf_kcnt;
     p.list[0] = h->wf_list[0]; p.list[1] = h->wf_list[1]; p.counts = h->wf_counts;
+    const bool diag = a->counters != nullptr;
+    const bool use_log = a->forward_serial != 0 && a->forward_serial == h->log_serial && h->log_H == a->in.H && h->log_W == a->in.W &&
+                         h->log_depth == a->in.max_trace_depth;
+    p.log_keys = h->log_keys; p.log_hdr = h->log_hdr; p.log_seg_head = h->log_seg_head; p.log_ray_ok = h->log_ray_ok;
+    p.log_seg_stride = a->in.max_trace_depth + 1;
+    DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 2 * (DST_WF_ROUNDS + 2), st));
+    if (use_log) {
+        // the forward kept its chunks: re-composite them, re-trace only rays the log could not hold
+        p.rounds = 0; p.min_count = 1;
+        dst_prof_mark(h, 2, 0, st);
+        const unsigned int blocks = (unsigned int)((slots + BWD_THREADS - 1) / BWD_THREADS);
+        if (diag) k_bwd_logged<true><<<blocks, BWD_THREADS, 0, st>>>(p, slots);
+        else k_bwd_logged<false><<<blocks, BWD_THREADS, 0, st>>>(p, slots);
+        const int g_tail = dst_wavefront_grid(h, 65536, BWD_THREADS, 4);
+        if (diag) k_bwd_tail<true><<<g_tail, BWD_THREADS, 0, st>>>(p);
+        else k_bwd_tail<false><<<g_tail, BWD_THREADS, 0, st>>>(p);
+        dst_prof_mark(h, 2, 1, st);
+        DST_CUDA_TRY(h, cudaGetLastError());
+        k_unpack<<<(unsigned int)((P + 255) / 256), 256, 0, st>>>((int)P, h->arena, a->dL_drotations, a->dL_dmeans3D, a->dL_dopacities,
+                                                                  a->dL_dgrads3D, a->dL_dscales, a->dL_dothers, a->dL_dcolors);
+        DST_CUDA_TRY(h, cudaGetLastError());
+        return DST_OK;
+    }
     const bool wave = slots >= h->wf_min_rays;
     p.rounds = wave ? DST_WF_ROUNDS : 0;
     p.min_count = wave ? (int)(slots / 64 > 4096 ? slots / 64 : 4096) : 1;
-    const bool diag = a->counters != nullptr;
-    DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 2 * (DST_WF_ROUNDS + 2), st));
     dst_prof_mark(h, 2, 0, st);
     k_bwd_init<<<(unsigned int)((slots + 255) / 256), 256, 0, st>>>(p, slots);
     const int g_enum = dst_wavefront_grid(h, slots, ENUM_THREADS, 10), g_shade = dst_wavefront_grid(h, slots, BWD_THREADS, 4);

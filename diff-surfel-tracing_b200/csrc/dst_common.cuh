@@ -78,6 +78,15 @@ struct dst_handle {
     void* wf_state; size_t wf_state_bytes; void* wf_req; unsigned long long* wf_kbuf; int* wf_kcnt; int* wf_list[2]; int* wf_counts;
     long long wf_cap;
     long long wf_min_rays;        // launches with fewer rays skip the wavefront rounds
+    // chunk log: the 16-hit chunks every ray composited in the last training forward, chained per ray and segment,
+    // so that the backward re-composites them without walking the hierarchy again
+    unsigned long long* log_keys; int2* log_hdr; int* log_count; int* log_seg_head; unsigned char* log_ray_ok;
+    long long log_cap;            // records
+    long long log_rays_cap; int log_seg_stride_cap;
+    unsigned long long log_serial;      // serial of the forward call the log belongs to (0 = none)
+    unsigned long long serial_counter;
+    int log_H, log_W, log_depth;
+    int log_enabled;
     // optional event timing (dst_profile_enable)
     int profiling;
     cudaEvent_t* ev[3];           // per kind: 2 * DST_PROF_SLOTS events (start, stop pairs)
@@ -109,6 +118,7 @@ int dst_knearest_impl(dst_handle* h, const float* ro, const float* rd, int64_t n
 int dst_prepare_cache(dst_handle* h, const dst_trace_inputs* in, cudaStream_t st);
 int dst_export_frames_impl(dst_handle* h, float* out, cudaStream_t st);
 int dst_ensure_wavefront(dst_handle* h, long long slots, size_t state_bytes);
+int dst_ensure_chunk_log(dst_handle* h, long long rays, int segs);
 int dst_wavefront_grid(const dst_handle* h, long long slots, int threads, int per_sm);
 
 #ifdef __CUDACC__

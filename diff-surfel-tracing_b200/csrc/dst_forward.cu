@@ -30,6 +30,9 @@ struct FwdParams {
     int* counts;
     int min_count;
     int rounds;
+    // chunk log (null log_keys: disabled)
+    unsigned long long* log_keys; int2* log_hdr; int* log_count; int* log_seg_head; unsigned char* log_ray_ok;
+    int log_cap, log_seg_stride;
 };
 
 struct __align__(16) FwdState {
@@ -40,7 +43,8 @@ struct __align__(16) FwdState {
     float O0, O1, s_prod, rgb0;
     float rgb1, rgb2; int last_gidx, contributor;
     int bounce, chunk, hit_count, pad0;
-    float pad1[4];
+    int log_prev;       // last chunk-log record of the current segment, -1 at a segment start
+    float pad1[3];
 };
 static_assert(sizeof(FwdState) == 128, "ray state is one 128-byte record");
 
@@ -76,7 +80,7 @@ __global__ void __launch_bounds__(256) k_prepare_cache(int P, const float* __res
 __device__ __forceinline__ void fwd_begin_segment(FwdState& s) {
     s.offset = 0.f; s.dpt = 0.f; s.T_prev = 1.f;
     s.C0 = s.C1 = s.C2 = 0.f; s.D = 0.f; s.Nx = s.Ny = s.Nz = 0.f; s.O0 = s.O1 = 0.f;
-    s.last_gidx = -1; s.contributor = 0; s.chunk = 0;
+    s.last_gidx = -1; s.contributor = 0; s.chunk = 0; s.log_prev = -1;
 }
 
 __device__ __forceinline__ void fwd_init_state(const FwdParams& p, int ray, FwdState& s) {
@@ -109,6 +113,19 @@ __device__ __forceinline__ bool fwd_shade(const FwdParams& p, int ray, FwdState&
     float sb[16];
     if (use_sh) sh_basis(in.sh_degree, s.sdx, s.sdy, s.sdz, sb);
     if (DIAG) { if (s.chunk == 0) tc.segs++; }
+    if (p.log_keys) {
+        // keep this chunk for the backward: one record per chunk, chained per segment
+        const int idx = atomicAdd(p.log_count, 1);
+        if (idx < p.log_cap) {
+            ulonglong2* dst = reinterpret_cast<ulonglong2*>(p.log_keys + (size_t)idx * DST_CHUNK);
+#pragma unroll
+            for (int k = 0; k < DST_CHUNK / 2; k++) if (2 * k < cnt) dst[k] = make_ulonglong2(kb[(2 * k) * KS], kb[(2 * k + 1) * KS]);
+            p.log_hdr[idx] = make_int2(-1, cnt);
+            if (s.log_prev < 0) p.log_seg_head[(size_t)ray * p.log_seg_stride + s.bounce] = idx;
+            else p.log_hdr[s.log_prev].x = idx;
+            s.log_prev = idx;
+        } else p.log_ray_ok[ray] = 0;       // log full: this ray's backward walks the hierarchy again
+    }
 
     float T_next = 1.0f;
     bool stop = false;
@@ -208,13 +225,13 @@ __device__ __forceinline__ void load_state(const void* base, int ray, FwdState& 
     const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const FwdState*>(base) + ray);
     float4* dst = reinterpret_cast<float4*>(&s);
 #pragma unroll
-    for (int i = 0; i < 7; i++) dst[i] = src[i];
+    for (int i = 0; i < 8; i++) dst[i] = src[i];
 }
 __device__ __forceinline__ void store_state(void* base, int ray, const FwdState& s) {
     float4* dst = reinterpret_cast<float4*>(reinterpret_cast<FwdState*>(base) + ray);
     const float4* src = reinterpret_cast<const float4*>(&s);
 #pragma unroll
-    for (int i = 0; i < 7; i++) dst[i] = src[i];
+    for (int i = 0; i < 8; i++) dst[i] = src[i];
 }
 
 __device__ __forceinline__ void flush_counters(unsigned long long* counters, const TraceCounters& tc) {
@@ -237,6 +254,10 @@ __global__ void __launch_bounds__(256) k_fwd_init(const __grid_constant__ FwdPar
     if (ray < 0) return;
     FwdState s;
     fwd_init_state(p, ray, s);
+    if (p.log_keys) {
+        p.log_ray_ok[ray] = 1;
+        for (int k = 0; k < p.log_seg_stride; k++) p.log_seg_head[(size_t)ray * p.log_seg_stride + k] = -1;
+    }
     store_state(p.state, ray, s);
     EnumReq q;
     fwd_request(s, q);
@@ -372,6 +393,30 @@ int dst_ensure_wavefront(dst_handle* h, long long slots, size_t state_bytes) {
     return DST_OK;
 }
 
+// chunk-log buffers for `rays` rays of up to `segs` segments (grow-only)
+int dst_ensure_chunk_log(dst_handle* h, long long rays, int segs) {
+    long long want = rays * 12 + 4096;
+    if (want > (48ll << 20)) want = 48ll << 20;           // 48 Mi records = 6.5 GB; rays beyond the log re-trace
+    if (want > h->log_cap) {
+        cudaFree(h->log_keys); cudaFree(h->log_hdr); h->log_keys = nullptr; h->log_hdr = nullptr; h->log_cap = 0;
+        cudaError_t e = cudaMalloc(&h->log_keys, 8 * DST_CHUNK * (size_t)want);
+        if (e == cudaSuccess) e = cudaMalloc(&h->log_hdr, sizeof(int2) * (size_t)want);
+        if (e != cudaSuccess) { cudaGetLastError(); return dst_set_error(h, DST_E_NOMEM, "chunk log allocation failed: %s", cudaGetErrorString(e)); }
+        h->log_cap = want;
+    }
+    if (!h->log_count && cudaMalloc(&h->log_count, 4) != cudaSuccess) { cudaGetLastError(); return dst_set_error(h, DST_E_NOMEM, "chunk log allocation failed"); }
+    if (rays > h->log_rays_cap || segs > h->log_seg_stride_cap) {
+        cudaFree(h->log_seg_head); cudaFree(h->log_ray_ok); h->log_seg_head = nullptr; h->log_ray_ok = nullptr;
+        const long long rc = rays > h->log_rays_cap ? rays + rays / 16 + 1024 : h->log_rays_cap;
+        const int sc = segs > h->log_seg_stride_cap ? segs : h->log_seg_stride_cap;
+        cudaError_t e = cudaMalloc(&h->log_seg_head, 4 * (size_t)rc * sc);
+        if (e == cudaSuccess) e = cudaMalloc(&h->log_ray_ok, (size_t)rc);
+        if (e != cudaSuccess) { cudaGetLastError(); h->log_rays_cap = 0; h->log_seg_stride_cap = 0; return dst_set_error(h, DST_E_NOMEM, "chunk log allocation failed: %s", cudaGetErrorString(e)); }
+        h->log_rays_cap = rc; h->log_seg_stride_cap = sc;
+    }
+    return DST_OK;
+}
+
 int dst_wavefront_grid(const dst_handle* h, long long slots, int threads, int per_sm) {
     const long long want = (slots + threads - 1) / threads;
     const long long cap = (long long)h->sm_count * per_sm;
@@ -396,6 +441,19 @@ int dst_forward_impl(dst_handle* h, const dst_fwd_args* a, cudaStream_t st) {
     if (a->training && a->a_weights) DST_CUDA_TRY(h, cudaMemsetAsync(a->a_weights, 0, 4 * (size_t)a->in.P, st));
     p.state = h->wf_state; p.req = static_cast<EnumReq*>(h->wf_req); p.kbuf = h->wf_kbuf; p.kcnt = h->wf_kcnt;
     p.list[0] = h->wf_list[0]; p.list[1] = h->wf_list[1]; p.counts = h->wf_counts;
+    // chunk log for the backward (training calls only)
+    p.log_keys = nullptr; p.log_hdr = nullptr; p.log_count = nullptr; p.log_seg_head = nullptr; p.log_ray_ok = nullptr;
+    p.log_cap = 0; p.log_seg_stride = a->in.max_trace_depth + 1;
+    h->log_serial = 0;
+    if (a->training && h->log_enabled) {
+        rc = dst_ensure_chunk_log(h, (long long)a->in.H * a->in.W, a->in.max_trace_depth + 1);
+        if (rc != DST_OK) return rc;
+        p.log_keys = h->log_keys; p.log_hdr = h->log_hdr; p.log_count = h->log_count; p.log_seg_head = h->log_seg_head;
+        p.log_ray_ok = h->log_ray_ok; p.log_cap = (int)h->log_cap;
+        DST_CUDA_TRY(h, cudaMemsetAsync(h->log_count, 0, 4, st));
+        h->log_serial = ++h->serial_counter;
+        h->log_H = a->in.H; h->log_W = a->in.W; h->log_depth = a->in.max_trace_depth;
+    }
     // small launches go straight to the per-ray kernel; large ones run wavefront rounds until few rays are left
     const bool wave = slots >= h->wf_min_rays;
     p.rounds = wave ? DST_WF_ROUNDS : 0;
@@ -493,6 +551,8 @@ extern "C" int dst_forward_static(dst_handle* h, const dst_fwd_args* a, void* st
     p.list[0] = reinterpret_cast<int*>(base + ST_OFF_LIST); p.list[1] = p.list[0];
     p.counts = reinterpret_cast<int*>(base + ST_OFF_COUNTS);
     p.rounds = 0; p.min_count = 1;
+    p.log_keys = nullptr; p.log_hdr = nullptr; p.log_count = nullptr; p.log_seg_head = nullptr; p.log_ray_ok = nullptr;
+    p.log_cap = 0; p.log_seg_stride = 0;
     // the array keeps the previous call's contents: the round counters must start at zero, everything else is rewritten
     DST_CUDA_TRY(h, cudaMemsetAsync(p.counts, 0, 4 * 2 * (DST_WF_ROUNDS + 2), st));
     if (a->training && a->a_weights) DST_CUDA_TRY(h, cudaMemsetAsync(a->a_weights, 0, 4 * (size_t)a->in.P, st));

@@ -38,7 +38,8 @@ class _BwdArgs(C.Structure):
                 + [(n, C.c_void_p) for n in ("out_rgb", "out_dpt", "out_acc", "out_norm", "out_dist", "out_aux", "mid_val",
                                              "dL_drgb", "dL_ddpt", "dL_dacc", "dL_dnorm", "dL_ddist", "dL_daux",
                                              "dL_dray_o", "dL_dray_d", "dL_dmeans3D", "dL_dgrads3D", "dL_dshs", "dL_dcolors",
-                                             "dL_dothers", "dL_dopacities", "dL_dscales", "dL_drotations", "counters")])
+                                             "dL_dothers", "dL_dopacities", "dL_dscales", "dL_drotations", "counters")]
+                + [("forward_serial", C.c_uint64)])
 
 
 _lib = None
@@ -63,6 +64,7 @@ def lib():
         l.dst_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), C.c_void_p]
         l.dst_bvh_info.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
         l.dst_debug_knearest.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+        l.dst_forward_serial.argtypes = [C.c_void_p, C.POINTER(C.c_uint64)]
         l.dst_set_option.argtypes = [C.c_void_p, C.c_int, C.c_int64]
         l.dst_profile_enable.argtypes = [C.c_void_p, C.c_int]
         l.dst_profile_read.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_int32)]
@@ -114,6 +116,7 @@ class OptiXStateWrapper:
             raise RuntimeError(lib().dst_last_error(None).decode())
         self.handle = h
         self._keep = None
+        self.last_forward_serial = 0
         self.grad_bucket = None     # flat buffer holding the per-surfel gradients of the last backward call
 
     def __del__(self):
@@ -134,6 +137,10 @@ class OptiXStateWrapper:
         """Trace calls with at least `n` rays run as rounds of gather / composite kernels over the
         live rays; smaller calls use one thread per ray for the whole path (same results)."""
         _check(self, lib().dst_set_option(self.handle, 1, int(n)))
+
+    def set_chunk_log(self, on):
+        """Keep (default) or drop the per-ray chunk log training forwards leave for the backward (about 1.6 KB per ray)."""
+        _check(self, lib().dst_set_option(self.handle, 2, int(bool(on))))
 
     def profile(self, on=True):
         """Records CUDA events around the build, forward and backward kernels of later calls."""
@@ -238,6 +245,9 @@ def trace_surfels(state, training, start_from_first, ray_o, ray_d, vertices, bac
         _diag["counters"] = torch.zeros((8,), dtype=torch.int64, device=dev)
         a.counters = _diag["counters"].data_ptr()
     _check(state, lib().dst_forward(state.handle, C.byref(a), _stream()))
+    ser = C.c_uint64(0)
+    _check(state, lib().dst_forward_serial(state.handle, C.byref(ser)))
+    state.last_forward_serial = ser.value       # names the chunk log this call left in the handle (0: none)
     return out_rgb, out_dpt, out_acc, out_norm, out_dist, out_aux, mid_val, a_weights
 
 
@@ -245,10 +255,14 @@ def trace_surfels_backward(state, start_from_first, ray_o, ray_d, vertices, back
                            others_precomp, opacities, scales, scale_modifier, rotations, transMat_precomp, viewmatrix,
                            projmatrix, campos, prefiltered, debug, max_trace_depth, specular_threshold,
                            out_rgb, out_dpt, out_acc, out_norm, out_dist, out_aux, mid_val,
-                           dL_drgb, dL_ddpt, dL_dacc, dL_dnorm, dL_ddist, dL_daux, _diag=None):
+                           dL_drgb, dL_ddpt, dL_dacc, dL_dnorm, dL_ddist, dL_daux, _diag=None, _forward_serial=0):
     """trace_surfels.cpp:307-464. Returns the 12 gradients in the reference's order:
     ray_o, ray_d, means3D, grads3D, grads3D_abs (zeros), shs, colors_precomp, others_precomp,
-    opacities, scales, rotations, transMat_precomp (zeros)."""
+    opacities, scales, rotations, transMat_precomp (zeros).
+
+    `_forward_serial`: `state.last_forward_serial` as it was right after the forward call these saved
+    tensors come from; when it still names the handle's chunk log the backward re-composites the logged
+    chunks instead of walking the hierarchy again (same result)."""
     i, keep = _inputs(state, start_from_first, ray_o, ray_d, vertices, background, means3D, shs, degree, colors_precomp,
                       others_precomp, opacities, scales, scale_modifier, rotations, max_trace_depth, specular_threshold)
     H, W, P, M = i.H, i.W, i.P, i.sh_coeffs
@@ -297,6 +311,7 @@ def trace_surfels_backward(state, start_from_first, ray_o, ray_d, vertices, back
     a.dL_dshs = _ptr(g_shs)
     a.dL_dcolors, a.dL_dothers, a.dL_dopacities = g_colors.data_ptr(), g_others.data_ptr(), g_opac.data_ptr()
     a.dL_dscales, a.dL_drotations = g_scales.data_ptr(), g_rot.data_ptr()
+    a.forward_serial = int(_forward_serial or 0)
     if _diag is not None:
         _diag["counters"] = torch.zeros((8,), dtype=torch.int64, device=dev)
         a.counters = _diag["counters"].data_ptr()

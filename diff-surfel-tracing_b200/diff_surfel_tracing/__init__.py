@@ -52,6 +52,7 @@ class _TraceSurfels(torch.autograd.Function):
         ctx.tracer_settings = tracer_settings
         ctx.optix_context = optix_context
         ctx.start_from_first = start_from_first
+        ctx.forward_serial = getattr(optix_context, "last_forward_serial", 0)
         ctx.save_for_backward(ray_o, ray_d, vertices, means3D, shs, colors_precomp, others_precomp, opacities, scales,
                               rotations, cov3Ds_precomp, out_rgb, out_dpt, out_acc, out_norm, out_dist, out_aux, mid_val)
         acc_wet = a_weights if a_weights is not None else torch.zeros_like(means3D[:, 0])
@@ -71,13 +72,13 @@ class _TraceSurfels(torch.autograd.Function):
         if s.debug:
             cpu_args = cpu_deep_copy_tuple(args[1:])
             try:
-                grads = _C.trace_surfels_backward(*args)
+                grads = _C.trace_surfels_backward(*args, _forward_serial=ctx.forward_serial)
             except Exception as ex:
                 torch.save(cpu_args, "snapshot_bw.dump")
                 print("\nAn error occured in backward. Writing snapshot_bw.dump for debugging.\n")
                 raise ex
         else:
-            grads = _C.trace_surfels_backward(*args)
+            grads = _C.trace_surfels_backward(*args, _forward_serial=ctx.forward_serial)
         (grad_ray_o, grad_ray_d, grad_means3D, grad_grads3D, grad_grads3D_abs, grad_shs, grad_colors_precomp,
          grad_others_precomp, grad_opacities, grad_scales, grad_rotations, grad_cov3Ds_precomp) = grads
 

@@ -34,6 +34,7 @@ extern "C" {
 /* bits of the device status word returned by dst_status */
 #define DST_STATUS_STACK_OVERFLOW  1u   /* traversal stack exhausted: some hits may be missing */
 #define DST_STATUS_CHUNK_LIMIT     2u   /* a ray hit the bound on 16-hit enumerations          */
+#define DST_STATUS_LOG_MISMATCH    8u   /* the chunk log ended before the backward of a ray did */
 
 #define DST_MID_CHANNELS 16             /* per-bounce record, optix_tracer/config.h:7-15       */
 #define DST_CHUNK 16                    /* hits gathered per enumeration, config.h:20          */
@@ -113,12 +114,21 @@ typedef struct dst_bwd_args {
     float *dL_dscales;            /* (P, 2)                                                       */
     float *dL_drotations;         /* (P, 4)                                                       */
     unsigned long long *counters; /* as in dst_fwd_args, or NULL                                  */
+    unsigned long long forward_serial; /* value of dst_forward_serial right after the forward call whose saved state
+                                     this is, or 0. When it still names the chunk log the handle holds, the backward
+                                     re-composites the logged chunks instead of walking the hierarchy again
+                                     (same result); otherwise it re-traces.                        */
 } dst_bwd_args;
 
 /* Forward trace (trace_surfels.cpp:162-304 + optix_tracer/forward.cu). */
 int dst_forward(dst_handle* h, const dst_fwd_args* args, void* stream);
 /* Backward trace (trace_surfels.cpp:307-464 + optix_tracer/backward.cu). */
 int dst_backward(dst_handle* h, const dst_bwd_args* args, void* stream);
+
+/* Serial number of the last dst_forward call with training != 0 on this handle (0 if none, or if a
+ * later dst_build invalidated it). Such a call keeps, in handle-owned memory, the 16-hit chunks
+ * every ray composited; dst_backward uses them when dst_bwd_args.forward_serial matches. */
+int dst_forward_serial(const dst_handle* h, unsigned long long* serial);
 
 /* Forward trace that allocates nothing. It has no counterpart in the reference.
  *
@@ -154,6 +164,8 @@ int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t*
  * separate gather / composite kernels over the live rays (default 131072); smaller calls use one
  * thread per ray for the whole path. Results do not depend on the setting. */
 #define DST_OPT_WAVEFRONT_MIN_RAYS 1
+/* DST_OPT_CHUNK_LOG: 1 (default) keeps the chunk log of training forwards for the backward, 0 disables it. */
+#define DST_OPT_CHUNK_LOG 2
 int dst_set_option(dst_handle* h, int option, int64_t value);
 
 /* Timing of the main kernels with CUDA events on the launching stream. While enabled, every

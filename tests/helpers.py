@@ -42,7 +42,7 @@ def cuda_forward(_C, state, wc, training=True, diag=None):
     return dict(zip(FWD_KEYS, out))
 
 
-def cuda_backward(_C, state, wc, fwd, grads, diag=None):
+def cuda_backward(_C, state, wc, fwd, grads, diag=None, serial=0):
     dev = wc["means3D"].device
     e = empty(dev)
     H, W = wc["ray_o"].shape[:2]
@@ -54,7 +54,8 @@ def cuda_backward(_C, state, wc, fwd, grads, diag=None):
                                     wc["opacities"], wc["scales"], 1.0, wc["rotations"], e, e, e, e, False, False,
                                     wc["max_trace_depth"], wc["specular_threshold"],
                                     fwd["rgb"], fwd["dpt"], fwd["acc"], fwd["norm"], fwd["dist"], fwd["aux"], fwd["mid"],
-                                    g("rgb", 3), g("dpt", 1), g("acc", 1), g("norm", 3), g("dist", 1), g("aux", 2), _diag=diag)
+                                    g("rgb", 3), g("dpt", 1), g("acc", 1), g("norm", 3), g("dist", 1), g("aux", 2), _diag=diag,
+                                    _forward_serial=serial)
     names = ("ray_o", "ray_d", "means3D", "grads3D", "grads3D_abs", "shs", "colors", "others", "opacities", "scales", "rotations", "trans")
     return dict(zip(names, out))
 

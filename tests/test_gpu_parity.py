@@ -106,21 +106,28 @@ def test_forward_parity(C, oracle_mod, config, wave):
     assert c[5] == want["stats"][3] and c[4] == want["stats"][2] and c[1] == want["stats"][0]
 
 
-@pytest.mark.parametrize("wave", [False, True], ids=["per-ray", "wavefront"])
+@pytest.mark.parametrize("mode", ["per-ray", "wavefront", "chunk-log"])
 @pytest.mark.parametrize("config", [1, 2, 3, 4, 5])
-def test_backward_parity(C, oracle_mod, config, wave):
-    w, wc, st, got, want, diag, orc = _forward_pair(C, oracle_mod, config, hit_cap=0, wave=wave)
+def test_backward_parity(C, oracle_mod, config, mode):
+    """Three routes to the same gradients: re-trace one thread per ray, re-trace in wavefront rounds,
+    and re-compositing the chunks the forward call logged (no hierarchy walk)."""
+    w, wc, st, got, want, diag, orc = _forward_pair(C, oracle_mod, config, hit_cap=0, wave=(mode == "wavefront"))
+    serial = st.last_forward_serial if mode == "chunk-log" else 0
+    assert st.last_forward_serial != 0
     gen = torch.Generator().manual_seed(100 + config)
     H, W = w["ray_o"].shape[:2]
     # unit upstream gradients on the outputs the configuration names, plus a seeded random run on all of them
-    for mode in ("unit", "random"):
-        if mode == "unit":
+    for upstream in ("unit", "random"):
+        if upstream == "unit":
             up = {k: torch.ones((H, W, 3 if k in ("rgb", "norm") else 2 if k == "aux" else 1)) for k in w["upstream"]}
         else:
             up = {k: torch.randn((H, W, c), generator=gen) for k, c in (("rgb", 3), ("dpt", 1), ("acc", 1), ("norm", 3), ("aux", 2))}
-        gb = hp.cuda_backward(C, st, wc, got, {k: v.cuda() for k, v in up.items()})
+        dg = {}
+        gb = hp.cuda_backward(C, st, wc, got, {k: v.cuda() for k, v in up.items()}, diag=dg, serial=serial)
         torch.cuda.synchronize()
         assert st.status() == 0
+        cb = dg["counters"].cpu().numpy()
+        assert (cb[2] == 0) == (mode == "chunk-log")        # nodes visited: none when the log is used
         ob = orc.backward(w, want, {k: v.numpy() for k, v in up.items()})
         for k in hp.GRAD_KEYS:
             g = gb[k].cpu().numpy().reshape(ob[k].shape)
@@ -132,8 +139,36 @@ def test_backward_parity(C, oracle_mod, config, wave):
             else:
                 o = ob[k]
             e = hp.rel_l2(g, o)
-            assert e <= GRAD_RTOL, f"config {config} {mode} grad {k}: rel L2 {e}"
+            assert e <= GRAD_RTOL, f"config {config} {mode} {upstream} grad {k}: rel L2 {e}"
         assert float(gb["grads3D_abs"].abs().max()) == 0.0 and float(gb["trans"].abs().max()) == 0.0
+
+
+def test_stale_chunk_log_is_not_used(C, oracle_mod):
+    """A backward whose forward is no longer the one the handle's log belongs to must re-trace."""
+    w = hp.reduced_workload(1)
+    wc = hp.to_cuda(w)
+    st = _build(C, wc)
+    f1 = hp.cuda_forward(C, st, wc)
+    s1 = st.last_forward_serial
+    H, W = w["ray_o"].shape[:2]
+    up = {"rgb": torch.ones((H, W, 3), device="cuda")}
+    ref = hp.cuda_backward(C, st, wc, f1, up, serial=0)
+    # a second forward over other rays replaces the log
+    wc2 = dict(wc, ray_o=wc["ray_o"].flip(0).contiguous(), ray_d=wc["ray_d"].flip(0).contiguous())
+    hp.cuda_forward(C, st, wc2)
+    assert st.last_forward_serial != s1
+    dg = {}
+    g = hp.cuda_backward(C, st, wc, f1, up, diag=dg, serial=s1)
+    assert int(dg["counters"][2]) > 0                       # it walked the hierarchy
+    for k in ("means3D", "opacities", "scales", "rotations", "shs"):
+        assert hp.rel_l2(g[k].cpu().numpy(), ref[k].cpu().numpy()) < 1e-5, k
+    # a rebuild invalidates the log as well
+    f3 = hp.cuda_forward(C, st, wc)
+    s3 = st.last_forward_serial
+    C.build_acceleration_structure(st, wc["v"], wc["f"], 1)
+    dg = {}
+    hp.cuda_backward(C, st, wc, f3, up, diag=dg, serial=s3)
+    assert int(dg["counters"][2]) > 0
 
 
 def test_refit_matches_rebuild(C, oracle_mod):
