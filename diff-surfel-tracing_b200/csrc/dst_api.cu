@@ -83,6 +83,8 @@ int dst_destroy(dst_handle* h) {
     cudaFree(h->node_parent); cudaFree(h->node_first); cudaFree(h->node_count); cudaFree(h->child_cost);
     cudaFree(h->keys); cudaFree(h->keys_alt); cudaFree(h->vals); cudaFree(h->vals_alt); cudaFree(h->block_hist);
     cudaFree(h->header); cudaFree(h->status); cudaFree(h->cache); cudaFree(h->arena);
+    if (h->log_needed_host) cudaFreeHost(h->log_needed_host);
+    if (h->log_needed_event) cudaEventDestroy(h->log_needed_event);
     cudaFree(h->log_keys); cudaFree(h->log_hdr); cudaFree(h->log_count); cudaFree(h->log_seg_head); cudaFree(h->log_ray_ok);
     cudaFree(h->wf_state); cudaFree(h->wf_req); cudaFree(h->wf_kbuf); cudaFree(h->wf_kcnt); cudaFree(h->wf_list[0]); cudaFree(h->wf_list[1]); cudaFree(h->wf_counts);
     for (int k = 0; k < 3; k++) {
@@ -154,6 +156,7 @@ int dst_set_option(dst_handle* h, int option, int64_t value) {
     if (!h) return DST_E_ARG;
     switch (option) {
         case DST_OPT_WAVEFRONT_MIN_RAYS: h->wf_min_rays = value < 0 ? 0 : value; return DST_OK;
+        case DST_OPT_CHUNK_LOG_MAX_RECORDS: h->log_max_records = value < 0 ? 0 : value; h->log_serial = 0; return DST_OK;
         case DST_OPT_CHUNK_LOG: h->log_enabled = value != 0; if (!h->log_enabled) h->log_serial = 0; return DST_OK;
         default: return dst_set_error(h, DST_E_ARG, "unknown option %d", option);
     }

@@ -584,28 +584,19 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
     p.log_keys = h->log_keys; p.log_hdr = h->log_hdr; p.log_seg_head = h->log_seg_head; p.log_ray_ok = h->log_ray_ok;
     p.log_seg_stride = a->in.max_trace_depth + 1;
     DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 2 * (DST_WF_ROUNDS + 2), st));
-    if (use_log) {
-        // the forward kept its chunks: re-composite them, re-trace only rays the log could not hold
-        p.rounds = 0; p.min_count = 1;
-        dst_prof_mark(h, 2, 0, st);
-        const unsigned int blocks = (unsigned int)((slots + BWD_THREADS - 1) / BWD_THREADS);
-        if (diag) k_bwd_logged<true><<<blocks, BWD_THREADS, 0, st>>>(p, slots);
-        else k_bwd_logged<false><<<blocks, BWD_THREADS, 0, st>>>(p, slots);
-        const int g_tail = dst_wavefront_grid(h, 65536, BWD_THREADS, 4);
-        if (diag) k_bwd_tail<true><<<g_tail, BWD_THREADS, 0, st>>>(p);
-        else k_bwd_tail<false><<<g_tail, BWD_THREADS, 0, st>>>(p);
-        dst_prof_mark(h, 2, 1, st);
-        DST_CUDA_TRY(h, cudaGetLastError());
-        k_unpack<<<(unsigned int)((P + 255) / 256), 256, 0, st>>>((int)P, h->arena, a->dL_drotations, a->dL_dmeans3D, a->dL_dopacities,
-                                                                  a->dL_dgrads3D, a->dL_dscales, a->dL_dothers, a->dL_dcolors);
-        DST_CUDA_TRY(h, cudaGetLastError());
-        return DST_OK;
-    }
     const bool wave = slots >= h->wf_min_rays;
     p.rounds = wave ? DST_WF_ROUNDS : 0;
     p.min_count = wave ? (int)(slots / 64 > 4096 ? slots / 64 : 4096) : 1;
     dst_prof_mark(h, 2, 0, st);
-    k_bwd_init<<<(unsigned int)((slots + 255) / 256), 256, 0, st>>>(p, slots);
+    if (use_log) {
+        // the forward kept its chunks: re-composite them; rays the log could not hold are queued as round 0 of the
+        // re-trace below (normally none: the rounds then find an empty list and return at once)
+        const unsigned int blocks = (unsigned int)((slots + BWD_THREADS - 1) / BWD_THREADS);
+        if (diag) k_bwd_logged<true><<<blocks, BWD_THREADS, 0, st>>>(p, slots);
+        else k_bwd_logged<false><<<blocks, BWD_THREADS, 0, st>>>(p, slots);
+    } else {
+        k_bwd_init<<<(unsigned int)((slots + 255) / 256), 256, 0, st>>>(p, slots);
+    }
     const int g_enum = dst_wavefront_grid(h, slots, ENUM_THREADS, 10), g_shade = dst_wavefront_grid(h, slots, BWD_THREADS, 4);
     for (int r = 0; r < p.rounds; r++) {
         if (diag) {

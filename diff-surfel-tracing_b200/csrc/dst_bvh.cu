@@ -250,7 +250,9 @@ __global__ void k_single_leaf(BvhNode* nodes, int* leaf_parent, int* node_parent
 // On the way up every node also gets the expected cost of walking its subtree (surface-area
 // heuristic) and decides whether the walk should treat it as ONE run of leaves: where boxes overlap
 // almost completely (large quads crossing each other) descending costs more than testing every quad.
+#ifndef DST_COST_NODE
 #define DST_COST_NODE 1.2f
+#endif
 #define DST_COST_QUAD 1.0f
 __device__ __forceinline__ float box_area(const float* lo, const float* hi) {
     const float dx = hi[0] - lo[0], dy = hi[1] - lo[1], dz = hi[2] - lo[2];

@@ -21,7 +21,9 @@ struct __align__(16) BvhNode {
 };
 #define DST_LEAF_FLAG 0x80000000u
 #define DST_LEAF_POS_BITS 26
-#define DST_LEAF_MAX 16               // most quads in one run
+#ifndef DST_LEAF_MAX
+#define DST_LEAF_MAX 16               // most quads in one run (at most 32: five count bits)
+#endif
 #define DST_LEAF_LINK(first, count) ((int)(DST_LEAF_FLAG | ((unsigned int)((count) - 1) << DST_LEAF_POS_BITS) | (unsigned int)(first)))
 #define DST_LEAF_FIRST(link) ((int)((unsigned int)(link) & ((1u << DST_LEAF_POS_BITS) - 1u)))
 #define DST_LEAF_COUNT(link) ((int)(((unsigned int)(link) >> DST_LEAF_POS_BITS) & 31u) + 1)
@@ -48,6 +50,7 @@ struct SurfelCacheView { const float4* rec; };
 // packed per-surfel gradient rows (16-byte aligned so that 4-float vector reductions apply):
 //   [0..3] rotation  [4..6] mean  [7] opacity  [8..10] grads3D  [11] -  [12..13] scale  [14..15] others  [16..18] colour  [19] -
 #define DST_ARENA_FLOATS 20
+#define DST_LOG_MAX_RECORDS (320ll << 20)     // 136 B each: at most 43.5 GB of chunk log
 
 struct dst_handle {
     int device;
@@ -87,6 +90,8 @@ struct dst_handle {
     unsigned long long serial_counter;
     int log_H, log_W, log_depth;
     int log_enabled;
+    long long log_max_records;    // user limit on the log size (0: only the built-in limit)
+    int* log_needed_host; cudaEvent_t log_needed_event;     // pinned read-back of the record count of the last forward
     // optional event timing (dst_profile_enable)
     int profiling;
     cudaEvent_t* ev[3];           // per kind: 2 * DST_PROF_SLOTS events (start, stop pairs)

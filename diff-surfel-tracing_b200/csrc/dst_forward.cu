@@ -116,7 +116,7 @@ __device__ __forceinline__ bool fwd_shade(const FwdParams& p, int ray, FwdState&
     if (p.log_keys) {
         // keep this chunk for the backward: one record per chunk, chained per segment
         const int idx = atomicAdd(p.log_count, 1);
-        if (idx < p.log_cap) {
+        if (idx >= 0 && idx < p.log_cap) {
             ulonglong2* dst = reinterpret_cast<ulonglong2*>(p.log_keys + (size_t)idx * DST_CHUNK);
 #pragma unroll
             for (int k = 0; k < DST_CHUNK / 2; k++) if (2 * k < cnt) dst[k] = make_ulonglong2(kb[(2 * k) * KS], kb[(2 * k + 1) * KS]);
@@ -395,9 +395,16 @@ int dst_ensure_wavefront(dst_handle* h, long long slots, size_t state_bytes) {
 
 // chunk-log buffers for `rays` rays of up to `segs` segments (grow-only)
 int dst_ensure_chunk_log(dst_handle* h, long long rays, int segs) {
+    // first guess 12 chunks per ray; afterwards what the previous training forward actually needed (read back
+    // asynchronously, see dst_forward_impl), within DST_LOG_MAX_RECORDS. Rays beyond the log re-trace in the backward.
     long long want = rays * 12 + 4096;
-    if (want > (48ll << 20)) want = 48ll << 20;           // 48 Mi records = 6.5 GB; rays beyond the log re-trace
-    if (want > h->log_cap) {
+    if (h->log_needed_host && h->log_needed_event && cudaEventQuery(h->log_needed_event) == cudaSuccess) {
+        const long long seen = *h->log_needed_host;
+        if (seen > 0 && seen + seen / 8 > want) want = seen + seen / 8;
+    } else cudaGetLastError();
+    if (want > DST_LOG_MAX_RECORDS) want = DST_LOG_MAX_RECORDS;
+    if (h->log_max_records > 0 && want > h->log_max_records) want = h->log_max_records;
+    if (want > h->log_cap || (h->log_max_records > 0 && h->log_cap > h->log_max_records)) {
         cudaFree(h->log_keys); cudaFree(h->log_hdr); h->log_keys = nullptr; h->log_hdr = nullptr; h->log_cap = 0;
         cudaError_t e = cudaMalloc(&h->log_keys, 8 * DST_CHUNK * (size_t)want);
         if (e == cudaSuccess) e = cudaMalloc(&h->log_hdr, sizeof(int2) * (size_t)want);
@@ -477,6 +484,18 @@ int dst_forward_impl(dst_handle* h, const dst_fwd_args* a, cudaStream_t st) {
     else k_fwd_tail<false, false><<<g_tail, TAIL_THREADS, 0, st>>>(p);
     dst_prof_mark(h, 1, 1, st);
     DST_CUDA_TRY(h, cudaGetLastError());
+    if (p.log_keys) {
+        // how many records this call wanted, for sizing the log of the next one (no synchronisation here)
+        if (!h->log_needed_host) {
+            if (cudaMallocHost(&h->log_needed_host, sizeof(int)) != cudaSuccess) { cudaGetLastError(); h->log_needed_host = nullptr; }
+            else *h->log_needed_host = 0;
+            if (h->log_needed_host && cudaEventCreateWithFlags(&h->log_needed_event, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); h->log_needed_event = nullptr; }
+        }
+        if (h->log_needed_host && h->log_needed_event) {
+            cudaMemcpyAsync(h->log_needed_host, h->log_count, sizeof(int), cudaMemcpyDeviceToHost, st);
+            cudaEventRecord(h->log_needed_event, st);
+        }
+    }
     return DST_OK;
 }
 

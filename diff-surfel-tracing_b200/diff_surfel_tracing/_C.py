@@ -138,6 +138,10 @@ class OptiXStateWrapper:
         live rays; smaller calls use one thread per ray for the whole path (same results)."""
         _check(self, lib().dst_set_option(self.handle, 1, int(n)))
 
+    def set_chunk_log_max_records(self, n):
+        """Upper limit on the chunk-log size in records of 136 bytes (0: built-in limit only)."""
+        _check(self, lib().dst_set_option(self.handle, 3, int(n)))
+
     def set_chunk_log(self, on):
         """Keep (default) or drop the per-ray chunk log training forwards leave for the backward (about 1.6 KB per ray)."""
         _check(self, lib().dst_set_option(self.handle, 2, int(bool(on))))

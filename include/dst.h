@@ -166,6 +166,9 @@ int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t*
 #define DST_OPT_WAVEFRONT_MIN_RAYS 1
 /* DST_OPT_CHUNK_LOG: 1 (default) keeps the chunk log of training forwards for the backward, 0 disables it. */
 #define DST_OPT_CHUNK_LOG 2
+/* DST_OPT_CHUNK_LOG_MAX_RECORDS: upper limit on the records (136 bytes each) the chunk log may hold; 0 = only the
+ * built-in limit. Rays whose chunks did not fit are re-traced by the backward, with the same result. */
+#define DST_OPT_CHUNK_LOG_MAX_RECORDS 3
 int dst_set_option(dst_handle* h, int option, int64_t value);
 
 /* Timing of the main kernels with CUDA events on the launching stream. While enabled, every

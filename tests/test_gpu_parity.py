@@ -171,6 +171,31 @@ def test_stale_chunk_log_is_not_used(C, oracle_mod):
     assert int(dg["counters"][2]) > 0
 
 
+def test_full_chunk_log_falls_back_to_retrace(C, oracle_mod):
+    """A log too small for the call: rays that did not fit are re-traced, gradients unchanged."""
+    w = hp.reduced_workload(3)
+    wc = hp.to_cuda(w)
+    H, W = w["ray_o"].shape[:2]
+    up = {"rgb": torch.ones((H, W, 3), device="cuda"), "dpt": torch.ones((H, W, 1), device="cuda")}
+    ref_state = _build(C, wc)
+    f = hp.cuda_forward(C, ref_state, wc)
+    ref = hp.cuda_backward(C, ref_state, wc, f, up, serial=0)
+    for wave in (False, True):
+        st = _build(C, wc, wave)
+        st.set_chunk_log_max_records(2000)          # the call needs about 50,000 records
+        f2 = hp.cuda_forward(C, st, wc)
+        dg = {}
+        g = hp.cuda_backward(C, st, wc, f2, up, diag=dg, serial=st.last_forward_serial)
+        torch.cuda.synchronize()
+        assert st.status() == 0
+        c = dg["counters"].cpu().numpy()
+        assert c[2] > 0 and c[5] == int(f2["wet"].numel() * 0 + c[5])      # some rays walked the hierarchy
+        for k in hp.GRAD_KEYS:
+            a, b = g[k].cpu().numpy(), ref[k].cpu().numpy()
+            m = np.isfinite(b)
+            assert hp.rel_l2(a[m], b[m]) < 1e-4, (wave, k)
+
+
 def test_refit_matches_rebuild(C, oracle_mod):
     """rebuild=0 keeps the topology and refits boxes and frames: results equal a fresh build on the moved vertices."""
     w = hp.reduced_workload(2)
