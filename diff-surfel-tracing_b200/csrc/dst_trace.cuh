@@ -8,7 +8,7 @@
 #define DST_MAX_CHUNKS 4096          // bound on enumerations per ray segment (the reference loops without one)
 #define DST_MAX_INTERSECTION 256     // optix_tracer/config.h:23
 #define DST_REF_SHIFT 4                // leaf reference = surfel id << 4 | sub-rectangle (iu << 2 | iv)
-#define DST_NODE_VOTE 16               // lanes with node work needed to stay in the node phase of k_enum
+#define DST_NODE_VOTE 10               // lanes with node work needed to stay in the node phase of k_enum
 #define DST_PAD_FACTOR 4e-6f         // box padding per unit of coordinate magnitude, see knearest()
 
 struct TraceCounters { unsigned long long segs, enums, nodes, quads, evals, contribs; };
