@@ -8,7 +8,10 @@
 #define DST_MAX_CHUNKS 4096          // bound on enumerations per ray segment (the reference loops without one)
 #define DST_MAX_INTERSECTION 256     // optix_tracer/config.h:23
 #define DST_REF_SHIFT 4                // leaf reference = surfel id << 4 | sub-rectangle (iu << 2 | iv)
-#define DST_NODE_VOTE 10               // lanes with node work needed to stay in the node phase of k_enum
+#define DST_NODE_VOTE 10
+#ifndef DST_SHARE_VOTE
+#define DST_SHARE_VOTE 8                // lanes that must want a subtree for the warp to walk it together (k_enum)
+#endif               // lanes with node work needed to stay in the node phase of k_enum
 #define DST_PAD_FACTOR 4e-6f         // box padding per unit of coordinate magnitude, see knearest()
 
 struct TraceCounters { unsigned long long segs, enums, nodes, quads, evals, contribs; };
@@ -303,29 +306,44 @@ __device__ __forceinline__ RaySlab make_slab(float ox, float oy, float oz, float
     return r;
 }
 
-// Persistent enumeration kernel: every lane walks the hierarchy for one ray at a time and, as soon
-// as its ray is done, takes the next entry of the live list from a shared cursor, so a warp stays
-// full until the list is exhausted however uneven the rays are. Same result as knearest().
+// Gather kernel: per live ray, the 16 nearest hits from the requested origin (same result as knearest()).
+//
+// A warp takes 32 consecutive entries of the live list: neighbouring pixels, whose rays start close to
+// each other. Large overlapping quads put hundreds of boxes around any origin, and every one of the
+// 32 rays has to open them, so the walk is split in two:
+//   shared phase   the warp walks the hierarchy TOGETHER from the root with one stack; a node is
+//                  fetched once (one broadcast load instead of 32 scattered ones) and every lane tests
+//                  its own ray against both child boxes. A child wanted by at least DST_SHARE_VOTE
+//                  lanes stays in the shared walk; a child wanted by fewer goes onto the private
+//                  stacks of those lanes. Leaf runs reached here are tested by all lanes.
+//   private phase  every lane drains its own stack as in knearest(), lanes alternating between a
+//                  node phase (kept while at least DST_NODE_VOTE lanes have node work) and a leaf phase.
+// Pruning uses each lane's own 16th-nearest distance throughout, so the hit set is exactly that of
+// an independent walk per ray. Blocks are persistent and take batches from a shared cursor.
+#define DST_SHARED_STACK 64
+#define DST_ENUM_STACK 160       // private stack of k_enum: subtrees deferred by the shared walk + one depth-first descent
+#define DST_ENUM_DEFER 64        // the shared walk pauses to drain the private stacks when a lane holds this many entries
 template <bool COUNT>
 __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumReq* __restrict__ req, const int* __restrict__ list,
                                                        const int* __restrict__ count_ptr, int* cursor, int min_count,
                                                        unsigned long long* __restrict__ kbuf, int* __restrict__ kcnt,
                                                        unsigned int* status, unsigned long long* counters) {
     __shared__ unsigned long long kshared[DST_CHUNK * ENUM_THREADS];
+    __shared__ int sstack[ENUM_THREADS / 32][DST_SHARED_STACK];
     const int total = *count_ptr;
     if (total < min_count || bvh.nrefs <= 0) return;
     constexpr int KS = ENUM_THREADS;
     constexpr int DONE = 0x7fffffff;
+    constexpr unsigned int FULL = 0xffffffffu;
     unsigned long long* kb = kshared + threadIdx.x;
-    const int lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const float absmax = __ldg(bvh.header + 6);
     TraceCounters tc = { 0, 0, 0, 0, 0, 0 };
-    unsigned long long stack[DST_STACK];
-    int sp = 0, n = 0, cur = DONE, ray = -1;
-    float kmax = DST_T_MAX;
+    unsigned long long stack[DST_ENUM_STACK];
+    int sp = 0, n = 0;
+    float kmax = -1.0f;
     float ox = 0.f, oy = 0.f, oz = 0.f, dx = 0.f, dy = 0.f, dz = 0.f;
     RaySlab sl = make_slab(0.f, 0.f, 0.f, 1.f, 1.f, 1.f, 0.f);
-    bool exhausted = false;            // warp-uniform: the list has no more entries
 
     auto pop = [&]() -> int {
         while (sp > 0) {
@@ -334,100 +352,152 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
         }
         return DONE;
     };
+    auto push = [&](int link, float tn) {
+        if (sp < DST_ENUM_STACK) stack[sp++] = ((unsigned long long)__float_as_uint(tn) << 32) | (unsigned int)link;
+        else atomicOr(status, DST_STATUS_STACK_OVERFLOW);
+    };
+    // both child boxes of one node against this lane's ray
+    auto test_node = [&](int node, float& tn0, float& tn1, bool& h0, bool& h1, int& l0, int& l1) {
+        const float4* np = bvh.nodes + 4 * (size_t)node;
+        const float4 a = __ldg(np), b = __ldg(np + 1), c = __ldg(np + 2);
+        const int4 lk = __ldg(reinterpret_cast<const int4*>(np + 3));
+        const float n0x = sl.px ? a.x : a.w, f0x = sl.px ? a.w : a.x;
+        const float n0y = sl.py ? a.y : b.x, f0y = sl.py ? b.x : a.y;
+        const float n0z = sl.pz ? a.z : b.y, f0z = sl.pz ? b.y : a.z;
+        const float n1x = sl.px ? b.z : c.y, f1x = sl.px ? c.y : b.z;
+        const float n1y = sl.py ? b.w : c.z, f1y = sl.py ? c.z : b.w;
+        const float n1z = sl.pz ? c.x : c.w, f1z = sl.pz ? c.w : c.x;
+        tn0 = fmaxf(fmaxf(fmaf(n0x, sl.ix, -sl.onx), fmaf(n0y, sl.iy, -sl.ony)), fmaxf(fmaf(n0z, sl.iz, -sl.onz), 0.0f));
+        const float tf0 = fminf(fminf(fmaf(f0x, sl.ix, -sl.ofx), fmaf(f0y, sl.iy, -sl.ofy)), fmaf(f0z, sl.iz, -sl.ofz));
+        tn1 = fmaxf(fmaxf(fmaf(n1x, sl.ix, -sl.onx), fmaf(n1y, sl.iy, -sl.ony)), fmaxf(fmaf(n1z, sl.iz, -sl.onz), 0.0f));
+        const float tf1 = fminf(fminf(fmaf(f1x, sl.ix, -sl.ofx), fmaf(f1y, sl.iy, -sl.ofy)), fmaf(f1z, sl.iz, -sl.ofz));
+        h0 = (tn0 <= tf0) && (tn0 <= kmax);
+        h1 = (tn1 <= tf1) && (tn1 <= kmax);
+        l0 = lk.z; l1 = lk.w;
+    };
+    // exact test of one quad and insertion into this lane's k-buffer
+    auto offer = [&](int pos) {
+        const float4* qp = bvh.quads + 3 * (size_t)pos;
+        const float4 qa = __ldg(qp), qb = __ldg(qp + 1), qc = __ldg(qp + 2);
+        float t; int tri;
+        if (!ray_quad(qa, qb, qc, ox, oy, oz, dx, dy, dz, kmax, t, tri)) return;
+        const unsigned int gid = (unsigned int)__ldg(bvh.leaf_gid + pos) >> DST_REF_SHIFT;
+        const unsigned long long key = make_key(t, 2u * gid + (unsigned int)tri);
+        if (n == DST_CHUNK && key >= kb[(DST_CHUNK - 1) * KS]) return;
+        int j = n;
+        while (j > 0 && kb[(j - 1) * KS] > key) j--;
+        if (j > 0 && kb[(j - 1) * KS] == key) return;
+        if (n == DST_CHUNK) n = DST_CHUNK - 1;
+        for (int i = n; i > j; i--) kb[i * KS] = kb[(i - 1) * KS];
+        kb[j * KS] = key;
+        n++;
+        if (n == DST_CHUNK) kmax = hitkey_t(kb[(DST_CHUNK - 1) * KS]);
+    };
 
     for (;;) {
-        // ---- hand finished lanes their next ray ----
-        const unsigned int idle = __ballot_sync(0xffffffffu, ray < 0);
-        if (idle && !exhausted) {
-            int base = 0;
-            const int leader = __ffs(idle) - 1;
-            if (lane == leader) base = atomicAdd(cursor, __popc(idle));
-            base = __shfl_sync(0xffffffffu, base, leader);
-            if (base + __popc(idle) >= total) exhausted = true;
-            if (ray < 0) {
-                const int idx = base + __popc(idle & ((1u << lane) - 1u));
-                const int r = idx < total ? list[idx] : -1;
-                if (r >= 0) {
-                    const float4 r0 = __ldg(reinterpret_cast<const float4*>(req + r)), r1 = __ldg(reinterpret_cast<const float4*>(req + r) + 1);
-                    ox = r0.x; oy = r0.y; oz = r0.z; dx = r0.w; dy = r1.x; dz = r1.y; kmax = r1.z;
-                    sl = make_slab(ox, oy, oz, dx, dy, dz, absmax);
-                    ray = r; n = 0; sp = 0;
-                    cur = sl.valid ? 0 : DONE;
-                    if (COUNT) tc.enums++;
-                }
-            }
+        // ---- next batch of 32 list entries for this warp ----
+        int base = 0;
+        if (lane == 0) base = atomicAdd(cursor, 32);
+        base = __shfl_sync(FULL, base, 0);
+        if (base >= total) break;
+        const int idx = base + lane;
+        const int ray = idx < total ? list[idx] : -1;
+        bool active = false;
+        n = 0; sp = 0; kmax = -1.0f;
+        if (ray >= 0) {
+            const float4 r0 = __ldg(reinterpret_cast<const float4*>(req + ray)), r1 = __ldg(reinterpret_cast<const float4*>(req + ray) + 1);
+            ox = r0.x; oy = r0.y; oz = r0.z; dx = r0.w; dy = r1.x; dz = r1.y;
+            sl = make_slab(ox, oy, oz, dx, dy, dz, absmax);
+            active = sl.valid;
+            if (active) kmax = r1.z;
+            if (COUNT) tc.enums++;
         }
-        if (__all_sync(0xffffffffu, ray < 0)) { if (exhausted) break; else continue; }
-
-        // ---- node phase: lanes holding an internal node step through it; the phase lasts while at
-        //      least DST_NODE_VOTE lanes have node work (or nobody has anything else to do), so that
-        //      lanes waiting with a leaf are not starved and node steps run with most lanes busy ----
+        int ssp = 0, scur = __any_sync(FULL, active) ? 0 : DONE;     // shared walk: stack pointer and current link (uniform)
         for (;;) {
-            const bool is_node = (unsigned int)cur < (unsigned int)DONE;
-            const unsigned int m = __ballot_sync(0xffffffffu, is_node);
-            if (m == 0u) break;
-            if (__popc(m) < DST_NODE_VOTE && __any_sync(0xffffffffu, cur < 0 || (cur == DONE && ray >= 0))) break;
-            if (!is_node) continue;
-            const float4* np = bvh.nodes + 4 * (size_t)cur;
-            const float4 a = __ldg(np), b = __ldg(np + 1), c = __ldg(np + 2);
-            const int4 lk = __ldg(reinterpret_cast<const int4*>(np + 3));
-            if (COUNT) tc.nodes++;
-            const float n0x = sl.px ? a.x : a.w, f0x = sl.px ? a.w : a.x;
-            const float n0y = sl.py ? a.y : b.x, f0y = sl.py ? b.x : a.y;
-            const float n0z = sl.pz ? a.z : b.y, f0z = sl.pz ? b.y : a.z;
-            const float n1x = sl.px ? b.z : c.y, f1x = sl.px ? c.y : b.z;
-            const float n1y = sl.py ? b.w : c.z, f1y = sl.py ? c.z : b.w;
-            const float n1z = sl.pz ? c.x : c.w, f1z = sl.pz ? c.w : c.x;
-            const float tn0 = fmaxf(fmaxf(fmaf(n0x, sl.ix, -sl.onx), fmaf(n0y, sl.iy, -sl.ony)), fmaxf(fmaf(n0z, sl.iz, -sl.onz), 0.0f));
-            const float tf0 = fminf(fminf(fmaf(f0x, sl.ix, -sl.ofx), fmaf(f0y, sl.iy, -sl.ofy)), fmaf(f0z, sl.iz, -sl.ofz));
-            const float tn1 = fmaxf(fmaxf(fmaf(n1x, sl.ix, -sl.onx), fmaf(n1y, sl.iy, -sl.ony)), fmaxf(fmaf(n1z, sl.iz, -sl.onz), 0.0f));
-            const float tf1 = fminf(fminf(fmaf(f1x, sl.ix, -sl.ofx), fmaf(f1y, sl.iy, -sl.ofy)), fmaf(f1z, sl.iz, -sl.ofz));
-            const bool h0 = (tn0 <= tf0) && (tn0 <= kmax);
-            const bool h1 = (tn1 <= tf1) && (tn1 <= kmax);
-            if (h0 && h1) {
-                const bool swap = tn1 < tn0;
-                const int cf = swap ? lk.z : lk.w;
-                const float tfar = swap ? tn0 : tn1;
-                if (sp < DST_STACK) stack[sp++] = ((unsigned long long)__float_as_uint(tfar) << 32) | (unsigned int)cf;
-                else atomicOr(status, DST_STATUS_STACK_OVERFLOW);
-                cur = swap ? lk.w : lk.z;
-            } else if (h0) cur = lk.z;
-            else if (h1) cur = lk.w;
-            else cur = pop();
-        }
-        // ---- leaf run: exact quad tests and k-buffer insertion ----
-        if (cur < 0) {
-            const int first = DST_LEAF_FIRST(cur), count = DST_LEAF_COUNT(cur);
-            for (int lq = 0; lq < count; lq++) {
-                const int pos = first + lq;
-                const float4* qp = bvh.quads + 3 * (size_t)pos;
-                const float4 qa = __ldg(qp), qb = __ldg(qp + 1), qc = __ldg(qp + 2);
-                if (COUNT) tc.quads++;
-                float t; int tri;
-                if (!ray_quad(qa, qb, qc, ox, oy, oz, dx, dy, dz, kmax, t, tri)) continue;
-                const unsigned int gid = (unsigned int)__ldg(bvh.leaf_gid + pos) >> DST_REF_SHIFT;
-                const unsigned long long key = make_key(t, 2u * gid + (unsigned int)tri);
-                if (n == DST_CHUNK && key >= kb[(DST_CHUNK - 1) * KS]) continue;
-                int j = n;
-                while (j > 0 && kb[(j - 1) * KS] > key) j--;
-                if (j > 0 && kb[(j - 1) * KS] == key) continue;
-                if (n == DST_CHUNK) n = DST_CHUNK - 1;
-                for (int i = n; i > j; i--) kb[i * KS] = kb[(i - 1) * KS];
-                kb[j * KS] = key;
-                n++;
-                if (n == DST_CHUNK) kmax = hitkey_t(kb[(DST_CHUNK - 1) * KS]);
+        // ---- shared phase (left early when a private stack is about to fill up: deferred subtrees pile up there) ----
+        if (scur != DONE) {
+            for (;;) {
+                if (__any_sync(FULL, sp >= DST_ENUM_DEFER)) break;     // drain the private stacks first, then come back to scur
+                if (scur >= 0) {
+                    float tn0, tn1; bool h0, h1; int l0, l1;
+                    test_node(scur, tn0, tn1, h0, h1, l0, l1);
+                    if (COUNT && lane == 0) tc.nodes++;
+                    const bool w0 = active && h0, w1 = active && h1;
+                    const unsigned int m0 = __ballot_sync(FULL, w0), m1 = __ballot_sync(FULL, w1);
+                    const bool s0 = __popc(m0) >= DST_SHARE_VOTE, s1 = __popc(m1) >= DST_SHARE_VOTE;
+                    int next = DONE;
+                    if (s0 && s1) {
+                        // the majority of the lanes that want both decides which child comes first
+                        const unsigned int pref1 = __ballot_sync(FULL, w0 && w1 && tn1 < tn0);
+                        const bool first1 = 2 * __popc(pref1) > __popc(m0 & m1);
+                        const int other = first1 ? l0 : l1;
+                        if (ssp < DST_SHARED_STACK) { if (lane == 0) sstack[wid][ssp] = other; ssp++; }
+                        else if (first1 ? w0 : w1) push(other, first1 ? tn0 : tn1);       // shared stack full: defer privately
+                        next = first1 ? l1 : l0;
+                    } else {
+                        // children wanted by too few lanes go onto those lanes' own stacks (farther one first)
+                        const bool d0 = w0 && !s0, d1 = w1 && !s1;
+                        if (d0 && d1) { if (tn1 < tn0) { push(l0, tn0); push(l1, tn1); } else { push(l1, tn1); push(l0, tn0); } }
+                        else if (d0) push(l0, tn0);
+                        else if (d1) push(l1, tn1);
+                        if (s0) next = l0; else if (s1) next = l1;
+                    }
+                    if (s0 && s1) {
+                        // (children shared by the warp need no private entry)
+                    }
+                    if (next != DONE) { scur = next; continue; }
+                } else {
+                    // a run of leaves reached together: one broadcast fetch per quad, every lane tests its own ray
+                    const int first = DST_LEAF_FIRST(scur), count = DST_LEAF_COUNT(scur);
+                    for (int lq = 0; lq < count; lq++) {
+                        if (COUNT && lane == 0) tc.quads++;
+                        if (active) offer(first + lq);
+                    }
+                }
+                if (ssp == 0) { scur = DONE; break; }
+                __syncwarp();
+                scur = sstack[wid][--ssp];
+                __syncwarp();
             }
-            cur = pop();
         }
-        // ---- done: publish the chunk ----
-        if (cur == DONE && ray >= 0) {
+        // ---- private phase ----
+        int cur = active ? pop() : DONE;
+        while (__any_sync(FULL, cur != DONE)) {
+            // node phase: kept while at least DST_NODE_VOTE lanes have node work or nobody holds a leaf
+            for (;;) {
+                const bool is_node = (unsigned int)cur < (unsigned int)DONE;
+                const unsigned int m = __ballot_sync(FULL, is_node);
+                if (m == 0u) break;
+                if (__popc(m) < DST_NODE_VOTE && __any_sync(FULL, cur < 0)) break;
+                if (!is_node) continue;
+                float tn0, tn1; bool h0, h1; int l0, l1;
+                test_node(cur, tn0, tn1, h0, h1, l0, l1);
+                if (COUNT) tc.nodes++;
+                if (h0 && h1) {
+                    const bool swap = tn1 < tn0;
+                    push(swap ? l0 : l1, swap ? tn0 : tn1);
+                    cur = swap ? l1 : l0;
+                } else if (h0) cur = l0;
+                else if (h1) cur = l1;
+                else cur = pop();
+            }
+            // leaf phase
+            if (cur < 0) {
+                const int first = DST_LEAF_FIRST(cur), count = DST_LEAF_COUNT(cur);
+                for (int lq = 0; lq < count; lq++) { if (COUNT) tc.quads++; offer(first + lq); }
+                cur = pop();
+            }
+        }
+        if (scur == DONE) break;
+        }
+        // ---- publish the chunks of this batch ----
+        if (ray >= 0) {
             kcnt[ray] = n;
             ulonglong2* out = reinterpret_cast<ulonglong2*>(kbuf + (size_t)ray * DST_CHUNK);
 #pragma unroll
             for (int k = 0; k < DST_CHUNK / 2; k++) {
                 if (2 * k < n) out[k] = make_ulonglong2(kb[(2 * k) * KS], kb[(2 * k + 1) * KS]);
             }
-            ray = -1;
         }
     }
     if (COUNT && counters) { atomicAdd(counters + 1, tc.enums); atomicAdd(counters + 2, tc.nodes); atomicAdd(counters + 3, tc.quads); }
