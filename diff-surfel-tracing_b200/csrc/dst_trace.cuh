@@ -10,7 +10,7 @@
 #define DST_REF_SHIFT 4                // leaf reference = surfel id << 4 | sub-rectangle (iu << 2 | iv)
 #define DST_NODE_VOTE 10
 #ifndef DST_SHARE_VOTE
-#define DST_SHARE_VOTE 8                // lanes that must want a subtree for the warp to walk it together (k_enum)
+#define DST_SHARE_VOTE 1                // lanes that must want a subtree for the warp to walk it together (k_enum)
 #endif               // lanes with node work needed to stay in the node phase of k_enum
 #define DST_PAD_FACTOR 4e-6f         // box padding per unit of coordinate magnitude, see knearest()
 
