@@ -586,7 +586,7 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
     DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 2 * (DST_WF_ROUNDS + 2), st));
     const bool wave = slots >= h->wf_min_rays;
     p.rounds = wave ? DST_WF_ROUNDS : 0;
-    p.min_count = wave ? (int)(slots / 64 > 4096 ? slots / 64 : 4096) : 1;
+    p.min_count = wave ? (int)(slots / 512 > 2048 ? slots / 512 : 2048) : 1;
     dst_prof_mark(h, 2, 0, st);
     if (use_log) {
         // the forward kept its chunks: re-composite them; rays the log could not hold are queued as round 0 of the

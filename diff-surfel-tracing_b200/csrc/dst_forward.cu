@@ -464,7 +464,7 @@ int dst_forward_impl(dst_handle* h, const dst_fwd_args* a, cudaStream_t st) {
     // small launches go straight to the per-ray kernel; large ones run wavefront rounds until few rays are left
     const bool wave = slots >= h->wf_min_rays;
     p.rounds = wave ? DST_WF_ROUNDS : 0;
-    p.min_count = wave ? (int)(slots / 64 > 4096 ? slots / 64 : 4096) : 1;
+    p.min_count = wave ? (int)(slots / 512 > 2048 ? slots / 512 : 2048) : 1;
     const bool diag = a->hit_log || a->hit_cnt || a->counters;
     DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 2 * (DST_WF_ROUNDS + 2), st));
     dst_prof_mark(h, 1, 0, st);

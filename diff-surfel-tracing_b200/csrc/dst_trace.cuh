@@ -9,6 +9,9 @@
 #define DST_MAX_INTERSECTION 256     // optix_tracer/config.h:23
 #define DST_REF_SHIFT 4                // leaf reference = surfel id << 4 | sub-rectangle (iu << 2 | iv)
 #define DST_NODE_VOTE 10
+#ifndef DST_SHARE_MIN_PCT
+#define DST_SHARE_MIN_PCT 25              // the warp gives up walking together when fewer than this % of the lane tests are wanted
+#endif
 #ifndef DST_SHARE_VOTE
 #define DST_SHARE_VOTE 1                // lanes that must want a subtree for the warp to walk it together (k_enum)
 #endif               // lanes with node work needed to stay in the node phase of k_enum
@@ -413,17 +416,29 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
             if (COUNT) tc.enums++;
         }
         int ssp = 0, scur = __any_sync(FULL, active) ? 0 : DONE;     // shared walk: stack pointer and current link (uniform)
+        int s_tests = 0, s_wanted = 0;                                // child tests made together / of them wanted by their lane
         for (;;) {
         // ---- shared phase (left early when a private stack is about to fill up: deferred subtrees pile up there) ----
         if (scur != DONE) {
             for (;;) {
                 if (__any_sync(FULL, sp >= DST_ENUM_DEFER)) break;     // drain the private stacks first, then come back to scur
+                if (s_tests >= 64 * 32 && s_wanted * 100 < s_tests * DST_SHARE_MIN_PCT && ssp + 1 <= DST_ENUM_STACK - DST_ENUM_DEFER - 40) {
+                    // these rays do not travel together (most lanes sit out most tests): every lane takes the
+                    // pending subtrees onto its own stack and the batch continues lane by lane
+                    if (active) {
+                        push(scur, 0.0f);
+                        for (int e = 0; e < ssp; e++) push(sstack[wid][e], 0.0f);
+                    }
+                    ssp = 0; scur = DONE;
+                    break;
+                }
                 if (scur >= 0) {
                     float tn0, tn1; bool h0, h1; int l0, l1;
                     test_node(scur, tn0, tn1, h0, h1, l0, l1);
                     if (COUNT && lane == 0) tc.nodes++;
                     const bool w0 = active && h0, w1 = active && h1;
                     const unsigned int m0 = __ballot_sync(FULL, w0), m1 = __ballot_sync(FULL, w1);
+                    s_tests += 64; s_wanted += __popc(m0) + __popc(m1);
                     const bool s0 = __popc(m0) >= DST_SHARE_VOTE, s1 = __popc(m1) >= DST_SHARE_VOTE;
                     int next = DONE;
                     if (s0 && s1) {
