@@ -82,7 +82,7 @@ int dst_destroy(dst_handle* h) {
     cudaFree(h->nodes); cudaFree(h->quads); cudaFree(h->leaf_gid); cudaFree(h->leaf_parent); cudaFree(h->arrive);
     cudaFree(h->node_parent); cudaFree(h->node_first); cudaFree(h->node_count); cudaFree(h->child_cost);
     cudaFree(h->keys); cudaFree(h->keys_alt); cudaFree(h->vals); cudaFree(h->vals_alt); cudaFree(h->block_hist);
-    cudaFree(h->header); cudaFree(h->status); cudaFree(h->cache); cudaFree(h->arena);
+    cudaFree(h->header); cudaFree(h->status); cudaFree(h->cache); cudaFree(h->arena); cudaFree(h->cam_dev);
     if (h->log_needed_host) cudaFreeHost(h->log_needed_host);
     if (h->log_needed_event) cudaEventDestroy(h->log_needed_event);
     cudaFree(h->log_keys); cudaFree(h->log_hdr); cudaFree(h->log_count); cudaFree(h->log_seg_head); cudaFree(h->log_ray_ok);
@@ -107,6 +107,41 @@ int dst_build(dst_handle* h, const float* vertices, int64_t n_vertices, const in
     if (!g.ok) return dst_set_error(h, DST_E_CUDA, "cudaSetDevice(%d) failed", h->device);
     h->log_serial = 0;      // the logged chunks refer to the hierarchy that is about to change
     return dst_bvh_build_impl(h, vertices, n_vertices / 4, rebuild, (cudaStream_t)stream);
+}
+
+int dst_surfel_quads(dst_handle* h, const float* means3D, const float* scales, const float* rotations, int64_t n_surfels,
+                     float* vertices, int32_t* triangles, void* stream) {
+    if (!h) return DST_E_ARG;
+    if (!means3D || !scales || !rotations || !vertices) return dst_set_error(h, DST_E_ARG, "a required pointer is null");
+    DeviceGuard g(h->device);
+    if (!g.ok) return dst_set_error(h, DST_E_CUDA, "cudaSetDevice(%d) failed", h->device);
+    return dst_surfel_quads_impl(h, means3D, scales, rotations, n_surfels, vertices, triangles, (cudaStream_t)stream);
+}
+
+int dst_build_from_surfels(dst_handle* h, const float* means3D, const float* scales, const float* rotations, int64_t n_surfels,
+                           float* vertices, int rebuild, void* stream) {
+    if (!h) return DST_E_ARG;
+    if (!means3D || !scales || !rotations || !vertices) return dst_set_error(h, DST_E_ARG, "a required pointer is null");
+    DeviceGuard g(h->device);
+    if (!g.ok) return dst_set_error(h, DST_E_CUDA, "cudaSetDevice(%d) failed", h->device);
+    h->log_serial = 0;
+    return dst_bvh_build_impl(h, vertices, n_surfels, rebuild, (cudaStream_t)stream, means3D, scales, rotations);
+}
+
+int dst_pinhole_rays(dst_handle* h, const dst_camera* cameras, int n_cameras, int H, int W, float* ray_o, float* ray_d, void* stream) {
+    if (!h) return DST_E_ARG;
+    if (!cameras || !ray_o || !ray_d) return dst_set_error(h, DST_E_ARG, "a required pointer is null");
+    DeviceGuard g(h->device);
+    if (!g.ok) return dst_set_error(h, DST_E_CUDA, "cudaSetDevice(%d) failed", h->device);
+    return dst_pinhole_rays_impl(h, cameras, n_cameras, H, W, ray_o, ray_d, (cudaStream_t)stream);
+}
+
+int dst_forward_camera(dst_handle* h, const dst_fwd_args* args, const dst_camera* camera, void* stream) {
+    if (!h) return DST_E_ARG;
+    if (!args || !camera) return dst_set_error(h, DST_E_ARG, "args or camera is null");
+    DeviceGuard g(h->device);
+    if (!g.ok) return dst_set_error(h, DST_E_CUDA, "cudaSetDevice(%d) failed", h->device);
+    return dst_forward_camera_impl(h, args, camera, (cudaStream_t)stream);
 }
 
 int dst_forward(dst_handle* h, const dst_fwd_args* args, void* stream) {

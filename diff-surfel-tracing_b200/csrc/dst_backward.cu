@@ -13,6 +13,9 @@
 namespace {
 
 constexpr int BWD_THREADS = 128;
+#ifndef DST_BWD_LOGGED_BLOCKS
+#define DST_BWD_LOGGED_BLOCKS 1      // resident blocks per SM the logged backward is compiled for
+#endif
 
 struct BwdParams {
     dst_bwd_args a;
@@ -208,6 +211,14 @@ __device__ __forceinline__ bool bwd_init_state(const BwdParams& p, int ray, BwdS
     return bwd_next_segment(p, ray, s, in.max_trace_depth);
 }
 
+// b[j] for a run-time j without indexing the array (which would move it from registers to local memory)
+__device__ __forceinline__ float basis_at(const float* b, int j) {
+    float r = b[0];
+#pragma unroll
+    for (int k = 1; k < 16; k++) r = (j == k) ? b[k] : r;
+    return r;
+}
+
 // Re-composites one gathered chunk of segment s.seg and accumulates the gradients of every
 // contributing hit (backward.cu:429-655). Returns true while the ray needs another enumeration.
 template <bool DIAG, int KS>
@@ -371,9 +382,12 @@ __device__ __forceinline__ bool bwd_shade(const BwdParams& p, int ray, BwdState&
                         red4(dsh + 4 * q4, o4[0], o4[1], o4[2], o4[3]);
                     }
                 }
-                for (int f = nv << 2; f < nf; f++) { const int j = f / 3, ch = f - 3 * j; atomicAdd(dsh + f, sb[j] * (ch == 0 ? m0c : ch == 1 ? m1c : m2c)); }
+                for (int f = nv << 2; f < nf; f++) { const int j = f / 3, ch = f - 3 * j; atomicAdd(dsh + f, basis_at(sb, j) * (ch == 0 ? m0c : ch == 1 ? m1c : m2c)); }
             } else {
-                for (int j = 0; j < ncoef; j++) { atomicAdd(dsh + 3 * j, sb[j] * m0c); atomicAdd(dsh + 3 * j + 1, sb[j] * m1c); atomicAdd(dsh + 3 * j + 2, sb[j] * m2c); }
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    if (j < ncoef) { atomicAdd(dsh + 3 * j, sb[j] * m0c); atomicAdd(dsh + 3 * j + 1, sb[j] * m1c); atomicAdd(dsh + 3 * j + 2, sb[j] * m2c); }
+                }
             }
             dir_gidx = gidx; dir_g0 = m0c; dir_g1 = m1c; dir_g2 = m2c;
         }
@@ -494,7 +508,7 @@ __device__ __forceinline__ void bwd_flush_counters(unsigned long long* counters,
 // segments. Rays whose log is incomplete (log full during the forward) are initialised and queued
 // for k_bwd_tail, which re-traces them.
 template <bool DIAG>
-__global__ void __launch_bounds__(BWD_THREADS) k_bwd_logged(const __grid_constant__ BwdParams p, long long slots) {
+__global__ void __launch_bounds__(BWD_THREADS, DST_BWD_LOGGED_BLOCKS) k_bwd_logged(const __grid_constant__ BwdParams p, long long slots) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const int ray = i < slots ? ray_of_slot(i, p.a.in.H, p.a.in.W, p.tiled != 0) : -1;
     TraceCounters tc = { 0, 0, 0, 0, 0, 0 };

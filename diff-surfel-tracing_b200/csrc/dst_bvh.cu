@@ -260,7 +260,57 @@ __device__ __forceinline__ float box_area(const float* lo, const float* hi) {
     return (a > 0.0f && a < INFINITY) ? a : 0.0f;
 }
 
-__global__ void __launch_bounds__(256) k_refit(const float* __restrict__ verts, int P, const unsigned int* __restrict__ vals,
+// The 4 corners of surfel g from its parameters, in the reference's expression order
+// (example/utils/gaussian_utils.py:176-210 with build_cov :286-296, build_scaling_rotation :273-282,
+// build_rotation :214-249): q = r / |r| in (w,x,y,z) order, tangent columns of R scaled by s_x and
+// s_y, corner k = (3 cu_k) L0 + (3 cv_k) L1 + mean, (cu,cv) = (-1,+1), (-1,-1), (+1,+1), (+1,-1).
+// One rounding per operation; bit-identical to the reference's CPU tensor ops on the test vectors.
+struct SurfelSource { const float* means; const float* scales; const float* rotations; float* v_out; };
+
+__device__ __forceinline__ void surfel_corners(const SurfelSource& src, int g, float* v) {
+    const float4 r = __ldg(reinterpret_cast<const float4*>(src.rotations) + g);
+    const float2 sc = __ldg(reinterpret_cast<const float2*>(src.scales) + g);
+    const float m[3] = { __ldg(src.means + 3 * (size_t)g), __ldg(src.means + 3 * (size_t)g + 1), __ldg(src.means + 3 * (size_t)g + 2) };
+    const float n = xsqrt(xadd(xadd(xadd(xmul(r.x, r.x), xmul(r.y, r.y)), xmul(r.z, r.z)), xmul(r.w, r.w)));
+    const float w = xdiv(r.x, n), x = xdiv(r.y, n), y = xdiv(r.z, n), z = xdiv(r.w, n);
+    float c0[3], c1[3];
+    c0[0] = xsub(1.0f, xmul(2.0f, xadd(xmul(y, y), xmul(z, z))));
+    c0[1] = xmul(2.0f, xadd(xmul(x, y), xmul(w, z)));
+    c0[2] = xmul(2.0f, xsub(xmul(x, z), xmul(w, y)));
+    c1[0] = xmul(2.0f, xsub(xmul(x, y), xmul(w, z)));
+    c1[1] = xsub(1.0f, xmul(2.0f, xadd(xmul(x, x), xmul(z, z))));
+    c1[2] = xmul(2.0f, xadd(xmul(y, z), xmul(w, x)));
+#pragma unroll
+    for (int a = 0; a < 3; a++) {
+        const float lu = xmul(c0[a], sc.x), lv = xmul(c1[a], sc.y);
+        const float u3 = xmul(lu, 3.0f), v3 = xmul(lv, 3.0f);
+        v[0 + a] = xadd(xadd(-u3, v3), m[a]);
+        v[3 + a] = xadd(xadd(-u3, -v3), m[a]);
+        v[6 + a] = xadd(xadd(u3, v3), m[a]);
+        v[9 + a] = xadd(xadd(u3, -v3), m[a]);
+    }
+}
+
+// get_triangles as one kernel: 36 B of parameters in, 48 B of vertices (+ 24 B of indices) out per surfel
+__global__ void __launch_bounds__(256) k_surfel_quads(SurfelSource src, int P, int32_t* __restrict__ tri) {
+    const int g = blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= P) return;
+    float v[12];
+    surfel_corners(src, g, v);
+    float4* o = reinterpret_cast<float4*>(src.v_out + 12 * (size_t)g);
+    o[0] = make_float4(v[0], v[1], v[2], v[3]); o[1] = make_float4(v[4], v[5], v[6], v[7]); o[2] = make_float4(v[8], v[9], v[10], v[11]);
+    if (tri) {
+        const int b = 4 * g;
+        int2* t = reinterpret_cast<int2*>(tri + 6 * (size_t)g);
+        t[0] = make_int2(b, b + 1); t[1] = make_int2(b + 2, b + 1); t[2] = make_int2(b + 2, b + 3);
+    }
+}
+
+// Bottom-up pass over the hierarchy: leaf level from the quads, then boxes, costs and walk links of
+// every ancestor. FROM_SURFELS: the quad corners are computed from the surfel parameters here and
+// written to the caller's vertex buffer on the way (the refit then never reads the vertices).
+template <bool FROM_SURFELS>
+__global__ void __launch_bounds__(256) k_refit(const float* __restrict__ verts, SurfelSource src, int P, const unsigned int* __restrict__ vals,
                                                BvhNode* nodes, const int* __restrict__ leaf_parent, const int* __restrict__ node_parent,
                                                const int* __restrict__ node_first, const int* __restrict__ node_count,
                                                float* child_cost, unsigned int* arrive,
@@ -269,7 +319,11 @@ __global__ void __launch_bounds__(256) k_refit(const float* __restrict__ verts, 
     if (pos >= P) return;
     const int gid = (int)vals[pos];
     float v[12];
-    {
+    if (FROM_SURFELS) {
+        surfel_corners(src, gid, v);
+        float4* o = reinterpret_cast<float4*>(src.v_out + 12 * (size_t)gid);
+        o[0] = make_float4(v[0], v[1], v[2], v[3]); o[1] = make_float4(v[4], v[5], v[6], v[7]); o[2] = make_float4(v[8], v[9], v[10], v[11]);
+    } else {
         const float4* p = reinterpret_cast<const float4*>(verts + 12 * (size_t)gid);
         float4 a = __ldg(p), b = __ldg(p + 1), c = __ldg(p + 2);
         v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
@@ -374,7 +428,26 @@ int ensure_capacity(dst_handle* h, int64_t P) {
 
 }  // namespace
 
-int dst_bvh_build_impl(dst_handle* h, const float* v, int64_t P, int rebuild, cudaStream_t st) {
+int dst_surfel_quads_impl(dst_handle* h, const float* means, const float* scales, const float* rotations, int64_t P,
+                          float* vertices, int32_t* triangles, cudaStream_t st) {
+    if (P <= 0 || P > (1ll << DST_LEAF_POS_BITS)) return dst_set_error(h, DST_E_ARG, "surfel count must be in [1, 2^26], got %lld", (long long)P);
+    if ((reinterpret_cast<uintptr_t>(vertices) & 15) || (reinterpret_cast<uintptr_t>(rotations) & 15) || (reinterpret_cast<uintptr_t>(scales) & 7) ||
+        (reinterpret_cast<uintptr_t>(triangles) & 7))
+        return dst_set_error(h, DST_E_ARG, "vertices and rotations must be 16-byte aligned, scales and triangles 8-byte aligned");
+    const SurfelSource src = { means, scales, rotations, vertices };
+    k_surfel_quads<<<(unsigned int)((P + 255) / 256), 256, 0, st>>>(src, (int)P, triangles);
+    DST_CUDA_TRY(h, cudaGetLastError());
+    return DST_OK;
+}
+
+// v: the vertex buffer. With means/scales/rotations non-null it is an OUTPUT: the quads are expanded
+// from the surfel parameters (rebuild: by k_surfel_quads before the sort; refit: inside k_refit).
+int dst_bvh_build_impl(dst_handle* h, const float* v, int64_t P, int rebuild, cudaStream_t st,
+                       const float* means, const float* scales, const float* rotations) {
+    const bool from_surfels = means != nullptr;
+    const SurfelSource src = { means, scales, rotations, const_cast<float*>(v) };
+    if (from_surfels && ((reinterpret_cast<uintptr_t>(rotations) & 15) || (reinterpret_cast<uintptr_t>(scales) & 7)))
+        return dst_set_error(h, DST_E_ARG, "rotations must be 16-byte aligned and scales 8-byte aligned");
     if (P <= 0) return dst_set_error(h, DST_E_ARG, "vertices must hold at least one surfel (4 vertices)");
     if (P > (1ll << DST_LEAF_POS_BITS)) return dst_set_error(h, DST_E_ARG, "at most 2^26 surfels are supported");
     if ((reinterpret_cast<uintptr_t>(v) & 15) != 0) return dst_set_error(h, DST_E_ARG, "vertices must be 16-byte aligned");
@@ -393,6 +466,7 @@ int dst_bvh_build_impl(dst_handle* h, const float* v, int64_t P, int rebuild, cu
     dst_prof_mark(h, 0, 0, st);
     if (rebuild) {
         h->built = false;
+        if (from_surfels) k_surfel_quads<<<grid, tpb, 0, st>>>(src, n, nullptr);
         k_init_bounds<<<1, 32, 0, st>>>(bw);
         const int rgrid = min(grid, h->sm_count * 8);
         k_centre_bounds<<<rgrid, tpb, 0, st>>>(v, n, bw);
@@ -414,8 +488,12 @@ int dst_bvh_build_impl(dst_handle* h, const float* v, int64_t P, int rebuild, cu
     }
     DST_CUDA_TRY(h, cudaMemsetAsync(h->arrive, 0, 4 * (size_t)(n > 1 ? n - 1 : 1), st));
     if (n == 1) k_single_leaf<<<1, 1, 0, st>>>(h->nodes, h->leaf_parent, h->node_parent, h->node_first, h->node_count, h->arrive);
-    k_refit<<<grid, tpb, 0, st>>>(v, n, h->vals, h->nodes, h->leaf_parent, h->node_parent, h->node_first, h->node_count, h->child_cost,
-                                  h->arrive, h->quads, h->leaf_gid, h->header);
+    if (from_surfels && !rebuild)
+        k_refit<true><<<grid, tpb, 0, st>>>(v, src, n, h->vals, h->nodes, h->leaf_parent, h->node_parent, h->node_first, h->node_count, h->child_cost,
+                                            h->arrive, h->quads, h->leaf_gid, h->header);
+    else
+        k_refit<false><<<grid, tpb, 0, st>>>(v, src, n, h->vals, h->nodes, h->leaf_parent, h->node_parent, h->node_first, h->node_count, h->child_cost,
+                                             h->arrive, h->quads, h->leaf_gid, h->header);
     dst_prof_mark(h, 0, 1, st);
     DST_CUDA_TRY(h, cudaGetLastError());
     h->built = true;

@@ -76,6 +76,7 @@ struct dst_handle {
     unsigned int* status;         // device status word
     float4* cache; int64_t cache_cap;
     float* arena;  int64_t arena_cap;
+    void* cam_dev;      // camera constants of the last ray-generation call
     int sm_count;
     // ray scratch of the wavefront trace (grow-only): state records, enumeration requests, hit buffers, live lists
     void* wf_state; size_t wf_state_bytes; void* wf_req; unsigned long long* wf_kbuf; int* wf_kcnt; int* wf_list[2]; int* wf_counts;
@@ -115,7 +116,12 @@ int dst_set_error(dst_handle* h, int code, const char* fmt, ...);
 void dst_global_error(const char* msg);
 
 // host entry points implemented in the kernel translation units
-int dst_bvh_build_impl(dst_handle* h, const float* v, int64_t P, int rebuild, cudaStream_t st);
+int dst_bvh_build_impl(dst_handle* h, const float* v, int64_t P, int rebuild, cudaStream_t st,
+                       const float* means = nullptr, const float* scales = nullptr, const float* rotations = nullptr);
+int dst_surfel_quads_impl(dst_handle* h, const float* means, const float* scales, const float* rotations, int64_t P,
+                          float* vertices, int32_t* triangles, cudaStream_t st);
+int dst_pinhole_rays_impl(dst_handle* h, const dst_camera* cams, int n_cameras, int H, int W, float* ray_o, float* ray_d, cudaStream_t st);
+int dst_forward_camera_impl(dst_handle* h, const dst_fwd_args* args, const dst_camera* cam, cudaStream_t st);
 int dst_forward_impl(dst_handle* h, const dst_fwd_args* a, cudaStream_t st);
 int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st);
 int dst_knearest_impl(dst_handle* h, const float* ro, const float* rd, int64_t n, unsigned long long* keys,

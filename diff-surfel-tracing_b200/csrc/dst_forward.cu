@@ -9,14 +9,21 @@
 // steps as a wavefront (k_enum / k_fwd_shade rounds over the list of live rays, state in scratch
 // memory); the stragglers and small launches run in k_fwd_tail, one thread per ray to completion.
 #include "dst_trace.cuh"
+#include <string.h>
 
 namespace {
 
 constexpr int SHADE_THREADS = 128;
 constexpr int TAIL_THREADS = 128;
 
+// One pinhole camera, reduced on the host to what a pixel needs: inverse intrinsics, rotation,
+// translation and centre (example/utils/ray_utils.py:19-60, 107).
+struct CamConst { float invK[9], R[9], T[3], c[3]; int correct_pix, z_depth; };
+
 struct FwdParams {
     dst_fwd_args a;
+    CamConst cam;       // used when cam_on: rays are generated, not loaded
+    int cam_on;
     BvhView bvh;
     const float4* cache;
     unsigned int* status;
@@ -83,10 +90,51 @@ __device__ __forceinline__ void fwd_begin_segment(FwdState& s) {
     s.last_gidx = -1; s.contributor = 0; s.chunk = 0; s.log_prev = -1;
 }
 
+// Ray of pixel (i, j) as get_rays_from_ij computes it (example/utils/ray_utils.py:121-133): camera point
+// invK (j+.5, i+.5, 1), world point R^T (camera point - T), direction = world point - centre, divided
+// by (norm + 1e-8) unless z_depth. One rounding per operation, sums left to right.
+__device__ __forceinline__ void pinhole_ray(const CamConst& c, int i, int j, float* d) {
+    const float x = c.correct_pix ? xadd((float)j, 0.5f) : (float)j, y = c.correct_pix ? xadd((float)i, 0.5f) : (float)i;
+    float pc[3];
+#pragma unroll
+    for (int a = 0; a < 3; a++) pc[a] = xsub(xadd(xadd(xmul(c.invK[3 * a], x), xmul(c.invK[3 * a + 1], y)), c.invK[3 * a + 2]), c.T[a]);
+#pragma unroll
+    for (int a = 0; a < 3; a++) d[a] = xsub(xadd(xadd(xmul(c.R[a], pc[0]), xmul(c.R[3 + a], pc[1])), xmul(c.R[6 + a], pc[2])), c.c[a]);
+    if (!c.z_depth) {
+        const float n = xadd(xsqrt(xadd(xadd(xmul(d[0], d[0]), xmul(d[1], d[1])), xmul(d[2], d[2]))), 1e-8f);
+        d[0] = xdiv(d[0], n); d[1] = xdiv(d[1], n); d[2] = xdiv(d[2], n);
+    }
+}
+
+// get_rays for a batch of cameras: ray_o, ray_d (B, H, W, 3)
+__global__ void __launch_bounds__(256) k_pinhole_rays(const CamConst* __restrict__ cams, int H, int W, long long total,
+                                                      float* __restrict__ ray_o, float* __restrict__ ray_d) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const long long per = (long long)H * W;
+    const int b = (int)(idx / per);
+    const int pix = (int)(idx - b * per);
+    const CamConst& c = cams[b];
+    float d[3];
+    pinhole_ray(c, pix / W, pix % W, d);
+    ray_o[3 * idx] = c.c[0]; ray_o[3 * idx + 1] = c.c[1]; ray_o[3 * idx + 2] = c.c[2];
+    ray_d[3 * idx] = d[0]; ray_d[3 * idx + 1] = d[1]; ray_d[3 * idx + 2] = d[2];
+}
+
 __device__ __forceinline__ void fwd_init_state(const FwdParams& p, int ray, FwdState& s) {
     const dst_trace_inputs& in = p.a.in;
-    s.sox = __ldg(in.ray_o + 3 * (size_t)ray); s.soy = __ldg(in.ray_o + 3 * (size_t)ray + 1); s.soz = __ldg(in.ray_o + 3 * (size_t)ray + 2);
-    s.sdx = __ldg(in.ray_d + 3 * (size_t)ray); s.sdy = __ldg(in.ray_d + 3 * (size_t)ray + 1); s.sdz = __ldg(in.ray_d + 3 * (size_t)ray + 2);
+    if (p.cam_on) {
+        // generated here and written to the caller's ray buffers, which the backward reads
+        float d[3];
+        pinhole_ray(p.cam, ray / in.W, ray % in.W, d);
+        s.sox = p.cam.c[0]; s.soy = p.cam.c[1]; s.soz = p.cam.c[2]; s.sdx = d[0]; s.sdy = d[1]; s.sdz = d[2];
+        float* o = const_cast<float*>(in.ray_o) + 3 * (size_t)ray;
+        float* dd = const_cast<float*>(in.ray_d) + 3 * (size_t)ray;
+        o[0] = s.sox; o[1] = s.soy; o[2] = s.soz; dd[0] = s.sdx; dd[1] = s.sdy; dd[2] = s.sdz;
+    } else {
+        s.sox = __ldg(in.ray_o + 3 * (size_t)ray); s.soy = __ldg(in.ray_o + 3 * (size_t)ray + 1); s.soz = __ldg(in.ray_o + 3 * (size_t)ray + 2);
+        s.sdx = __ldg(in.ray_d + 3 * (size_t)ray); s.sdy = __ldg(in.ray_d + 3 * (size_t)ray + 1); s.sdz = __ldg(in.ray_d + 3 * (size_t)ray + 2);
+    }
     s.s_prod = 1.f; s.rgb0 = s.rgb1 = s.rgb2 = 0.f; s.bounce = 0; s.hit_count = 0; s.pad0 = 0;
     fwd_begin_segment(s);
 }
@@ -430,7 +478,55 @@ int dst_wavefront_grid(const dst_handle* h, long long slots, int threads, int pe
     return (int)(want < cap ? (want > 0 ? want : 1) : cap);
 }
 
-int dst_forward_impl(dst_handle* h, const dst_fwd_args* a, cudaStream_t st) {
+// Host part of get_rays: torch_inverse_3x3 of K (example/utils/ray_utils.py:19-60; float epsilon
+// added to the determinant) and the centre -R^T T (:107), in binary32 with the reference's order.
+static void camera_constants(const dst_camera* cam, CamConst* out) {
+    const float* K = cam->K; const float* R = cam->R; const float* T = cam->T;
+    const float r00 = K[0], r01 = K[1], r02 = K[2], r10 = K[3], r11 = K[4], r12 = K[5], r20 = K[6], r21 = K[7], r22 = K[8];
+    volatile float M[9];      // volatile: every product and sum is rounded to binary32 as written
+    M[0] = r11 * r22 - r21 * r12;
+    M[3] = -r10 * r22 + r20 * r12;
+    M[6] = r10 * r21 - r20 * r11;
+    M[1] = -r01 * r22 + r21 * r02;
+    M[4] = r00 * r22 - r20 * r02;
+    M[7] = -r00 * r21 + r20 * r01;
+    M[2] = r01 * r12 - r11 * r02;
+    M[5] = -r00 * r12 + r10 * r02;
+    M[8] = r00 * r11 - r10 * r01;
+    volatile float D = r00 * M[0] + r01 * M[3];
+    D = D + r02 * M[6];
+    const float den = D + 1.1920928955078125e-07f;
+    for (int i = 0; i < 9; i++) { out->invK[i] = M[i] / den; out->R[i] = R[i]; }
+    for (int a = 0; a < 3; a++) {
+        volatile float acc = R[a] * T[0] + R[3 + a] * T[1];
+        acc = acc + R[6 + a] * T[2];
+        out->c[a] = -acc; out->T[a] = T[a];
+    }
+    out->correct_pix = cam->correct_pix != 0; out->z_depth = cam->z_depth != 0;
+}
+
+int dst_pinhole_rays_impl(dst_handle* h, const dst_camera* cams, int n_cameras, int H, int W, float* ray_o, float* ray_d, cudaStream_t st) {
+    if (n_cameras <= 0 || n_cameras > DST_MAX_CAMERAS) return dst_set_error(h, DST_E_ARG, "camera count must be in [1, %d], got %d", DST_MAX_CAMERAS, n_cameras);
+    if (H <= 0 || W <= 0) return dst_set_error(h, DST_E_ARG, "ray grid must be non-empty, got %d x %d", H, W);
+    const long long total = (long long)n_cameras * H * W;
+    if (total > 0x3fffffffll) return dst_set_error(h, DST_E_ARG, "too many rays");
+    if (!h->cam_dev) {
+        if (cudaMalloc(&h->cam_dev, sizeof(CamConst) * DST_MAX_CAMERAS) != cudaSuccess) { cudaGetLastError(); h->cam_dev = nullptr; return dst_set_error(h, DST_E_NOMEM, "camera buffer allocation failed"); }
+    }
+    // a copy from pageable host memory has left the source buffer when the call returns, so a local array will do
+    CamConst stage[DST_MAX_CAMERAS];
+    for (int b = 0; b < n_cameras; b++) camera_constants(cams + b, stage + b);
+    DST_CUDA_TRY(h, cudaMemcpyAsync(h->cam_dev, stage, sizeof(CamConst) * n_cameras, cudaMemcpyHostToDevice, st));
+    k_pinhole_rays<<<(unsigned int)((total + 255) / 256), 256, 0, st>>>(static_cast<const CamConst*>(h->cam_dev), H, W, total, ray_o, ray_d);
+    DST_CUDA_TRY(h, cudaGetLastError());
+    return DST_OK;
+}
+
+static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera* cam, cudaStream_t st);
+int dst_forward_impl(dst_handle* h, const dst_fwd_args* a, cudaStream_t st) { return forward_common(h, a, nullptr, st); }
+int dst_forward_camera_impl(dst_handle* h, const dst_fwd_args* a, const dst_camera* cam, cudaStream_t st) { return forward_common(h, a, cam, st); }
+
+static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera* cam, cudaStream_t st) {
     int rc = dst_check_inputs(h, &a->in);
     if (rc != DST_OK) return rc;
     if (!a->out_rgb || !a->out_dpt || !a->out_acc || !a->out_norm || !a->out_dist || !a->out_aux || !a->mid_val)
@@ -438,6 +534,8 @@ int dst_forward_impl(dst_handle* h, const dst_fwd_args* a, cudaStream_t st) {
     if ((reinterpret_cast<uintptr_t>(a->mid_val) & 15) != 0) return dst_set_error(h, DST_E_ARG, "mid_val must be 16-byte aligned");
     FwdParams p;
     p.a = *a; p.bvh = dst_bvh_view(h); p.cache = h->cache; p.status = h->status;
+    p.cam_on = cam != nullptr;
+    if (cam) camera_constants(cam, &p.cam); else memset(&p.cam, 0, sizeof(p.cam));
     p.tiled = a->in.H >= 16;
     const long long slots = slots_of_grid(a->in.H, a->in.W, p.tiled != 0);
     rc = dst_ensure_wavefront(h, slots, sizeof(FwdState));
@@ -563,6 +661,7 @@ extern "C" int dst_forward_static(dst_handle* h, const dst_fwd_args* a, void* st
 
     FwdParams p;
     p.a = *a; p.bvh = dst_bvh_view(h); p.status = h->status; p.tiled = tiled;
+    p.cam_on = 0; memset(&p.cam, 0, sizeof(p.cam));
     p.cache = reinterpret_cast<const float4*>(base + ST_OFF_CACHE);
     p.state = base + ST_OFF_STATE;
     p.req = reinterpret_cast<EnumReq*>(base + ST_OFF_REQ);

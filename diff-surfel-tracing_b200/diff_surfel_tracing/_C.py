@@ -45,6 +45,13 @@ class _BwdArgs(C.Structure):
 _lib = None
 
 
+class _Camera(C.Structure):
+    _fields_ = [("K", C.c_float * 9), ("R", C.c_float * 9), ("T", C.c_float * 3), ("correct_pix", C.c_int32), ("z_depth", C.c_int32)]
+
+
+MAX_CAMERAS = 64
+
+
 def lib():
     """Loads the CUDA library on first use; raises if it has not been built."""
     global _lib
@@ -61,6 +68,10 @@ def lib():
         l.dst_forward.argtypes = [C.c_void_p, C.POINTER(_FwdArgs), C.c_void_p]
         l.dst_backward.argtypes = [C.c_void_p, C.POINTER(_BwdArgs), C.c_void_p]
         l.dst_forward_static.argtypes = [C.c_void_p, C.POINTER(_FwdArgs), C.c_void_p]
+        l.dst_surfel_quads.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]
+        l.dst_build_from_surfels.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_void_p]
+        l.dst_pinhole_rays.argtypes = [C.c_void_p, C.POINTER(_Camera), C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+        l.dst_forward_camera.argtypes = [C.c_void_p, C.POINTER(_FwdArgs), C.POINTER(_Camera), C.c_void_p]
         l.dst_status.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), C.c_void_p]
         l.dst_bvh_info.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
         l.dst_debug_knearest.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
@@ -248,7 +259,14 @@ def trace_surfels(state, training, start_from_first, ray_o, ray_d, vertices, bac
             a.hit_cap, a.hit_log, a.hit_cnt = cap, _diag["hit_log"].data_ptr(), _diag["hit_cnt"].data_ptr()
         _diag["counters"] = torch.zeros((8,), dtype=torch.int64, device=dev)
         a.counters = _diag["counters"].data_ptr()
-    _check(state, lib().dst_forward(state.handle, C.byref(a), _stream()))
+    cam = getattr(state, "next_camera", None)
+    state.next_camera = None
+    if cam is not None:       # the rays are generated by the first kernel of the call, into ray_o / ray_d
+        if keep["ray_o"].data_ptr() != ray_o.data_ptr() or keep["ray_d"].data_ptr() != ray_d.data_ptr():
+            raise RuntimeError("with a camera, ray_o and ray_d must be contiguous 16-byte aligned buffers")
+        _check(state, lib().dst_forward_camera(state.handle, C.byref(a), C.byref(cam), _stream()))
+    else:
+        _check(state, lib().dst_forward(state.handle, C.byref(a), _stream()))
     ser = C.c_uint64(0)
     _check(state, lib().dst_forward_serial(state.handle, C.byref(ser)))
     state.last_forward_serial = ser.value       # names the chunk log this call left in the handle (0: none)
@@ -370,3 +388,81 @@ def trace_surfels_static(state, training, start_from_first, ray_o, ray_d, vertic
     a.a_weights = _ptr(a_weights)
     _check(state, lib().dst_forward_static(state.handle, C.byref(a), _stream()))
     return (*outs, a_weights)
+
+
+def _surfel_params(means3D, scales, rotations):
+    if means3D.dim() != 2 or means3D.size(1) != 3:
+        raise RuntimeError("means3D must have dimensions (num_points, 3)")
+    P = means3D.size(0)
+    if tuple(scales.shape) != (P, 2) or tuple(rotations.shape) != (P, 4):
+        raise RuntimeError("scales must have dimensions (num_points, 2) and rotations (num_points, 4)")
+    return _cuda_f32(means3D.detach(), "means3D"), _cuda_f32(scales.detach(), "scales"), _cuda_f32(rotations.detach(), "rotations")
+
+
+def surfel_quads(state, means3D, scales, rotations, with_triangles=True):
+    """GaussianModel.get_triangles (example/utils/gaussian_utils.py:176-210) as one kernel:
+    v (4P,3) float32 and f (2P,3) int32 (None unless with_triangles) from the activated surfel
+    parameters the tracer also receives. No gradient flows to the parameters (the reference detaches
+    the vertices before use, example/render.py:62)."""
+    m, s, r = _surfel_params(means3D, scales, rotations)
+    P = m.size(0)
+    v = torch.empty((4 * P, 3), dtype=torch.float32, device=m.device)
+    f = torch.empty((2 * P, 3), dtype=torch.int32, device=m.device) if with_triangles else None
+    _check(state, lib().dst_surfel_quads(state.handle, m.data_ptr(), s.data_ptr(), r.data_ptr(), P, v.data_ptr(), _ptr(f), _stream()))
+    return v, f
+
+
+def build_from_surfels(state, means3D, scales, rotations, rebuild, vertices=None):
+    """get_triangles + build_acceleration_structure in one call; returns the vertex tensor (4P,3) to pass
+    to the tracer. With rebuild=0 (refit) one kernel writes the vertices and the hierarchy together.
+    `vertices`, if given, is the (4P,3) buffer to fill (so a training loop can reuse one tensor)."""
+    m, s, r = _surfel_params(means3D, scales, rotations)
+    P = m.size(0)
+    if vertices is None:
+        vertices = torch.empty((4 * P, 3), dtype=torch.float32, device=m.device)
+    elif tuple(vertices.shape) != (4 * P, 3) or vertices.dtype != torch.float32 or not vertices.is_cuda or \
+            not vertices.is_contiguous() or vertices.data_ptr() % 16:
+        raise RuntimeError("vertices must be a contiguous 16-byte aligned float32 CUDA tensor of shape (4 * num_points, 3)")
+    _check(state, lib().dst_build_from_surfels(state.handle, m.data_ptr(), s.data_ptr(), r.data_ptr(), P, vertices.data_ptr(),
+                                               int(rebuild), _stream()))
+    state._keep = (m, s, r, vertices)
+    return vertices
+
+
+def make_camera(K, R, T, correct_pix=True, z_depth=False):
+    """dst_camera from 3x3 K, 3x3 R and 3 (or 3x1) T given as tensors, arrays or nested lists."""
+    def flat(x, n):
+        if isinstance(x, torch.Tensor):
+            x = x.detach().cpu()
+        t = torch.as_tensor(x, dtype=torch.float32).reshape(-1)
+        if t.numel() != n:
+            raise RuntimeError(f"camera matrix has {t.numel()} elements, expected {n}")
+        return t.tolist()
+    c = _Camera()
+    c.K[:] = flat(K, 9)
+    c.R[:] = flat(R, 9)
+    c.T[:] = flat(T, 3)
+    c.correct_pix, c.z_depth = int(bool(correct_pix)), int(bool(z_depth))
+    return c
+
+
+def pinhole_rays(state, H, W, K, R, T, correct_pix=True, z_depth=False, device=None):
+    """get_rays (example/utils/ray_utils.py:80-136): ray_o, ray_d of shape (H,W,3), or (B,H,W,3) when
+    K, R, T carry a leading batch dimension."""
+    Kt = torch.as_tensor(K, dtype=torch.float32) if not isinstance(K, torch.Tensor) else K.detach().float().cpu()
+    batched = Kt.dim() == 3
+    B = Kt.size(0) if batched else 1
+    if B > MAX_CAMERAS:
+        raise RuntimeError(f"at most {MAX_CAMERAS} cameras per call")
+    Rt = torch.as_tensor(R, dtype=torch.float32).reshape(B, 9) if not isinstance(R, torch.Tensor) else R.detach().float().cpu().reshape(B, 9)
+    Tt = torch.as_tensor(T, dtype=torch.float32).reshape(B, 3) if not isinstance(T, torch.Tensor) else T.detach().float().cpu().reshape(B, 3)
+    Kt = Kt.reshape(B, 9)
+    cams = (_Camera * B)()
+    for b in range(B):
+        cams[b] = make_camera(Kt[b], Rt[b], Tt[b], correct_pix, z_depth)
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    shape = (B, H, W, 3) if batched else (H, W, 3)
+    ray_o = torch.empty(shape, dtype=torch.float32, device=dev)
+    ray_d = torch.empty(shape, dtype=torch.float32, device=dev)
+    _check(state, lib().dst_pinhole_rays(state.handle, cams, B, int(H), int(W), ray_o.data_ptr(), ray_d.data_ptr(), _stream()))
+    return ray_o, ray_d

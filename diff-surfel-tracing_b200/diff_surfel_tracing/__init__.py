@@ -140,3 +140,38 @@ class SurfelTracer(nn.Module):
 
         return trace_surfels(self.optix_context, self.training, start_from_first, ray_o, ray_d, vertices, means3D, grads3D,
                              shs, colors_precomp, others_precomp, opacities, scales, rotations, cov3D_precomp, tracer_settings)
+
+    # ---- the two steps that sit next to the tracer in the reference's example pipeline ----
+
+    def get_triangles(self, means3D: torch.Tensor, scales: torch.Tensor, rotations: torch.Tensor):
+        """GaussianModel.get_triangles (example/utils/gaussian_utils.py:176-210): (v (4P,3), f (2P,3) int32)."""
+        return _C.surfel_quads(self.optix_context, means3D, scales, rotations, True)
+
+    def build_from_surfels(self, means3D: torch.Tensor, scales: torch.Tensor, rotations: torch.Tensor,
+                           rebuild: bool = 1, vertices: torch.Tensor = None):
+        """get_triangles followed by build_acceleration_structure as one call; returns `v` for the tracer.
+        With rebuild=0 the quads and the refitted hierarchy come out of a single kernel."""
+        return _C.build_from_surfels(self.optix_context, means3D, scales, rotations, rebuild, vertices)
+
+    def get_rays(self, H: int, W: int, K, R, T, correct_pix: bool = True, z_depth: bool = False):
+        """get_rays (example/utils/ray_utils.py:80-136): (ray_o, ray_d), each (H,W,3) (or (B,H,W,3) for batched K, R, T)."""
+        return _C.pinhole_rays(self.optix_context, H, W, K, R, T, correct_pix, z_depth)
+
+    def forward_camera(self, H: int, W: int, K, R, T, vertices: torch.Tensor, means3D: torch.Tensor, grads3D: torch.Tensor,
+                       shs: torch.Tensor = None, colors_precomp: torch.Tensor = None, others_precomp: torch.Tensor = None,
+                       opacities: torch.Tensor = None, scales: torch.Tensor = None, rotations: torch.Tensor = None,
+                       cov3D_precomp: torch.Tensor = None, tracer_settings: SurfelTracingSettings = None,
+                       start_from_first: bool = True):
+        """forward() for the rays of one pinhole camera, generated inside the trace call instead of by a
+        separate get_rays step. Returns forward()'s tuple; the generated rays are kept in `self.last_rays`."""
+        dev = means3D.device
+        ray_o = torch.empty((H, W, 3), dtype=torch.float32, device=dev)
+        ray_d = torch.empty((H, W, 3), dtype=torch.float32, device=dev)
+        self.optix_context.next_camera = _C.make_camera(K, R, T, True, False)
+        try:
+            out = self.forward(ray_o, ray_d, vertices, means3D, grads3D, shs, colors_precomp, others_precomp, opacities,
+                               scales, rotations, cov3D_precomp, tracer_settings, start_from_first)
+        finally:
+            self.optix_context.next_camera = None
+        self.last_rays = (ray_o, ray_d)
+        return out

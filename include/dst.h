@@ -154,6 +154,47 @@ int dst_forward_serial(const dst_handle* h, unsigned long long* serial);
 #define DST_STATIC_MAX_RAYS    65536
 int dst_forward_static(dst_handle* h, const dst_fwd_args* args, void* stream);
 
+/* ---- The two steps next to the tracer in the reference's example pipeline ------------------------ */
+
+/* Quad expansion: GaussianModel.get_triangles (example/utils/gaussian_utils.py:176-210). For each
+ * surfel the 4 corners mean +- 3 s_x R[:,0] +- 3 s_y R[:,1] in the order (-,+), (-,-), (+,+), (+,-),
+ * with R = build_rotation(rotations) (quaternion (w,x,y,z), normalised inside; :214-249).
+ * means3D (P,3), scales (P,2) (already activated, as the tracer receives them), rotations (P,4);
+ * vertices (4P,3) out; triangles (2P,3) int32 out or NULL: (4g,4g+1,4g+2), (4g+1,4g+2,4g+3).
+ * vertices and rotations 16-byte aligned, scales and triangles 8-byte aligned. */
+int dst_surfel_quads(dst_handle* h, const float* means3D, const float* scales, const float* rotations, int64_t n_surfels,
+                     float* vertices, int32_t* triangles, void* stream);
+
+/* get_triangles followed by build_acceleration_structure (the pair the reference's training loop
+ * runs every iteration, example/render.py:58-63) as one call. `vertices` (4P,3) is an output the
+ * caller keeps and later hands to dst_forward / dst_backward. rebuild == 0 (refit) is one kernel:
+ * it reads the 36 bytes of parameters per surfel, writes the vertices and the hierarchy's leaf
+ * level and propagates the boxes, without reading the vertices back. rebuild != 0 expands the
+ * quads first and then builds as dst_build does. */
+int dst_build_from_surfels(dst_handle* h, const float* means3D, const float* scales, const float* rotations, int64_t n_surfels,
+                           float* vertices, int rebuild, void* stream);
+
+/* One pinhole camera as get_rays takes it (example/utils/ray_utils.py:80-136): intrinsics K (3x3),
+ * world-to-camera rotation R (3x3), translation T (3), row-major; correct_pix adds 0.5 to the pixel
+ * indices (the reference's default); z_depth leaves the directions un-normalised. */
+typedef struct dst_camera {
+    float K[9];
+    float R[9];
+    float T[3];
+    int32_t correct_pix;
+    int32_t z_depth;
+} dst_camera;
+#define DST_MAX_CAMERAS 64
+
+/* Ray generation: get_rays for n_cameras cameras (host array) of H x W pixels. ray_o, ray_d
+ * (n_cameras, H, W, 3) out, device memory. */
+int dst_pinhole_rays(dst_handle* h, const dst_camera* cameras, int n_cameras, int H, int W, float* ray_o, float* ray_d, void* stream);
+
+/* dst_forward with the rays of one camera generated in its first kernel instead of loaded:
+ * args->in.ray_o / ray_d must point to (H,W,3) buffers, which the call FILLS (the backward and the
+ * caller read them afterwards); everything else as dst_forward. Same rays as dst_pinhole_rays. */
+int dst_forward_camera(dst_handle* h, const dst_fwd_args* args, const dst_camera* camera, void* stream);
+
 /* Synchronises `stream`, returns and clears the device status word (DST_STATUS_* bits). */
 int dst_status(dst_handle* h, uint32_t* flags, void* stream);
 

@@ -1,6 +1,7 @@
 """TEST INFRASTRUCTURE ONLY: builds the CPU oracle.
 
-  liboracle.so            the restatement (surfel_oracle.cpp), always
+  liboracle.so            the restatement (surfel_oracle.cpp: the tracer; prep_oracle.cpp: quad
+                          expansion and ray generation), always
   _ref/libref_{fwd,bwd}{1,2}.so   the reference's own shader sources compiled for the host
                           (ref_driver.cpp), only where the reference tree is present
 
@@ -26,9 +27,9 @@ def _stale(out, srcs):
 
 def build_restatement(force=False):
     out = os.path.join(HERE, "liboracle.so")
-    srcs = [os.path.join(HERE, f) for f in ("surfel_oracle.cpp", "quad_enum.h", "orc_args.h")]
+    srcs = [os.path.join(HERE, f) for f in ("surfel_oracle.cpp", "prep_oracle.cpp", "quad_enum.h", "orc_args.h")]
     if force or _stale(out, srcs):
-        subprocess.check_call(COMMON + ["-Wall", "-Wno-unused", "-o", out, srcs[0]])
+        subprocess.check_call(COMMON + ["-Wall", "-Wno-unused", "-o", out, srcs[0], srcs[1]])
     return out
 
 

@@ -215,3 +215,26 @@ class Oracle:
         a.stats = _ptr(out["stats"])
         self._run(True, a, a.max_trace_depth)
         return out
+
+
+def surfel_quads(means3D, scales, rotations, with_triangles=True):
+    """get_triangles (example/utils/gaussian_utils.py:176-210): (v (4P,3) f32, f (2P,3) i32 or None)."""
+    lib = restatement_lib()
+    m, s, r = _np(means3D), _np(scales), _np(rotations)
+    P = m.shape[0]
+    v = np.empty((4 * P, 3), np.float32)
+    f = np.empty((2 * P, 3), np.int32) if with_triangles else None
+    lib.orc_surfel_quads.argtypes = [C.c_int64] + [C.c_void_p] * 5
+    lib.orc_surfel_quads(P, _ptr(m), _ptr(s), _ptr(r), _ptr(v), _ptr(f))
+    return v, f
+
+
+def pinhole_rays(H, W, K, R, T, correct_pix=True, z_depth=False):
+    """get_rays (example/utils/ray_utils.py:80-136) for one camera: (ray_o, ray_d), each (H,W,3) f32."""
+    lib = restatement_lib()
+    K, R, T = _np(K).reshape(9), _np(R).reshape(9), _np(T).reshape(3)
+    o = np.empty((H, W, 3), np.float32)
+    d = np.empty((H, W, 3), np.float32)
+    lib.orc_pinhole_rays.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+    lib.orc_pinhole_rays(H, W, _ptr(K), _ptr(R), _ptr(T), int(correct_pix), int(z_depth), _ptr(o), _ptr(d))
+    return o, d

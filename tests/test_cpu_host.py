@@ -147,6 +147,41 @@ def test_restatement_matches_golden_vectors(oracle_mod, config):
         assert hp.rel_l2(b[k][m], ref[m]) < 1e-5, (config, k)
 
 
+def test_prep_restatement_pinned_to_reference_python(oracle_mod):
+    """Quad expansion and ray generation against the outputs of the reference's own Python functions
+    (tests/golden/make_golden_prep.py ran them): vertices and origins bit for bit, un-normalised
+    directions bit for bit, normalised directions to 2e-7 relative."""
+    import make_golden_prep as mg
+    g = np.load(os.path.join(GOLDEN, "prep.npz"))
+    means, log_scales, rot, cams = mg.prep_inputs()
+    assert np.allclose(np.exp(log_scales), g["scales"], rtol=1e-6)
+    v, f = oracle_mod.surfel_quads(means, g["scales"], g["rotations"])
+    assert np.array_equal(v.view(np.uint32), g["v"].view(np.uint32))
+    assert np.array_equal(f, g["f"])
+    # build_rotation normalises internally: the raw quaternions give the same quads to rounding
+    v_raw, _ = oracle_mod.surfel_quads(means, g["scales"], rot)
+    assert np.abs(v_raw - v).max() <= 1e-5 * np.abs(v).max()
+    for c, (K, R, T) in enumerate(cams):
+        for z in (0, 1):
+            o, d = oracle_mod.pinhole_rays(mg.H_GOLDEN, mg.W_GOLDEN, K, R, T, True, bool(z))
+            go, gd = g[f"ray_o_{c}_{z}"], g[f"ray_d_{c}_{z}"]
+            assert np.array_equal(o.view(np.uint32), go.view(np.uint32))
+            if z:
+                assert np.array_equal(d.view(np.uint32), gd.view(np.uint32))
+            else:
+                assert np.abs(d - gd).max() <= 2e-7 * np.abs(gd).max()
+                assert np.allclose(np.linalg.norm(d, axis=-1), 1.0, atol=1e-6)
+
+
+def test_prep_restatement_agrees_with_workload_generators(oracle_mod):
+    """The synthetic workloads build their quads and pinhole rays with torch expressions of their own;
+    the restatement reproduces them to rounding (they feed the same tracer)."""
+    w = hp.reduced_workload(3)
+    v, f = oracle_mod.surfel_quads(w["means3D"], w["scales"], w["rotations"])
+    assert np.abs(v - w["v"].numpy()).max() <= 2e-6 * np.abs(v).max()
+    assert np.array_equal(f, w["f"].numpy())
+
+
 def test_split_rows_covers_everything():
     import shard
     for n in (1, 7, 8, 1080, 1081):
