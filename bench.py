@@ -208,6 +208,52 @@ def main():
     refit_ms = st.profile_read()["build"]
     build_ms, refit_ms = build_ms[0] / max(build_ms[1], 1), refit_ms[0] / max(refit_ms[1], 1)
 
+    # the steps on either side of the tracer in the reference's pipeline, on a handle of their own: quad
+    # expansion (get_triangles), expansion fused with the refit, the same with torch tensor ops, ray generation
+    neighbours = None
+    if rank == 0:
+        def timed(fn, n=5):
+            for _ in range(2):
+                fn()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            for _ in range(n):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / n
+        t2 = SurfelTracer().to(dev)
+        m_, s_, r_ = wc["means3D"], wc["scales"], wc["rotations"]
+        vbuf = t2.build_from_surfels(m_, s_, r_, rebuild=True)
+        quads_ms = timed(lambda: _C.surfel_quads(t2.optix_context, m_, s_, r_, True))
+        torch_ms = timed(lambda: workloads.get_triangles(m_, s_, r_))
+        st2 = t2.optix_context
+        st2.profile(True)
+        timed(lambda: t2.build_from_surfels(m_, s_, r_, rebuild=False, vertices=vbuf))
+        two = st2.profile_read()["build"]            # the library's own events around its kernels, as for bvh_refit_ms
+        two_ms = two[0] / max(two[1], 1)
+        st2.set_single_kernel_refit(True)
+        timed(lambda: t2.build_from_surfels(m_, s_, r_, rebuild=False, vertices=vbuf))
+        fused = st2.profile_read()["build"]
+        fused_ms = fused[0] / max(fused[1], 1)
+        st2.set_single_kernel_refit(False)
+        timed(lambda: t2.build_from_surfels(m_, s_, r_, rebuild=True, vertices=vbuf))
+        fused_b = st2.profile_read()["build"]
+        fused_build_ms = fused_b[0] / max(fused_b[1], 1)
+        Kc, Rc, Tc = workloads.pinhole_camera(1080, 1920, 50.0, (4.0, 0.0, 0.0))
+        rays_ms = timed(lambda: t2.get_rays(1080, 1920, Kc, Rc, Tc))
+        peak_n, _ = measured_peak_hbm()
+        qb, rb = (36 + 48 + 24) * P, 24 * 1080 * 1920
+        neighbours = {"quad_expansion": {"ms": quads_ms, "algorithmic_bytes": qb, "achieved_gbs": qb / quads_ms / 1e6,
+                                         "frac_of_hbm_peak": qb / quads_ms / 1e6 / peak_n, "torch_ops_ms": torch_ms},
+                      "refit_from_surfels_ms": two_ms, "refit_from_surfels_single_kernel_ms": fused_ms,
+                      "build_from_surfels_ms": fused_build_ms,
+                      "torch_expansion_then_refit_ms": torch_ms + refit_ms,
+                      "ray_generation_1080p": {"ms": rays_ms, "algorithmic_bytes": rb, "achieved_gbs": rb / rays_ms / 1e6,
+                                               "frac_of_hbm_peak": rb / rays_ms / 1e6 / peak_n}}
+        del t2, vbuf
+
     e = torch.empty((0,), device=dev)
     shs = wc["shs"] if wc["shs"] is not None else e
     cols = wc["colors_precomp"] if wc["colors_precomp"] is not None else e
@@ -354,7 +400,7 @@ def main():
                            "max_trace_depth": w["max_trace_depth"], "specular_threshold": w["specular_threshold"],
                            "parallelism": f"one 1080p camera batch per GPU x{world}, hierarchy replicated, 1 all-reduce/step" if world > 1 else "1 GPU",
                            "l2": "inputs larger than L2 (hierarchy + surfel records + SH rows > 126 MB), no flush"},
-                "bvh_build_ms": build_ms, "bvh_refit_ms": refit_ms, "device_status": status,
+                "bvh_build_ms": build_ms, "bvh_refit_ms": refit_ms, "device_status": status, "neighbours": neighbours,
                 "per_ray": {"forward": per_ray(cf), "backward": per_ray(cb_)},
                 "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
                 "gpu_launches": 5 * args.steps, "clocks": clocks}

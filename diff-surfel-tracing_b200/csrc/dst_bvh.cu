@@ -485,10 +485,14 @@ int dst_bvh_build_impl(dst_handle* h, const float* v, int64_t P, int rebuild, cu
         // 8 passes: the sorted data is back in keys / vals
         if (n > 1) k_karras<<<(n - 1 + tpb - 1) / tpb, tpb, 0, st>>>(h->keys, n, h->nodes, h->leaf_parent, h->node_parent, h->node_first, h->node_count);
         h->P = P; h->nrefs = P;
+    } else if (from_surfels && !h->single_kernel_refit) {
+        // measured at 3M surfels: the coalesced expansion pass (0.07 ms) plus the refit's gathered re-read of the
+        // vertices is faster than one kernel that scatters 48-byte vertex writes in Morton order (0.57 vs 0.64 ms)
+        k_surfel_quads<<<grid, tpb, 0, st>>>(src, n, nullptr);
     }
     DST_CUDA_TRY(h, cudaMemsetAsync(h->arrive, 0, 4 * (size_t)(n > 1 ? n - 1 : 1), st));
     if (n == 1) k_single_leaf<<<1, 1, 0, st>>>(h->nodes, h->leaf_parent, h->node_parent, h->node_first, h->node_count, h->arrive);
-    if (from_surfels && !rebuild)
+    if (from_surfels && !rebuild && h->single_kernel_refit)
         k_refit<true><<<grid, tpb, 0, st>>>(v, src, n, h->vals, h->nodes, h->leaf_parent, h->node_parent, h->node_first, h->node_count, h->child_cost,
                                             h->arrive, h->quads, h->leaf_gid, h->header);
     else

@@ -77,6 +77,7 @@ struct dst_handle {
     float4* cache; int64_t cache_cap;
     float* arena;  int64_t arena_cap;
     void* cam_dev;      // camera constants of the last ray-generation call
+    int single_kernel_refit;   // dst_build_from_surfels(rebuild = 0): expand the quads inside the refit kernel
     int sm_count;
     // ray scratch of the wavefront trace (grow-only): state records, enumeration requests, hit buffers, live lists
     void* wf_state; size_t wf_state_bytes; void* wf_req; unsigned long long* wf_kbuf; int* wf_kcnt; int* wf_list[2]; int* wf_counts;

@@ -153,6 +153,10 @@ class OptiXStateWrapper:
         """Upper limit on the chunk-log size in records of 136 bytes (0: built-in limit only)."""
         _check(self, lib().dst_set_option(self.handle, 3, int(n)))
 
+    def set_single_kernel_refit(self, on):
+        """build_from_surfels(rebuild=0): expand the quads inside the refit kernel (one launch) instead of before it."""
+        _check(self, lib().dst_set_option(self.handle, 4, int(bool(on))))
+
     def set_chunk_log(self, on):
         """Keep (default) or drop the per-ray chunk log training forwards leave for the backward (about 1.6 KB per ray)."""
         _check(self, lib().dst_set_option(self.handle, 2, int(bool(on))))
@@ -414,7 +418,7 @@ def surfel_quads(state, means3D, scales, rotations, with_triangles=True):
 
 def build_from_surfels(state, means3D, scales, rotations, rebuild, vertices=None):
     """get_triangles + build_acceleration_structure in one call; returns the vertex tensor (4P,3) to pass
-    to the tracer. With rebuild=0 (refit) one kernel writes the vertices and the hierarchy together.
+    to the tracer.
     `vertices`, if given, is the (4P,3) buffer to fill (so a training loop can reuse one tensor)."""
     m, s, r = _surfel_params(means3D, scales, rotations)
     P = m.size(0)

@@ -149,8 +149,7 @@ class SurfelTracer(nn.Module):
 
     def build_from_surfels(self, means3D: torch.Tensor, scales: torch.Tensor, rotations: torch.Tensor,
                            rebuild: bool = 1, vertices: torch.Tensor = None):
-        """get_triangles followed by build_acceleration_structure as one call; returns `v` for the tracer.
-        With rebuild=0 the quads and the refitted hierarchy come out of a single kernel."""
+        """get_triangles followed by build_acceleration_structure as one call; returns `v` for the tracer."""
         return _C.build_from_surfels(self.optix_context, means3D, scales, rotations, rebuild, vertices)
 
     def get_rays(self, H: int, W: int, K, R, T, correct_pix: bool = True, z_depth: bool = False):

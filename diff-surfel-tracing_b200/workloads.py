@@ -22,7 +22,7 @@ def build_rotation(q: torch.Tensor) -> torch.Tensor:
     """Rotation matrices of quaternions stored as (w, x, y, z); columns 0/1 are the tangents."""
     q = q / q.norm(dim=-1, keepdim=True)
     r, x, y, z = q[:, 0], q[:, 1], q[:, 2], q[:, 3]
-    R = torch.empty((q.shape[0], 3, 3), dtype=q.dtype)
+    R = torch.empty((q.shape[0], 3, 3), dtype=q.dtype, device=q.device)
     R[:, 0, 0] = 1 - 2 * (y * y + z * z)
     R[:, 0, 1] = 2 * (x * y - r * z)
     R[:, 0, 2] = 2 * (x * z + r * y)
@@ -40,10 +40,10 @@ def get_triangles(means3D: torch.Tensor, scales: torch.Tensor, rotations: torch.
     R = build_rotation(rotations)
     a = R[:, :, 0] * scales[:, 0:1]
     b = R[:, :, 1] * scales[:, 1:2]
-    corners = torch.tensor([[-1.0, 1.0], [-1.0, -1.0], [1.0, 1.0], [1.0, -1.0]], dtype=means3D.dtype) * 3
+    corners = torch.tensor([[-1.0, 1.0], [-1.0, -1.0], [1.0, 1.0], [1.0, -1.0]], dtype=means3D.dtype, device=means3D.device) * 3
     v = means3D[:, None, :] + corners[None, :, 0:1] * a[:, None, :] + corners[None, :, 1:2] * b[:, None, :]
     v = v.reshape(-1, 3).contiguous()
-    idx = torch.arange(v.shape[0]).reshape(-1, 4)
+    idx = torch.arange(v.shape[0], device=v.device).reshape(-1, 4)
     f = torch.stack([idx[:, :3], idx[:, 1:]], dim=1).reshape(-1, 3).int().contiguous()
     return v, f
 
@@ -74,6 +74,18 @@ def pinhole_rays(H: int, W: int, fovx_deg: float, cam_pos, target=(0.0, 0.0, 0.0
     d = d / d.norm(dim=-1, keepdim=True)
     o = cam_pos.expand(H, W, 3).contiguous()
     return o, d.contiguous()
+
+
+def pinhole_camera(H: int, W: int, fovx_deg: float, cam_pos, target=(0.0, 0.0, 0.0)):
+    """K (3,3), R (3,3), T (3,) of the camera pinhole_rays() describes, in the reference's convention
+    (world-to-camera R, T; example/utils/ray_utils.py:80-136), as float32 tensors."""
+    cam_pos = torch.as_tensor(cam_pos, dtype=torch.float32)
+    right, down, fwd = _look_at(cam_pos, torch.as_tensor(target, dtype=torch.float32))
+    R = torch.stack([right, down, fwd], dim=0)
+    T = -(R @ cam_pos)
+    fx = 0.5 * W / math.tan(0.5 * math.radians(fovx_deg))
+    K = torch.tensor([[fx, 0.0, 0.5 * W], [0.0, fx, 0.5 * H], [0.0, 0.0, 1.0]], dtype=torch.float32)
+    return K, R, T
 
 
 def _rand_quat(n, g):

@@ -167,10 +167,10 @@ int dst_surfel_quads(dst_handle* h, const float* means3D, const float* scales, c
 
 /* get_triangles followed by build_acceleration_structure (the pair the reference's training loop
  * runs every iteration, example/render.py:58-63) as one call. `vertices` (4P,3) is an output the
- * caller keeps and later hands to dst_forward / dst_backward. rebuild == 0 (refit) is one kernel:
- * it reads the 36 bytes of parameters per surfel, writes the vertices and the hierarchy's leaf
- * level and propagates the boxes, without reading the vertices back. rebuild != 0 expands the
- * quads first and then builds as dst_build does. */
+ * caller keeps and later hands to dst_forward / dst_backward. The quads are expanded by one
+ * coalesced kernel (36 bytes of parameters in, 48 bytes of vertices out per surfel) and the
+ * hierarchy is then built or refitted as dst_build does; with DST_OPT_SINGLE_KERNEL_REFIT the refit
+ * expands the quads itself and never reads the vertices back. */
 int dst_build_from_surfels(dst_handle* h, const float* means3D, const float* scales, const float* rotations, int64_t n_surfels,
                            float* vertices, int rebuild, void* stream);
 
@@ -210,6 +210,10 @@ int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t*
 /* DST_OPT_CHUNK_LOG_MAX_RECORDS: upper limit on the records (136 bytes each) the chunk log may hold; 0 = only the
  * built-in limit. Rays whose chunks did not fit are re-traced by the backward, with the same result. */
 #define DST_OPT_CHUNK_LOG_MAX_RECORDS 3
+/* dst_build_from_surfels with rebuild == 0: non-zero expands the quads inside the refit kernel (one
+ * launch, no re-read of the vertices); zero (default) runs the expansion kernel and then the refit,
+ * which is faster on large scenes because the expansion's writes are coalesced. Same results. */
+#define DST_OPT_SINGLE_KERNEL_REFIT 4
 int dst_set_option(dst_handle* h, int option, int64_t value);
 
 /* Timing of the main kernels with CUDA events on the launching stream. While enabled, every

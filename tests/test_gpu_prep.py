@@ -69,12 +69,14 @@ def test_surfel_quads_match_reference_golden_and_oracle(C, oracle_mod, golden):
     assert np.array_equal(_bits(v.cpu().numpy()), _bits(want))
 
 
-def test_build_from_surfels_equals_expand_then_build(C, oracle_mod):
+@pytest.mark.parametrize("single_kernel", [False, True], ids=["expand-then-refit", "single-kernel-refit"])
+def test_build_from_surfels_equals_expand_then_build(C, oracle_mod, single_kernel):
     """One call from the parameters == get_triangles + build_acceleration_structure, for build and for refit."""
     w = hp.reduced_workload(3)
     wc = hp.to_cuda(w)
     v_ref, _ = oracle_mod.surfel_quads(w["means3D"], w["scales"], w["rotations"], with_triangles=False)
     st = C.OptiXStateWrapper("")
+    st.set_single_kernel_refit(single_kernel)
     v = C.build_from_surfels(st, wc["means3D"], wc["scales"], wc["rotations"], 1)
     assert np.array_equal(_bits(v.cpu().numpy()), _bits(v_ref))
     st_b = C.OptiXStateWrapper("")
@@ -85,7 +87,7 @@ def test_build_from_surfels_equals_expand_then_build(C, oracle_mod):
     for k in ("rgb", "dpt", "acc", "norm", "aux", "mid"):
         assert torch.equal(out_a[k], out_b[k]), k
     assert torch.allclose(out_a["wet"], out_b["wet"], rtol=1e-4, atol=1e-6)      # float atomics: the order differs run to run
-    # refit: the surfels move; the fused kernel writes the new vertices into the same tensor
+    # refit: the surfels move; the new vertices are written into the same tensor
     gen = torch.Generator().manual_seed(5)
     means2 = w["means3D"] + 0.01 * torch.randn(w["means3D"].shape, generator=gen)
     rot2 = w["rotations"] + 0.02 * torch.randn(w["rotations"].shape, generator=gen)
@@ -184,3 +186,23 @@ def test_forward_camera_equals_forward_on_generated_rays(C):
     for k in la:
         assert hp.rel_l2(la[k].grad.cpu().numpy(), lb[k].grad.cpu().numpy()) < 1e-3, k      # fp32 atomics: order differs run to run
     assert tracer.optix_context.status() == 0
+
+
+def test_example_render_script(tmp_path):
+    """The counterpart of the reference's example/render.py runs end to end on a synthetic scene and writes its images."""
+    import importlib.util
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "diff-surfel-tracing_b200", "example", "render.py")
+    spec = importlib.util.spec_from_file_location("example_render", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    out = str(tmp_path / "render")
+    status = mod.main(["--result_dir", out, "--surfels", "30000", "--height", "54", "--width", "96", "--frames", "2",
+                       "--max_trace_depth", "1", "--specular_threshold", "0.5"])
+    assert status == 0
+    for sub in ("RENDER", "DEPTH", "NORMAL"):
+        files = sorted(os.listdir(os.path.join(out, sub)))
+        assert len(files) == 2 and all(os.path.getsize(os.path.join(out, sub, f)) > 100 for f in files), sub
+    from PIL import Image
+    img = np.asarray(Image.open(os.path.join(out, "RENDER", "0000.png")))
+    assert img.shape == (54, 96, 3) and img.max() > 0
