@@ -390,6 +390,11 @@ def main():
         except Exception as ex:  # the baseline is a report, never a reason to lose the GPU numbers
             cpu_baseline = {"value": None, "unit": "Mrays/s", "cores": os.cpu_count(), "kind": "port", "sample": f"failed: {ex}"}
 
+    # kernels of this library enqueued per step: forward = surfel records + ray init + 48 x (gather, composite) + tail;
+    # backward = surfel records + logged re-composite + 48 x (gather, composite) + tail + unpack (rounds on an empty
+    # list return at once); calls below the wavefront threshold run no rounds
+    rounds = 48 if R >= 131072 else 0
+    launches_per_step = (3 + 2 * rounds) + (4 + 2 * rounds)
     if rank == 0:
         per_ray = lambda c: {"segments": c[0] / R, "enumerations": c[1] / R, "nodes_visited": c[2] / R, "quads_tested": c[3] / R,
                              "slots_evaluated": c[4] / R, "contributions": c[5] / R}
@@ -403,7 +408,7 @@ def main():
                 "bvh_build_ms": build_ms, "bvh_refit_ms": refit_ms, "device_status": status, "neighbours": neighbours,
                 "per_ray": {"forward": per_ray(cf), "backward": per_ray(cb_)},
                 "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-                "gpu_launches": 5 * args.steps, "clocks": clocks}
+                "gpu_launches": launches_per_step * args.steps, "clocks": clocks}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
