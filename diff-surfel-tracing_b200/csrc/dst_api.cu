@@ -62,6 +62,7 @@ int dst_create(int device, dst_handle** out) {
     h->device = device;
     h->wf_min_rays = 1 << 17;
     h->log_enabled = 1;
+    h->refill_mode = -1;
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete h; dst_global_error("dst_create: cudaGetDeviceProperties failed"); return DST_E_CUDA; }
     h->sm_count = prop.multiProcessorCount;
@@ -86,7 +87,7 @@ int dst_destroy(dst_handle* h) {
     if (h->log_needed_host) cudaFreeHost(h->log_needed_host);
     if (h->log_needed_event) cudaEventDestroy(h->log_needed_event);
     cudaFree(h->log_keys); cudaFree(h->log_hdr); cudaFree(h->log_count); cudaFree(h->log_seg_head); cudaFree(h->log_ray_ok);
-    cudaFree(h->wf_state); cudaFree(h->wf_req); cudaFree(h->wf_kbuf); cudaFree(h->wf_kcnt); cudaFree(h->wf_list[0]); cudaFree(h->wf_list[1]); cudaFree(h->wf_counts);
+    cudaFree(h->wf_state); cudaFree(h->wf_req); cudaFree(h->wf_kbuf); cudaFree(h->wf_kcnt); cudaFree(h->wf_list[0]); cudaFree(h->wf_list[1]); cudaFree(h->wf_counts); cudaFree(h->wf_claim);
     for (int k = 0; k < 3; k++) {
         if (h->ev[k]) { for (int i = 0; i < 2 * DST_PROF_SLOTS; i++) cudaEventDestroy(h->ev[k][i]); delete[] h->ev[k]; }
     }
@@ -192,6 +193,7 @@ int dst_set_option(dst_handle* h, int option, int64_t value) {
     switch (option) {
         case DST_OPT_WAVEFRONT_MIN_RAYS: h->wf_min_rays = value < 0 ? 0 : value; return DST_OK;
         case DST_OPT_CHUNK_LOG_MAX_RECORDS: h->log_max_records = value < 0 ? 0 : value; h->log_serial = 0; return DST_OK;
+        case DST_OPT_GATHER_REFILL: h->refill_mode = value < 0 ? -1 : (value != 0); return DST_OK;
         case DST_OPT_SINGLE_KERNEL_REFIT: h->single_kernel_refit = value != 0; return DST_OK;
         case DST_OPT_CHUNK_LOG: h->log_enabled = value != 0; if (!h->log_enabled) h->log_serial = 0; return DST_OK;
         default: return dst_set_error(h, DST_E_ARG, "unknown option %d", option);

@@ -128,7 +128,7 @@ __device__ __forceinline__ void bwd_store_state(void* base, int ray, const BwdSt
 __device__ __forceinline__ void bwd_request(const BwdState& s, EnumReq& q) {
     if (s.chunk == 0) { q.ox = s.sox; q.oy = s.soy; q.oz = s.soz; }
     else { q.ox = xadd(s.sox, xmul(s.offset, s.sdx)); q.oy = xadd(s.soy, xmul(s.offset, s.sdy)); q.oz = xadd(s.soz, xmul(s.offset, s.sdz)); }
-    q.dx = s.sdx; q.dy = s.sdy; q.dz = s.sdz; q.kmax0 = DST_T_MAX; q.pad = 0.f;
+    q.dx = s.sdx; q.dy = s.sdy; q.dz = s.sdz; q.kmax0 = DST_T_MAX; q.pad = s.seg > 0 ? 1.f : 0.f;       // pad: the ray is on a reflected segment
 }
 
 // Finds the next segment to differentiate, from segment `start` downwards (backward.cu:706-802):
@@ -597,8 +597,10 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
                          h->log_depth == a->in.max_trace_depth;
     p.log_keys = h->log_keys; p.log_hdr = h->log_hdr; p.log_seg_head = h->log_seg_head; p.log_ray_ok = h->log_ray_ok;
     p.log_seg_stride = a->in.max_trace_depth + 1;
-    DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 2 * (DST_WF_ROUNDS + 2), st));
+    DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 3 * (DST_WF_ROUNDS + 2), st));
     const bool wave = slots >= h->wf_min_rays;
+    const int refill = h->refill_mode < 0 ? (a->in.max_trace_depth >= 2) : (h->refill_mode != 0);
+    if (wave) DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_claim, 0, 4 * (size_t)slots, st));
     p.rounds = wave ? DST_WF_ROUNDS : 0;
     p.min_count = wave ? (int)(slots / 512 > 2048 ? slots / 512 : 2048) : 1;
     dst_prof_mark(h, 2, 0, st);
@@ -614,10 +616,12 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
     const int g_enum = dst_wavefront_grid(h, slots, ENUM_THREADS, 10), g_shade = dst_wavefront_grid(h, slots, BWD_THREADS, 4);
     for (int r = 0; r < p.rounds; r++) {
         if (diag) {
-            k_enum<true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters);
+            if (refill) k_enum<true, true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
+            else k_enum<true, false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
             k_bwd_shade<true><<<g_shade, BWD_THREADS, 0, st>>>(p, r);
         } else {
-            k_enum<false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr);
+            if (refill) k_enum<false, true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
+            else k_enum<false, false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
             k_bwd_shade<false><<<g_shade, BWD_THREADS, 0, st>>>(p, r);
         }
     }

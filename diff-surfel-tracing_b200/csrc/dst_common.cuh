@@ -77,10 +77,11 @@ struct dst_handle {
     float4* cache; int64_t cache_cap;
     float* arena;  int64_t arena_cap;
     void* cam_dev;      // camera constants of the last ray-generation call
+    int refill_mode;           // gather kernel: idle lanes take extra reflected-segment rays (-1: when max_trace_depth >= 2, 0: never, 1: always)
     int single_kernel_refit;   // dst_build_from_surfels(rebuild = 0): expand the quads inside the refit kernel
     int sm_count;
     // ray scratch of the wavefront trace (grow-only): state records, enumeration requests, hit buffers, live lists
-    void* wf_state; size_t wf_state_bytes; void* wf_req; unsigned long long* wf_kbuf; int* wf_kcnt; int* wf_list[2]; int* wf_counts;
+    void* wf_state; size_t wf_state_bytes; void* wf_req; unsigned long long* wf_kbuf; int* wf_kcnt; int* wf_list[2]; int* wf_counts; int* wf_claim;
     long long wf_cap;
     long long wf_min_rays;        // launches with fewer rays skip the wavefront rounds
     // chunk log: the 16-hit chunks every ray composited in the last training forward, chained per ray and segment,

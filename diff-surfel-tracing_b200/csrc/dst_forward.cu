@@ -143,7 +143,7 @@ __device__ __forceinline__ void fwd_init_state(const FwdParams& p, int ray, FwdS
 __device__ __forceinline__ void fwd_request(const FwdState& s, EnumReq& q) {
     if (s.chunk == 0) { q.ox = s.sox; q.oy = s.soy; q.oz = s.soz; }
     else { q.ox = xadd(s.sox, xmul(s.offset, s.sdx)); q.oy = xadd(s.soy, xmul(s.offset, s.sdy)); q.oz = xadd(s.soz, xmul(s.offset, s.sdz)); }
-    q.dx = s.sdx; q.dy = s.sdy; q.dz = s.sdz; q.kmax0 = DST_T_MAX; q.pad = 0.f;
+    q.dx = s.sdx; q.dy = s.sdy; q.dz = s.sdz; q.kmax0 = DST_T_MAX; q.pad = s.bounce > 0 ? 1.f : 0.f;       // pad: the ray is on a reflected segment
 }
 
 // Composites one gathered chunk (forward.cu:197-306) and, when the segment ends, finishes it
@@ -424,7 +424,7 @@ int dst_prepare_cache(dst_handle* h, const dst_trace_inputs* in, cudaStream_t st
 int dst_ensure_wavefront(dst_handle* h, long long slots, size_t state_bytes) {
     if (slots <= h->wf_cap && state_bytes <= h->wf_state_bytes) return DST_OK;
     cudaFree(h->wf_state); cudaFree(h->wf_req); cudaFree(h->wf_kbuf); cudaFree(h->wf_kcnt); cudaFree(h->wf_list[0]); cudaFree(h->wf_list[1]);
-    cudaFree(h->wf_counts);
+    cudaFree(h->wf_counts); cudaFree(h->wf_claim); h->wf_claim = nullptr;
     h->wf_state = nullptr; h->wf_req = nullptr; h->wf_kbuf = nullptr; h->wf_kcnt = nullptr; h->wf_list[0] = h->wf_list[1] = nullptr; h->wf_counts = nullptr;
     h->wf_cap = 0; h->wf_state_bytes = 0;
     const long long cap = slots > h->wf_cap ? slots + slots / 16 + 1024 : h->wf_cap;
@@ -435,7 +435,8 @@ int dst_ensure_wavefront(dst_handle* h, long long slots, size_t state_bytes) {
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_kcnt, 4 * (size_t)cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_list[0], 4 * (size_t)cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_list[1], 4 * (size_t)cap);
-    if (e == cudaSuccess) e = cudaMalloc(&h->wf_counts, 4 * 2 * (DST_WF_ROUNDS + 2));
+    if (e == cudaSuccess) e = cudaMalloc(&h->wf_counts, 4 * 3 * (DST_WF_ROUNDS + 2));
+    if (e == cudaSuccess) e = cudaMalloc(&h->wf_claim, 4 * (size_t)cap);
     if (e != cudaSuccess) { cudaGetLastError(); return dst_set_error(h, DST_E_NOMEM, "ray scratch allocation for %lld rays failed: %s", slots, cudaGetErrorString(e)); }
     h->wf_cap = cap; h->wf_state_bytes = sb;
     return DST_OK;
@@ -561,19 +562,23 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
     }
     // small launches go straight to the per-ray kernel; large ones run wavefront rounds until few rays are left
     const bool wave = slots >= h->wf_min_rays;
+    const int refill = h->refill_mode < 0 ? (a->in.max_trace_depth >= 2) : (h->refill_mode != 0);
     p.rounds = wave ? DST_WF_ROUNDS : 0;
     p.min_count = wave ? (int)(slots / 512 > 2048 ? slots / 512 : 2048) : 1;
     const bool diag = a->hit_log || a->hit_cnt || a->counters;
-    DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 2 * (DST_WF_ROUNDS + 2), st));
+    DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 3 * (DST_WF_ROUNDS + 2), st));
+    if (wave) DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_claim, 0, 4 * (size_t)slots, st));
     dst_prof_mark(h, 1, 0, st);
     k_fwd_init<<<(unsigned int)((slots + 255) / 256), 256, 0, st>>>(p, slots);
     const int g_enum = dst_wavefront_grid(h, slots, ENUM_THREADS, 12), g_shade = dst_wavefront_grid(h, slots, SHADE_THREADS, 8);
     for (int r = 0; r < p.rounds; r++) {
         if (diag) {
-            k_enum<true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters);
+            if (refill) k_enum<true, true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
+            else k_enum<true, false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
             k_fwd_shade<true><<<g_shade, SHADE_THREADS, 0, st>>>(p, r);
         } else {
-            k_enum<false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr);
+            if (refill) k_enum<false, true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
+            else k_enum<false, false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
             k_fwd_shade<false><<<g_shade, SHADE_THREADS, 0, st>>>(p, r);
         }
     }

@@ -323,14 +323,28 @@ __device__ __forceinline__ RaySlab make_slab(float ox, float oy, float oz, float
 //                  node phase (kept while at least DST_NODE_VOTE lanes have node work) and a leaf phase.
 // Pruning uses each lane's own 16th-nearest distance throughout, so the hit set is exactly that of
 // an independent walk per ray. Blocks are persistent and take batches from a shared cursor.
+//   refill         a batch that gave up the shared walk (incoherent rays, typically after a bounce) runs
+//                  lane by lane, and lanes finish at very different times. While at least DST_STEAL_MIN_BUSY
+//                  lanes are still walking, a lane that is done publishes its chunk and takes one more
+//                  ray from the BACK of the list (second cursor) for a walk of its own from the root.
+//                  List positions are claimed with atomicMax(claim[pos], tag) (tag = round + 1; the
+//                  claim words are zeroed once per call), so front batches and refills never share a ray.
+//                  Only rays on reflected segments are taken, and only when the caller asks for it
+//                  (`refill`): a ray walked alone pays for every box around its origin by itself, which
+//                  the shared start of a batch spreads over 32 rays. Measured: with two bounces on 6M
+//                  surfels the forward gets a third faster, with one bounce on 3M surfels 7 % slower.
 #define DST_SHARED_STACK 64
 #define DST_ENUM_STACK 160       // private stack of k_enum: subtrees deferred by the shared walk + one depth-first descent
 #define DST_ENUM_DEFER 64        // the shared walk pauses to drain the private stacks when a lane holds this many entries
-template <bool COUNT>
+#ifndef DST_STEAL_MIN_BUSY
+#define DST_STEAL_MIN_BUSY 26    // idle lanes take extra rays only while this many lanes of the warp are still walking
+#endif
+template <bool COUNT, bool REFILL>
 __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumReq* __restrict__ req, const int* __restrict__ list,
                                                        const int* __restrict__ count_ptr, int* cursor, int min_count,
                                                        unsigned long long* __restrict__ kbuf, int* __restrict__ kcnt,
-                                                       unsigned int* status, unsigned long long* counters) {
+                                                       unsigned int* status, unsigned long long* counters,
+                                                       int* back_cursor, int* claim, int tag) {
     __shared__ unsigned long long kshared[DST_CHUNK * ENUM_THREADS];
     __shared__ int sstack[ENUM_THREADS / 32][DST_SHARED_STACK];
     const int total = *count_ptr;
@@ -404,17 +418,35 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
         base = __shfl_sync(FULL, base, 0);
         if (base >= total) break;
         const int idx = base + lane;
-        const int ray = idx < total ? list[idx] : -1;
+        int ray = (idx < total && (!REFILL || atomicMax(claim + idx, tag) < tag)) ? list[idx] : -1;
         bool active = false;
-        n = 0; sp = 0; kmax = -1.0f;
-        if (ray >= 0) {
-            const float4 r0 = __ldg(reinterpret_cast<const float4*>(req + ray)), r1 = __ldg(reinterpret_cast<const float4*>(req + ray) + 1);
-            ox = r0.x; oy = r0.y; oz = r0.z; dx = r0.w; dy = r1.x; dz = r1.y;
-            sl = make_slab(ox, oy, oz, dx, dy, dz, absmax);
-            active = sl.valid;
-            if (active) kmax = r1.z;
-            if (COUNT) tc.enums++;
-        }
+        // takes up `ray`: request, slab constants, empty k-buffer and stack
+        auto begin_ray = [&]() {
+            n = 0; sp = 0; kmax = -1.0f;
+            active = false;
+            if (ray >= 0) {
+                const float4 r0 = __ldg(reinterpret_cast<const float4*>(req + ray)), r1 = __ldg(reinterpret_cast<const float4*>(req + ray) + 1);
+                ox = r0.x; oy = r0.y; oz = r0.z; dx = r0.w; dy = r1.x; dz = r1.y;
+                sl = make_slab(ox, oy, oz, dx, dy, dz, absmax);
+                active = sl.valid;
+                if (active) kmax = r1.z;
+                if (COUNT) tc.enums++;
+            }
+        };
+        // writes the chunk of `ray` and lets go of it
+        auto publish = [&]() {
+            if (ray >= 0) {
+                kcnt[ray] = n;
+                ulonglong2* out = reinterpret_cast<ulonglong2*>(kbuf + (size_t)ray * DST_CHUNK);
+#pragma unroll
+                for (int k = 0; k < DST_CHUNK / 2; k++) {
+                    if (2 * k < n) out[k] = make_ulonglong2(kb[(2 * k) * KS], kb[(2 * k + 1) * KS]);
+                }
+            }
+            ray = -1;
+        };
+        begin_ray();
+        bool bailed = false, dry = false;      // warp gave up the shared walk / the back of the list is used up (per lane)
         int ssp = 0, scur = __any_sync(FULL, active) ? 0 : DONE;     // shared walk: stack pointer and current link (uniform)
         int s_tests = 0, s_wanted = 0;                                // child tests made together / of them wanted by their lane
         for (;;) {
@@ -430,6 +462,7 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
                         for (int e = 0; e < ssp; e++) push(sstack[wid][e], 0.0f);
                     }
                     ssp = 0; scur = DONE;
+                    bailed = true;
                     break;
                 }
                 if (scur >= 0) {
@@ -477,7 +510,22 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
         }
         // ---- private phase ----
         int cur = active ? pop() : DONE;
-        while (__any_sync(FULL, cur != DONE)) {
+        for (;;) {
+            const unsigned int busy = __ballot_sync(FULL, cur != DONE);
+            if (busy == 0u) break;
+            if (REFILL && bailed && scur == DONE && __popc(busy) >= DST_STEAL_MIN_BUSY && cur == DONE && !dry) {
+                // this lane is done while most of the warp still walks: publish and take a ray from the back of the list
+                publish();
+                const int pos = total - 1 - atomicAdd(back_cursor, 1);
+                // only rays on a reflected segment are taken: primary rays of neighbouring pixels are far cheaper walked together
+                const int cand = pos >= 0 ? list[pos] : -1;
+                const bool take = pos >= 0 && (cand < 0 || __ldg(&req[cand].pad) != 0.0f);
+                if (take && atomicMax(claim + pos, tag) < tag) {
+                    ray = cand;
+                    begin_ray();
+                    if (active) cur = 0;        // walk of its own from the root
+                } else dry = true;              // a primary ray, or the front batches have reached this position
+            }
             // node phase: kept while at least DST_NODE_VOTE lanes have node work or nobody holds a leaf
             for (;;) {
                 const bool is_node = (unsigned int)cur < (unsigned int)DONE;
@@ -506,14 +554,7 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
         if (scur == DONE) break;
         }
         // ---- publish the chunks of this batch ----
-        if (ray >= 0) {
-            kcnt[ray] = n;
-            ulonglong2* out = reinterpret_cast<ulonglong2*>(kbuf + (size_t)ray * DST_CHUNK);
-#pragma unroll
-            for (int k = 0; k < DST_CHUNK / 2; k++) {
-                if (2 * k < n) out[k] = make_ulonglong2(kb[(2 * k) * KS], kb[(2 * k + 1) * KS]);
-            }
-        }
+        publish();
     }
     if (COUNT && counters) { atomicAdd(counters + 1, tc.enums); atomicAdd(counters + 2, tc.nodes); atomicAdd(counters + 3, tc.quads); }
 }

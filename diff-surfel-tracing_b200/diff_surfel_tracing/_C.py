@@ -153,6 +153,10 @@ class OptiXStateWrapper:
         """Upper limit on the chunk-log size in records of 136 bytes (0: built-in limit only)."""
         _check(self, lib().dst_set_option(self.handle, 3, int(n)))
 
+    def set_gather_refill(self, mode):
+        """Gather kernel scheduling: 1 idle lanes take extra reflected-segment rays, 0 never, -1 automatic (default)."""
+        _check(self, lib().dst_set_option(self.handle, 5, int(mode)))
+
     def set_single_kernel_refit(self, on):
         """build_from_surfels(rebuild=0): expand the quads inside the refit kernel (one launch) instead of before it."""
         _check(self, lib().dst_set_option(self.handle, 4, int(bool(on))))

@@ -210,6 +210,10 @@ int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t*
 /* DST_OPT_CHUNK_LOG_MAX_RECORDS: upper limit on the records (136 bytes each) the chunk log may hold; 0 = only the
  * built-in limit. Rays whose chunks did not fit are re-traced by the backward, with the same result. */
 #define DST_OPT_CHUNK_LOG_MAX_RECORDS 3
+/* Gather kernel scheduling (results are not affected): 1 lets lanes whose ray is finished take further
+ * rays on reflected segments while the rest of their warp is still walking, 0 never does, -1
+ * (default) does it for calls with max_trace_depth >= 2, where it was measured to pay. */
+#define DST_OPT_GATHER_REFILL 5
 /* dst_build_from_surfels with rebuild == 0: non-zero expands the quads inside the refit kernel (one
  * launch, no re-read of the vertices); zero (default) runs the expansion kernel and then the refit,
  * which is faster on large scenes because the expansion's writes are coalesced. Same results. */

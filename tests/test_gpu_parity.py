@@ -196,6 +196,21 @@ def test_full_chunk_log_falls_back_to_retrace(C, oracle_mod):
             assert hp.rel_l2(a[m], b[m]) < 1e-4, (wave, k)
 
 
+@pytest.mark.parametrize("config", [3, 5])
+def test_gather_refill_does_not_change_results(C, config):
+    """Scheduling option of the gather kernel (idle lanes take extra reflected-segment rays): same bits either way."""
+    wc = hp.to_cuda(hp.reduced_workload(config))
+    outs = []
+    for mode in (0, 1):
+        st = _build(C, wc, wave=True)
+        st.set_gather_refill(mode)
+        outs.append(hp.cuda_forward(C, st, wc))
+        torch.cuda.synchronize()
+        assert st.status() == 0
+    for k in ("rgb", "dpt", "acc", "norm", "aux", "mid"):
+        assert torch.equal(outs[0][k], outs[1][k]), k
+
+
 def test_refit_matches_rebuild(C, oracle_mod):
     """rebuild=0 keeps the topology and refits boxes and frames: results equal a fresh build on the moved vertices."""
     w = hp.reduced_workload(2)
