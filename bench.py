@@ -370,11 +370,12 @@ def main():
     dom = "backward" if bwd_ms >= fwd_ms else "forward"
     dom_bytes, dom_ms = (bytes_b, bwd_ms) if dom == "backward" else (bytes_f, fwd_ms)
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9 if dom_ms > 0 else 0.0
-    # DRAM bytes of one trace sequence from the ncu launch list (profiles/launch_list_config3_step.md: quarter of the
-    # rays, per-ray part scaled to the ray count, per-surfel part kept); only quoted for the workload it was measured on
+    # DRAM bytes of one trace sequence from the ncu launch list (profiles/launch_list_config3_step.md: measured at a quarter
+    # of the rays; the per-ray part is scaled to the ray count, the per-surfel part kept); only quoted for the workload it
+    # was measured on
     traffic = None
     if args.config == 3 and P == 3_000_000:
-        per_ray_q, per_surfel = (2.96e9 - 0.6e9, 0.6e9) if dom == "forward" else (3.91e9 - 1.0e9, 1.0e9)
+        per_ray_q, per_surfel = (2.72e9 - 0.255e9, 0.255e9) if dom == "forward" else (1.41e9 - 0.705e9, 0.705e9)
         traffic = int(per_ray_q * R / 518400 + per_surfel)
     roofline = {"bound": "hbm", "kernel": f"{dom} trace sequence (k_enum gather rounds + k_{'bwd' if dom == 'backward' else 'fwd'}_shade + tail)",
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
