@@ -185,9 +185,15 @@ def main():
 
     t0 = time.perf_counter()
     w = workloads.make_workload(args.config, P=args.surfels, H=args.height, W=args.width)
+    # Configuration 5 is the scale-out protocol: 8 cameras split over the ranks (strong scaling), and every step
+    # rebuilds the hierarchy before tracing. All other configurations: with N > 1 every rank traces one synthetic
+    # camera batch of identical cost (weak scaling): per-GPU work is fixed, what is added is the gradient exchange.
+    scale_out = args.config == 5
+    total_rays = w["ray_o"].shape[0] * w["ray_o"].shape[1]
+    if scale_out and world > 1:
+        ro, rd = shard.shard_rays(w["ray_o"], w["ray_d"], world, rank)
+        w = dict(w, ray_o=ro.contiguous(), ray_d=rd.contiguous())
     H, W = w["ray_o"].shape[:2]
-    # With N > 1 every rank traces one synthetic 1080p camera batch of identical cost (the configuration's camera), the
-    # usual weak-scaling set-up of a synthetic benchmark: per-GPU work is fixed, what is added is the gradient exchange.
     log(f"[rank {rank}] workload '{w['name']}' generated in {time.perf_counter() - t0:.1f} s")
     wc = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in w.items()}
     R, P = H * W, w["means3D"].shape[0]
@@ -274,6 +280,8 @@ def main():
                                          _forward_serial=st.last_forward_serial)
 
     def step():
+        if scale_out:
+            tracer.build_acceleration_structure(wc["v"], wc["f"], rebuild=True)
         f = fwd()
         g = bwd(f)
         if world > 1:
@@ -314,7 +322,8 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total = float(t.item())
     ms_step = ms_total / args.steps
-    value = world * R / (ms_step * 1e-3) / 1e6
+    job_rays = total_rays if scale_out else world * R
+    value = job_rays / (ms_step * 1e-3) / 1e6
 
     # end to end through the public module API: pinned host rays in, loss out, every step
     e2e = None
@@ -332,6 +341,8 @@ def main():
 
         def e2e_step():
             ro, rd = ro_h.to(dev, non_blocking=True), rd_h.to(dev, non_blocking=True)
+            if scale_out:
+                tracer.build_acceleration_structure(wc["v"], wc["f"], rebuild=True)
             out = tracer(ro, rd, wc["v"], leaves["means3D"], g3d, shs=shs_l, colors_precomp=col_l, others_precomp=oth_l,
                          opacities=leaves["opacities"], scales=leaves["scales"], rotations=leaves["rotations"],
                          tracer_settings=settings, start_from_first=w["start_from_first"])
@@ -356,7 +367,7 @@ def main():
             t = torch.tensor([e2e_ms], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             e2e_ms = float(t.item())
-        e2e = {"value": world * R / (e2e_ms * 1e-3) / 1e6, "unit": "Mrays/s", "ms_per_step": e2e_ms,
+        e2e = {"value": job_rays / (e2e_ms * 1e-3) / 1e6, "unit": "Mrays/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": int(ro_h.numel() * 4 + rd_h.numel() * 4), "d2h_bytes_per_step": 4}
 
     # roofline of the dominant kernel (the longer of the two trace kernels)
@@ -395,16 +406,17 @@ def main():
     # backward = surfel records + logged re-composite + 48 x (gather, composite) + tail + unpack (rounds on an empty
     # list return at once); calls below the wavefront threshold run no rounds
     rounds = 48 if R >= 131072 else 0
-    launches_per_step = (3 + 2 * rounds) + (4 + 2 * rounds)
+    launches_per_step = (3 + 2 * rounds) + (4 + 2 * rounds) + (29 if scale_out else 0)     # + the 29 kernels of a build
     if rank == 0:
         per_ray = lambda c: {"segments": c[0] / R, "enumerations": c[1] / R, "nodes_visited": c[2] / R, "quads_tested": c[3] / R,
                              "slots_evaluated": c[4] / R, "contributions": c[5] / R}
         line = {"metric": METRIC, "value": value, "unit": "Mrays/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-                "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if scale_out else "weak", "vs_baseline": None, "dtype": "f32",
                 "data": "synthetic",
                 "config": {"workload": w["name"], "surfels": P, "rays_per_gpu": R, "sh_degree": w["sh_degree"],
                            "max_trace_depth": w["max_trace_depth"], "specular_threshold": w["specular_threshold"],
-                           "parallelism": f"one 1080p camera batch per GPU x{world}, hierarchy replicated, 1 all-reduce/step" if world > 1 else "1 GPU",
+                           "parallelism": (f"8 cameras split over {world} GPUs, hierarchy replicated and rebuilt every step, 1 all-reduce/step" if scale_out
+                                           else f"one camera batch per GPU x{world}, hierarchy replicated, 1 all-reduce/step" if world > 1 else "1 GPU"),
                            "l2": "inputs larger than L2 (hierarchy + surfel records + SH rows > 126 MB), no flush"},
                 "bvh_build_ms": build_ms, "bvh_refit_ms": refit_ms, "device_status": status, "neighbours": neighbours,
                 "per_ray": {"forward": per_ray(cf), "backward": per_ray(cb_)},
