@@ -137,7 +137,7 @@ def run_cpu(w, kind, steps, warmup, stride=24):
             times.append(dt)
     ms = 1e3 * float(np.mean(times))
     return dict(value=R / (ms * 1e-3) / 1e6, unit="Mrays/s", cores=os.cpu_count(), kind="reference" if impl == "reference" else "port",
-                sample=f"every {stride}th pixel of the 1080x1920 grid ({R} rays) against the full {w['means3D'].shape[0]}-surfel scene, "
+                sample=f"every {stride}th ray in both directions of the {w['ray_o'].shape[0]}x{w['ray_o'].shape[1]} ray grid ({R} rays) against the full {w['means3D'].shape[0]}-surfel scene, "
                        f"fwd+bwd, host hierarchy built in {t_bvh:.1f} s (not timed)"), ms, R
 
 
