@@ -309,10 +309,12 @@ def main():
     sampler = ClockSampler(local_rank)
     sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = st.kernel_launches()
     ev0.record()
     for _ in range(args.steps):
         step()
     ev1.record()
+    launches = st.kernel_launches() - launches0
     barrier()
     clocks = sampler.stop()
     ms_total = ev0.elapsed_time(ev1)
@@ -395,6 +397,25 @@ def main():
                 "other_kernel": {"algorithmic_bytes_per_launch": int(bytes_f if dom == "backward" else bytes_b),
                                  "achieved": (bytes_f if dom == "backward" else bytes_b) / ((fwd_ms if dom == "backward" else bwd_ms) * 1e-3) / 1e9}}
 
+    if rank == 0 and world == 1 and not args.no_cpu and neighbours is not None:
+        # the CPU restatement of the two neighbouring steps on the host cores (whole workload, a few repetitions)
+        try:
+            from oracle import oracle as orc
+            Kc, Rc, Tc = workloads.pinhole_camera(1080, 1920, 50.0, (4.0, 0.0, 0.0))
+            orc.surfel_quads(w["means3D"], w["scales"], w["rotations"])
+            t0 = time.perf_counter()
+            for _ in range(3):
+                orc.surfel_quads(w["means3D"], w["scales"], w["rotations"])
+            neighbours["quad_expansion"]["cpu_ms"] = 1e3 * (time.perf_counter() - t0) / 3
+            orc.pinhole_rays(1080, 1920, Kc.numpy(), Rc.numpy(), Tc.numpy())
+            t0 = time.perf_counter()
+            for _ in range(3):
+                orc.pinhole_rays(1080, 1920, Kc.numpy(), Rc.numpy(), Tc.numpy())
+            neighbours["ray_generation_1080p"]["cpu_ms"] = 1e3 * (time.perf_counter() - t0) / 3
+            neighbours["cpu_cores"] = os.cpu_count()
+        except Exception as ex:
+            neighbours["cpu_error"] = str(ex)
+
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
         try:
@@ -402,11 +423,6 @@ def main():
         except Exception as ex:  # the baseline is a report, never a reason to lose the GPU numbers
             cpu_baseline = {"value": None, "unit": "Mrays/s", "cores": os.cpu_count(), "kind": "port", "sample": f"failed: {ex}"}
 
-    # kernels of this library enqueued per step: forward = surfel records + ray init + 48 x (gather, composite) + tail;
-    # backward = surfel records + logged re-composite + 48 x (gather, composite) + tail + unpack (rounds on an empty
-    # list return at once); calls below the wavefront threshold run no rounds
-    rounds = 48 if R >= 131072 else 0
-    launches_per_step = (3 + 2 * rounds) + (4 + 2 * rounds) + (29 if scale_out else 0)     # + the 29 kernels of a build
     if rank == 0:
         per_ray = lambda c: {"segments": c[0] / R, "enumerations": c[1] / R, "nodes_visited": c[2] / R, "quads_tested": c[3] / R,
                              "slots_evaluated": c[4] / R, "contributions": c[5] / R}
@@ -421,7 +437,7 @@ def main():
                 "bvh_build_ms": build_ms, "bvh_refit_ms": refit_ms, "device_status": status, "neighbours": neighbours,
                 "per_ray": {"forward": per_ray(cf), "backward": per_ray(cb_)},
                 "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-                "gpu_launches": launches_per_step * args.steps, "clocks": clocks}
+                "gpu_launches": launches, "clocks": clocks}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -86,6 +86,8 @@ int dst_destroy(dst_handle* h) {
     cudaFree(h->header); cudaFree(h->status); cudaFree(h->cache); cudaFree(h->arena); cudaFree(h->cam_dev);
     if (h->log_needed_host) cudaFreeHost(h->log_needed_host);
     if (h->log_needed_event) cudaEventDestroy(h->log_needed_event);
+    if (h->rounds_host) cudaFreeHost(h->rounds_host);
+    if (h->rounds_event) cudaEventDestroy(h->rounds_event);
     cudaFree(h->log_keys); cudaFree(h->log_hdr); cudaFree(h->log_count); cudaFree(h->log_seg_head); cudaFree(h->log_ray_ok);
     cudaFree(h->wf_state); cudaFree(h->wf_req); cudaFree(h->wf_kbuf); cudaFree(h->wf_kcnt); cudaFree(h->wf_list[0]); cudaFree(h->wf_list[1]); cudaFree(h->wf_counts); cudaFree(h->wf_claim);
     for (int k = 0; k < 3; k++) {
@@ -203,6 +205,12 @@ int dst_set_option(dst_handle* h, int option, int64_t value) {
 int dst_forward_serial(const dst_handle* h, unsigned long long* serial) {
     if (!h || !serial) return DST_E_ARG;
     *serial = h->log_serial;
+    return DST_OK;
+}
+
+int dst_kernel_launches(const dst_handle* h, int64_t* launches) {
+    if (!h || !launches) return DST_E_ARG;
+    *launches = h->launches;
     return DST_OK;
 }
 

@@ -437,6 +437,7 @@ int dst_surfel_quads_impl(dst_handle* h, const float* means, const float* scales
     const SurfelSource src = { means, scales, rotations, vertices };
     k_surfel_quads<<<(unsigned int)((P + 255) / 256), 256, 0, st>>>(src, (int)P, triangles);
     DST_CUDA_TRY(h, cudaGetLastError());
+    h->launches += 1;
     return DST_OK;
 }
 
@@ -500,6 +501,7 @@ int dst_bvh_build_impl(dst_handle* h, const float* v, int64_t P, int rebuild, cu
                                              h->arrive, h->quads, h->leaf_gid, h->header);
     dst_prof_mark(h, 0, 1, st);
     DST_CUDA_TRY(h, cudaGetLastError());
+    h->launches += (rebuild ? 27 + (n > 1 ? 1 : 0) : 0) + (from_surfels && (rebuild || !h->single_kernel_refit) ? 1 : 0) + (n == 1 ? 1 : 0) + 1;
     h->built = true;
     return DST_OK;
 }

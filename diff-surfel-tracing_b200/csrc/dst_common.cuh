@@ -95,6 +95,12 @@ struct dst_handle {
     int log_enabled;
     long long log_max_records;    // user limit on the log size (0: only the built-in limit)
     int* log_needed_host; cudaEvent_t log_needed_event;     // pinned read-back of the record count of the last forward
+    long long log_known_sig, log_known_needed;              // last completed read-back: call shape and records wanted (0: none yet)
+    long long log_pending_sig;                              // call shape of the forward whose read-back is in flight
+    // pinned read-back of the per-round list lengths of the last wavefront forward, for the round count of the next one
+    long long launches;        // kernels enqueued by this handle so far (dst_kernel_launches)
+    int* rounds_host; cudaEvent_t rounds_event;
+    long long rounds_pending_sig, rounds_known_sig; int rounds_pending_min, rounds_known;
     // optional event timing (dst_profile_enable)
     int profiling;
     cudaEvent_t* ev[3];           // per kind: 2 * DST_PROF_SLOTS events (start, stop pairs)

@@ -416,6 +416,7 @@ int dst_prepare_cache(dst_handle* h, const dst_trace_inputs* in, cudaStream_t st
         h->cache_cap = cap;
     }
     k_prepare_cache<<<(in->P + 255) / 256, 256, 0, st>>>(in->P, in->means3D, in->scales, in->rotations, in->opacities, h->cache);
+    h->launches += 1;
     DST_CUDA_TRY(h, cudaGetLastError());
     return DST_OK;
 }
@@ -442,6 +443,11 @@ int dst_ensure_wavefront(dst_handle* h, long long slots, size_t state_bytes) {
     return DST_OK;
 }
 
+// one number for "the same kind of call": ray grid, surfel count, bounce limit
+long long dst_call_signature(const dst_trace_inputs* in) {
+    return ((long long)in->H * 1000003ll + in->W) * 1000033ll + (long long)in->P * 131ll + in->max_trace_depth + 1;
+}
+
 // chunk-log buffers for `rays` rays of up to `segs` segments (grow-only)
 int dst_ensure_chunk_log(dst_handle* h, long long rays, int segs) {
     // first guess 12 chunks per ray; afterwards what the previous training forward actually needed (read back
@@ -450,6 +456,7 @@ int dst_ensure_chunk_log(dst_handle* h, long long rays, int segs) {
     if (h->log_needed_host && h->log_needed_event && cudaEventQuery(h->log_needed_event) == cudaSuccess) {
         const long long seen = *h->log_needed_host;
         if (seen > 0 && seen + seen / 8 > want) want = seen + seen / 8;
+        if (seen > 0) { h->log_known_needed = seen; h->log_known_sig = h->log_pending_sig; }
     } else cudaGetLastError();
     if (want > DST_LOG_MAX_RECORDS) want = DST_LOG_MAX_RECORDS;
     if (h->log_max_records > 0 && want > h->log_max_records) want = h->log_max_records;
@@ -519,6 +526,7 @@ int dst_pinhole_rays_impl(dst_handle* h, const dst_camera* cams, int n_cameras, 
     for (int b = 0; b < n_cameras; b++) camera_constants(cams + b, stage + b);
     DST_CUDA_TRY(h, cudaMemcpyAsync(h->cam_dev, stage, sizeof(CamConst) * n_cameras, cudaMemcpyHostToDevice, st));
     k_pinhole_rays<<<(unsigned int)((total + 255) / 256), 256, 0, st>>>(static_cast<const CamConst*>(h->cam_dev), H, W, total, ray_o, ray_d);
+    h->launches += 1;
     DST_CUDA_TRY(h, cudaGetLastError());
     return DST_OK;
 }
@@ -565,6 +573,22 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
     const int refill = h->refill_mode < 0 ? (a->in.max_trace_depth >= 2) : (h->refill_mode != 0);
     p.rounds = wave ? DST_WF_ROUNDS : 0;
     p.min_count = wave ? (int)(slots / 512 > 2048 ? slots / 512 : 2048) : 1;
+    // Rounds are enqueued without knowing how many the rays will need; a round on an exhausted list costs a few
+    // microseconds per kernel. The list lengths of the previous forward of the same shape (read back without
+    // synchronising) say how many were used: enqueue that many plus a margin. Scheduling only: rays that need more
+    // are finished by the tail kernel, and the next call sees the longer history.
+    const long long sig = dst_call_signature(&a->in);
+    if (wave) {
+        if (h->rounds_host && h->rounds_event && cudaEventQuery(h->rounds_event) == cudaSuccess) {
+            int used = 0;
+            while (used < DST_WF_ROUNDS && h->rounds_host[used] >= h->rounds_pending_min) used++;
+            h->rounds_known = used; h->rounds_known_sig = h->rounds_pending_sig;
+        } else cudaGetLastError();
+        if (h->rounds_known > 0 && h->rounds_known_sig == sig) {
+            const int want = h->rounds_known + (h->rounds_known / 2 > 4 ? h->rounds_known / 2 : 4);
+            p.rounds = want < DST_WF_ROUNDS ? want : DST_WF_ROUNDS;
+        }
+    }
     const bool diag = a->hit_log || a->hit_cnt || a->counters;
     DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 3 * (DST_WF_ROUNDS + 2), st));
     if (wave) DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_claim, 0, 4 * (size_t)slots, st));
@@ -587,6 +611,20 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
     else k_fwd_tail<false, false><<<g_tail, TAIL_THREADS, 0, st>>>(p);
     dst_prof_mark(h, 1, 1, st);
     DST_CUDA_TRY(h, cudaGetLastError());
+    h->launches += 2 + 2 * p.rounds;       // ray init, the rounds, tail
+    if (wave) {
+        if (!h->rounds_host) {
+            if (cudaMallocHost(&h->rounds_host, 4 * (DST_WF_ROUNDS + 2)) != cudaSuccess) { cudaGetLastError(); h->rounds_host = nullptr; }
+            if (h->rounds_host && cudaEventCreateWithFlags(&h->rounds_event, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); h->rounds_event = nullptr; }
+        }
+        if (h->rounds_host && h->rounds_event && cudaEventQuery(h->rounds_event) != cudaErrorNotReady) {
+            // (a copy still in flight keeps the buffer: its event decides when the buffer may be read)
+            cudaGetLastError();
+            cudaMemcpyAsync(h->rounds_host, h->wf_counts, 4 * (DST_WF_ROUNDS + 2), cudaMemcpyDeviceToHost, st);
+            cudaEventRecord(h->rounds_event, st);
+            h->rounds_pending_sig = sig; h->rounds_pending_min = p.min_count;
+        }
+    }
     if (p.log_keys) {
         // how many records this call wanted, for sizing the log of the next one (no synchronisation here)
         if (!h->log_needed_host) {
@@ -597,6 +635,7 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
         if (h->log_needed_host && h->log_needed_event) {
             cudaMemcpyAsync(h->log_needed_host, h->log_count, sizeof(int), cudaMemcpyDeviceToHost, st);
             cudaEventRecord(h->log_needed_event, st);
+            h->log_pending_sig = sig;
         }
     }
     return DST_OK;
@@ -687,5 +726,6 @@ extern "C" int dst_forward_static(dst_handle* h, const dst_fwd_args* a, void* st
     if (diag) k_fwd_tail<false, true><<<g_tail, TAIL_THREADS, 0, st>>>(p);
     else k_fwd_tail<false, false><<<g_tail, TAIL_THREADS, 0, st>>>(p);
     DST_CUDA_TRY(h, cudaGetLastError());
+    h->launches += 3;
     return DST_OK;
 }

@@ -77,6 +77,7 @@ def lib():
         l.dst_debug_knearest.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
         l.dst_forward_serial.argtypes = [C.c_void_p, C.POINTER(C.c_uint64)]
         l.dst_set_option.argtypes = [C.c_void_p, C.c_int, C.c_int64]
+        l.dst_kernel_launches.argtypes = [C.c_void_p, C.POINTER(C.c_int64)]
         l.dst_profile_enable.argtypes = [C.c_void_p, C.c_int]
         l.dst_profile_read.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_int32)]
         l.dst_debug_quad_frames.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
@@ -164,6 +165,12 @@ class OptiXStateWrapper:
     def set_chunk_log(self, on):
         """Keep (default) or drop the per-ray chunk log training forwards leave for the backward (about 1.6 KB per ray)."""
         _check(self, lib().dst_set_option(self.handle, 2, int(bool(on))))
+
+    def kernel_launches(self):
+        """Kernels this state has enqueued since it was created."""
+        n = C.c_int64(0)
+        _check(self, lib().dst_kernel_launches(self.handle, C.byref(n)))
+        return n.value
 
     def profile(self, on=True):
         """Records CUDA events around the build, forward and backward kernels of later calls."""

@@ -198,6 +198,11 @@ int dst_forward_camera(dst_handle* h, const dst_fwd_args* args, const dst_camera
 /* Synchronises `stream`, returns and clears the device status word (DST_STATUS_* bits). */
 int dst_status(dst_handle* h, uint32_t* flags, void* stream);
 
+/* Number of kernels this handle has enqueued since it was created (build, trace, unpack and neighbouring
+ * steps; memsets and copies are not counted). The number of wavefront rounds a trace call enqueues adapts to
+ * what earlier calls of the same shape used, so the count per call is not a constant. */
+int dst_kernel_launches(const dst_handle* h, int64_t* launches);
+
 /* Hierarchy facts for tests and reports: surfels, internal nodes, bytes held on the device. */
 int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t* device_bytes);
 

@@ -211,6 +211,37 @@ def test_gather_refill_does_not_change_results(C, config):
         assert torch.equal(outs[0][k], outs[1][k]), k
 
 
+def test_adaptive_round_count_keeps_results(C):
+    """Later calls of one shape enqueue fewer wavefront rounds (history of the earlier ones); rays that then need more
+    rounds are finished by the tail kernel. Results do not depend on it."""
+    w = hp.reduced_workload(3)
+    wc = hp.to_cuda(w)
+    st = _build(C, wc, wave=True)
+    n0 = st.kernel_launches()
+    first = hp.cuda_forward(C, st, wc)
+    torch.cuda.synchronize()
+    n1 = st.kernel_launches()
+    hp.cuda_forward(C, st, wc)              # reads the history of the first call, leaves its own
+    torch.cuda.synchronize()
+    n2 = st.kernel_launches()
+    again = hp.cuda_forward(C, st, wc)
+    torch.cuda.synchronize()
+    n3 = st.kernel_launches()
+    assert n3 - n2 < n1 - n0                # fewer rounds enqueued than the 48 of a call without history
+    for k in ("rgb", "dpt", "acc", "norm", "aux", "mid"):
+        assert torch.equal(first[k], again[k]), k
+    # same shape, harder rays (camera inside the scene, more chunks and bounces per ray): the short round list is
+    # not enough, the tail kernel finishes the rest, and the result is that of a state without history
+    o2, d2 = hp.workloads.pinhole_rays(wc["ray_o"].shape[0], wc["ray_o"].shape[1], 90.0, (0.9, 0.1, 0.05))
+    wc2 = dict(wc, ray_o=o2.cuda(), ray_d=d2.cuda())
+    got = hp.cuda_forward(C, st, wc2)
+    ref = hp.cuda_forward(C, _build(C, wc, wave=True), wc2)
+    torch.cuda.synchronize()
+    for k in ("rgb", "dpt", "acc", "norm", "aux", "mid"):
+        assert torch.equal(got[k], ref[k]), k
+    assert st.status() == 0
+
+
 def test_refit_matches_rebuild(C, oracle_mod):
     """rebuild=0 keeps the topology and refits boxes and frames: results equal a fresh build on the moved vertices."""
     w = hp.reduced_workload(2)
