@@ -201,6 +201,8 @@ def main():
     tracer = SurfelTracer().to(dev)
     st = tracer.optix_context
     st.profile(True)
+    if scale_out:
+        st.set_image_width(1920)          # what SurfelTracingSettings.image_width tells the module API: 1080x1920 images
     # hierarchy: build (timed 3x) and refit (timed 3x)
     for _ in range(3):
         tracer.build_acceleration_structure(wc["v"], wc["f"], rebuild=True)
@@ -337,7 +339,8 @@ def main():
         oth_l = wc["others_precomp"].clone().requires_grad_(True) if wc["others_precomp"] is not None else None
         g3d = torch.zeros_like(wc["means3D"], requires_grad=True)
         z = torch.zeros(1, device=dev)
-        settings = SurfelTracingSettings(H, W, 1.0, 1.0, wc["bg"], 1.0, z, z, w["sh_degree"], z, False, False,
+        ih, iw = (1080, 1920) if scale_out else (H, W)
+        settings = SurfelTracingSettings(ih, iw, 1.0, 1.0, wc["bg"], 1.0, z, z, w["sh_degree"], z, False, False,
                                          w["max_trace_depth"], w["specular_threshold"])
         tracer.train()
 

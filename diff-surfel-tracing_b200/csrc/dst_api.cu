@@ -195,6 +195,7 @@ int dst_set_option(dst_handle* h, int option, int64_t value) {
     switch (option) {
         case DST_OPT_WAVEFRONT_MIN_RAYS: h->wf_min_rays = value < 0 ? 0 : value; return DST_OK;
         case DST_OPT_CHUNK_LOG_MAX_RECORDS: h->log_max_records = value < 0 ? 0 : value; h->log_serial = 0; return DST_OK;
+        case DST_OPT_IMAGE_WIDTH: h->image_width = value < 0 ? 0 : value; h->log_serial = 0; return DST_OK;
         case DST_OPT_GATHER_REFILL: h->refill_mode = value < 0 ? -1 : (value != 0); return DST_OK;
         case DST_OPT_SINGLE_KERNEL_REFIT: h->single_kernel_refit = value != 0; return DST_OK;
         case DST_OPT_CHUNK_LOG: h->log_enabled = value != 0; if (!h->log_enabled) h->log_serial = 0; return DST_OK;

@@ -23,7 +23,7 @@ struct BwdParams {
     const float4* cache;
     float* arena;
     unsigned int* status;
-    int tiled;
+    int tiled, grid_h, grid_w;      // ray order, as in the forward
     // wavefront scratch
     void* state;
     EnumReq* req;
@@ -423,7 +423,7 @@ __global__ void __launch_bounds__(256) k_bwd_init(const __grid_constant__ BwdPar
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= slots) return;
     if (i == 0) p.counts[0] = (int)slots;
-    int ray = ray_of_slot(i, p.a.in.H, p.a.in.W, p.tiled != 0);
+    int ray = ray_of_slot(i, p.grid_h, p.grid_w, p.tiled != 0);
     if (ray >= 0) {
         BwdState s;
         if (bwd_init_state(p, ray, s)) {
@@ -510,7 +510,7 @@ __device__ __forceinline__ void bwd_flush_counters(unsigned long long* counters,
 template <bool DIAG>
 __global__ void __launch_bounds__(BWD_THREADS, DST_BWD_LOGGED_BLOCKS) k_bwd_logged(const __grid_constant__ BwdParams p, long long slots) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const int ray = i < slots ? ray_of_slot(i, p.a.in.H, p.a.in.W, p.tiled != 0) : -1;
+    const int ray = i < slots ? ray_of_slot(i, p.grid_h, p.grid_w, p.tiled != 0) : -1;
     TraceCounters tc = { 0, 0, 0, 0, 0, 0 };
     bool requeue = false;
     if (ray >= 0) {
@@ -561,6 +561,7 @@ __global__ void __launch_bounds__(256) k_unpack(int P, const float* __restrict__
 BvhView dst_bvh_view(const dst_handle* h);
 int dst_check_inputs(dst_handle* h, const dst_trace_inputs* in);
 long long dst_call_signature(const dst_trace_inputs* in);
+void dst_slot_grid(const dst_handle* h, const dst_trace_inputs* in, int* gh, int* gw);
 
 int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
     int rc = dst_check_inputs(h, &a->in);
@@ -587,8 +588,9 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
     if (a->dL_dshs) DST_CUDA_TRY(h, cudaMemsetAsync(a->dL_dshs, 0, 12 * (size_t)P * a->in.sh_coeffs, st));
     BwdParams p;
     p.a = *a; p.bvh = dst_bvh_view(h); p.cache = h->cache; p.arena = h->arena; p.status = h->status;
-    p.tiled = a->in.H >= 16;
-    const long long slots = slots_of_grid(a->in.H, a->in.W, p.tiled != 0);
+    dst_slot_grid(h, &a->in, &p.grid_h, &p.grid_w);
+    p.tiled = p.grid_h >= 16;
+    const long long slots = slots_of_grid(p.grid_h, p.grid_w, p.tiled != 0);
     rc = dst_ensure_wavefront(h, slots, sizeof(BwdState));
     if (rc != DST_OK) return rc;
     p.state = h->wf_state; p.req = static_cast<EnumReq*>(h->wf_req); p.kbuf = h->wf_kbuf; p.kcnt = h->wf_kcnt;

@@ -77,6 +77,7 @@ struct dst_handle {
     float4* cache; int64_t cache_cap;
     float* arena;  int64_t arena_cap;
     void* cam_dev;      // camera constants of the last ray-generation call
+    long long image_width;     // hint: rays given as (B, h*w, 3) are whole images of this width (0: unknown)
     int refill_mode;           // gather kernel: idle lanes take extra reflected-segment rays (-1: when max_trace_depth >= 2, 0: never, 1: always)
     int single_kernel_refit;   // dst_build_from_surfels(rebuild = 0): expand the quads inside the refit kernel
     int sm_count;

@@ -27,7 +27,7 @@ struct FwdParams {
     BvhView bvh;
     const float4* cache;
     unsigned int* status;
-    int tiled;
+    int tiled, grid_h, grid_w;      // ray order: 8x4 tiles over a grid_h x grid_w pixel grid, or linear
     // wavefront scratch
     void* state;
     EnumReq* req;
@@ -297,7 +297,7 @@ __global__ void __launch_bounds__(256) k_fwd_init(const __grid_constant__ FwdPar
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= slots) return;
     if (i == 0) p.counts[0] = (int)slots;
-    const int ray = ray_of_slot(i, p.a.in.H, p.a.in.W, p.tiled != 0);
+    const int ray = ray_of_slot(i, p.grid_h, p.grid_w, p.tiled != 0);
     p.list[0][i] = ray;
     if (ray < 0) return;
     FwdState s;
@@ -443,6 +443,14 @@ int dst_ensure_wavefront(dst_handle* h, long long slots, size_t state_bytes) {
     return DST_OK;
 }
 
+// Pixel grid the rays are walked over in 8x4 tiles. Rays given as (B, h*w, 3) batches of whole images are
+// contiguous image rows, so with the image width known they form one (B*h) x w grid; otherwise the (H, W) of the call.
+void dst_slot_grid(const dst_handle* h, const dst_trace_inputs* in, int* gh, int* gw) {
+    *gh = in->H; *gw = in->W;
+    const long long iw = h->image_width;
+    if (iw >= 8 && in->W > iw && in->W % iw == 0 && (long long)in->H * (in->W / iw) < 0x7fffffffll) { *gh = (int)(in->H * (in->W / iw)); *gw = (int)iw; }
+}
+
 // one number for "the same kind of call": ray grid, surfel count, bounce limit
 long long dst_call_signature(const dst_trace_inputs* in) {
     return ((long long)in->H * 1000003ll + in->W) * 1000033ll + (long long)in->P * 131ll + in->max_trace_depth + 1;
@@ -545,8 +553,9 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
     p.a = *a; p.bvh = dst_bvh_view(h); p.cache = h->cache; p.status = h->status;
     p.cam_on = cam != nullptr;
     if (cam) camera_constants(cam, &p.cam); else memset(&p.cam, 0, sizeof(p.cam));
-    p.tiled = a->in.H >= 16;
-    const long long slots = slots_of_grid(a->in.H, a->in.W, p.tiled != 0);
+    dst_slot_grid(h, &a->in, &p.grid_h, &p.grid_w);
+    p.tiled = p.grid_h >= 16;
+    const long long slots = slots_of_grid(p.grid_h, p.grid_w, p.tiled != 0);
     rc = dst_ensure_wavefront(h, slots, sizeof(FwdState));
     if (rc != DST_OK) return rc;
     rc = dst_prepare_cache(h, &a->in, st);
@@ -704,7 +713,7 @@ extern "C" int dst_forward_static(dst_handle* h, const dst_fwd_args* a, void* st
     unsigned char* base = g_static_ptr[h->device];
 
     FwdParams p;
-    p.a = *a; p.bvh = dst_bvh_view(h); p.status = h->status; p.tiled = tiled;
+    p.a = *a; p.bvh = dst_bvh_view(h); p.status = h->status; p.tiled = tiled; p.grid_h = a->in.H; p.grid_w = a->in.W;
     p.cam_on = 0; memset(&p.cam, 0, sizeof(p.cam));
     p.cache = reinterpret_cast<const float4*>(base + ST_OFF_CACHE);
     p.state = base + ST_OFF_STATE;

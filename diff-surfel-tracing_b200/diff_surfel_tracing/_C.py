@@ -154,6 +154,10 @@ class OptiXStateWrapper:
         """Upper limit on the chunk-log size in records of 136 bytes (0: built-in limit only)."""
         _check(self, lib().dst_set_option(self.handle, 3, int(n)))
 
+    def set_image_width(self, width):
+        """Hint for (B, h*w, 3) ray batches of whole images: the image width (0: unknown). Scheduling only."""
+        _check(self, lib().dst_set_option(self.handle, 6, int(width)))
+
     def set_gather_refill(self, mode):
         """Gather kernel scheduling: 1 idle lanes take extra reflected-segment rays, 0 never, -1 automatic (default)."""
         _check(self, lib().dst_set_option(self.handle, 5, int(mode)))

@@ -34,6 +34,10 @@ class _TraceSurfels(torch.autograd.Function):
     def forward(ctx, optix_context, training, start_from_first, ray_o, ray_d, vertices, means3D, grads3D, shs,
                 colors_precomp, others_precomp, opacities, scales, rotations, cov3Ds_precomp, tracer_settings):
         s = tracer_settings
+        # image_width / image_height are unused by the reference's tracer; here they tell the kernels that a
+        # (B, h*w, 3) ray batch consists of whole images, so that they can be walked in pixel tiles (scheduling only)
+        iw, ih = int(s.image_width or 0), int(s.image_height or 0)
+        optix_context.set_image_width(iw if (iw > 0 and ih > 0 and ray_o.dim() == 3 and ray_o.shape[1] == iw * ih) else 0)
         args = (optix_context, training, start_from_first, ray_o, ray_d, vertices, s.bg, means3D, shs, s.sh_degree,
                 colors_precomp, others_precomp, opacities, scales, s.scale_modifier, rotations, cov3Ds_precomp,
                 s.viewmatrix, s.projmatrix, s.campos, s.prefiltered, s.debug, s.max_trace_depth, s.specular_threshold)

@@ -215,6 +215,11 @@ int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t*
 /* DST_OPT_CHUNK_LOG_MAX_RECORDS: upper limit on the records (136 bytes each) the chunk log may hold; 0 = only the
  * built-in limit. Rays whose chunks did not fit are re-traced by the backward, with the same result. */
 #define DST_OPT_CHUNK_LOG_MAX_RECORDS 3
+/* Hint for rays given as (B, h*w, 3) batches of whole images (the reference's "(B, P, 3)" form, __init__.py:246):
+ * the image width w. The kernels then walk the rays in 8x4 pixel tiles, as they do for (H, W, 3) rays, so that a
+ * warp holds neighbouring pixels. 0 (default): unknown, batched rays are walked in the order given. Results are
+ * not affected. */
+#define DST_OPT_IMAGE_WIDTH 6
 /* Gather kernel scheduling (results are not affected): 1 lets lanes whose ray is finished take further
  * rays on reflected segments while the rest of their warp is still walking, 0 never does, -1
  * (default) does it for calls with max_trace_depth >= 2, where it was measured to pay. */

@@ -211,6 +211,26 @@ def test_gather_refill_does_not_change_results(C, config):
         assert torch.equal(outs[0][k], outs[1][k]), k
 
 
+def test_image_width_hint_does_not_change_results(C):
+    """(B, h*w, 3) ray batches walked in pixel tiles (image width known) or in the order given: same bits."""
+    wc = hp.to_cuda(hp.reduced_workload(5))               # 2 cameras of 54 x 96 pixels as a (2, 5184, 3) batch
+    outs = []
+    for width in (0, 96):
+        st = _build(C, wc, wave=True)
+        st.set_image_width(width)
+        f = hp.cuda_forward(C, st, wc)
+        g = hp.cuda_backward(C, st, wc, f, dict(rgb=torch.ones_like(f["rgb"])), serial=st.last_forward_serial)
+        torch.cuda.synchronize()
+        assert st.status() == 0
+        outs.append((f, g))
+    for k in ("rgb", "dpt", "acc", "norm", "aux", "mid"):
+        assert torch.equal(outs[0][0][k], outs[1][0][k]), k
+    for k in ("ray_o", "ray_d"):
+        assert torch.equal(outs[0][1][k], outs[1][1][k]), k
+    for k in ("means3D", "shs", "opacities", "scales", "rotations"):
+        assert hp.rel_l2(outs[0][1][k].cpu().numpy(), outs[1][1][k].cpu().numpy()) < 1e-4, k
+
+
 def test_adaptive_round_count_keeps_results(C):
     """Later calls of one shape enqueue fewer wavefront rounds (history of the earlier ones); rays that then need more
     rounds are finished by the tail kernel. Results do not depend on it."""
