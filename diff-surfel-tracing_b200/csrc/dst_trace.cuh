@@ -317,8 +317,11 @@ __device__ __forceinline__ RaySlab make_slab(float ox, float oy, float oz, float
 //   shared phase   the warp walks the hierarchy TOGETHER from the root with one stack; a node is
 //                  fetched once (one broadcast load instead of 32 scattered ones) and every lane tests
 //                  its own ray against both child boxes. A child wanted by at least DST_SHARE_VOTE
-//                  lanes stays in the shared walk; a child wanted by fewer goes onto the private
-//                  stacks of those lanes. Leaf runs reached here are tested by all lanes.
+//                  lanes (1: any lane, measured best) stays in the shared walk; a child wanted by fewer
+//                  goes onto the private stacks of those lanes. Leaf runs reached here are tested by
+//                  all lanes. When most lanes sit out most tests (after 32 nodes, under
+//                  DST_SHARE_MIN_PCT % of the lane x test slots wanted) the warp gives the shared walk
+//                  up: every lane takes the pending subtrees onto its own stack.
 //   private phase  every lane drains its own stack as in knearest(), lanes alternating between a
 //                  node phase (kept while at least DST_NODE_VOTE lanes have node work) and a leaf phase.
 // Pruning uses each lane's own 16th-nearest distance throughout, so the hit set is exactly that of
@@ -329,8 +332,8 @@ __device__ __forceinline__ RaySlab make_slab(float ox, float oy, float oz, float
 //                  ray from the BACK of the list (second cursor) for a walk of its own from the root.
 //                  List positions are claimed with atomicMax(claim[pos], tag) (tag = round + 1; the
 //                  claim words are zeroed once per call), so front batches and refills never share a ray.
-//                  Only rays on reflected segments are taken, and only when the caller asks for it
-//                  (`refill`): a ray walked alone pays for every box around its origin by itself, which
+//                  Only rays on reflected segments are taken, and only in the REFILL instantiation, which the
+//                  host picks per call: a ray walked alone pays for every box around its origin by itself, which
 //                  the shared start of a batch spreads over 32 rays. Measured: with two bounces on 6M
 //                  surfels the forward gets a third faster, with one bounce on 3M surfels 7 % slower.
 #define DST_SHARED_STACK 64
@@ -489,9 +492,6 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
                         else if (d0) push(l0, tn0);
                         else if (d1) push(l1, tn1);
                         if (s0) next = l0; else if (s1) next = l1;
-                    }
-                    if (s0 && s1) {
-                        // (children shared by the warp need no private entry)
                     }
                     if (next != DONE) { scur = next; continue; }
                 } else {
