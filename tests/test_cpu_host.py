@@ -182,6 +182,35 @@ def test_prep_restatement_agrees_with_workload_generators(oracle_mod):
     assert np.array_equal(f, w["f"].numpy())
 
 
+def test_camera_helper_describes_the_workload_rays(oracle_mod):
+    """workloads.pinhole_camera gives K, R, T of the camera whose rays workloads.pinhole_rays generates: fed to the
+    restatement of the reference's get_rays they reproduce those rays."""
+    import workloads
+    H, W = 36, 64
+    eye = (3.2, -1.5, 0.8)
+    o_ref, d_ref = workloads.pinhole_rays(H, W, 50.0, eye)
+    K, R, T = workloads.pinhole_camera(H, W, 50.0, eye)
+    o, d = oracle_mod.pinhole_rays(H, W, K.numpy(), R.numpy(), T.numpy())
+    assert np.abs(o - o_ref.numpy()).max() < 1e-5
+    assert np.abs(d - d_ref.numpy()).max() < 1e-5
+
+
+def test_binding_rejects_bad_arguments_before_touching_the_gpu():
+    """Host-side checks of the ctypes binding that need neither a GPU nor the library."""
+    from diff_surfel_tracing import _C
+    m, s, r = torch.zeros((5, 3)), torch.ones((5, 2)), torch.ones((5, 4))
+    with pytest.raises(RuntimeError, match="dimensions"):
+        _C._surfel_params(m.reshape(-1), s, r)
+    with pytest.raises(RuntimeError, match="dimensions"):
+        _C._surfel_params(m, s[:, :1], r)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        _C._surfel_params(m, s, r)                       # CPU tensors: CHECK_INPUT of the reference (trace_surfels.cpp:23-24)
+    with pytest.raises(RuntimeError, match="elements"):
+        _C.make_camera(np.eye(2), np.eye(3), np.zeros(3))
+    cam = _C.make_camera(np.arange(9.0).reshape(3, 3), np.eye(3), np.array([[1.0], [2.0], [3.0]]), correct_pix=False, z_depth=True)
+    assert list(cam.K) == list(range(9)) and list(cam.T) == [1.0, 2.0, 3.0] and cam.correct_pix == 0 and cam.z_depth == 1
+
+
 def test_split_rows_covers_everything():
     import shard
     for n in (1, 7, 8, 1080, 1081):
