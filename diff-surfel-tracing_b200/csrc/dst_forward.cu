@@ -9,6 +9,12 @@
 // steps as a wavefront (k_enum / k_fwd_shade rounds over the list of live rays, state in scratch
 // memory); the stragglers and small launches run in k_fwd_tail, one thread per ray to completion.
 #include "dst_trace.cuh"
+#ifndef DST_ENUM_GRID_PER_SM
+#define DST_ENUM_GRID_PER_SM 12       // blocks per SM of the forward gather and composite kernels (persistent: more blocks than fit just start later)
+#endif
+#ifndef DST_SHADE_GRID_PER_SM
+#define DST_SHADE_GRID_PER_SM 8
+#endif
 #include <string.h>
 
 namespace {
@@ -603,7 +609,7 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
     if (wave) DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_claim, 0, 4 * (size_t)slots, st));
     dst_prof_mark(h, 1, 0, st);
     k_fwd_init<<<(unsigned int)((slots + 255) / 256), 256, 0, st>>>(p, slots);
-    const int g_enum = dst_wavefront_grid(h, slots, ENUM_THREADS, 12), g_shade = dst_wavefront_grid(h, slots, SHADE_THREADS, 8);
+    const int g_enum = dst_wavefront_grid(h, slots, ENUM_THREADS, DST_ENUM_GRID_PER_SM), g_shade = dst_wavefront_grid(h, slots, SHADE_THREADS, DST_SHADE_GRID_PER_SM);
     for (int r = 0; r < p.rounds; r++) {
         if (diag) {
             if (refill) k_enum<true, true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
