@@ -12,7 +12,10 @@
 
 namespace {
 
-constexpr int BWD_THREADS = 128;
+#ifndef DST_BWD_THREADS
+#define DST_BWD_THREADS 128
+#endif
+constexpr int BWD_THREADS = DST_BWD_THREADS;
 #ifndef DST_BWD_LOGGED_BLOCKS
 #define DST_BWD_LOGGED_BLOCKS 1      // resident blocks per SM the logged backward is compiled for
 #endif

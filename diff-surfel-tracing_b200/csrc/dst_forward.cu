@@ -19,8 +19,14 @@
 
 namespace {
 
-constexpr int SHADE_THREADS = 128;
-constexpr int TAIL_THREADS = 128;
+#ifndef DST_SHADE_THREADS
+#define DST_SHADE_THREADS 128
+#endif
+#ifndef DST_TAIL_THREADS
+#define DST_TAIL_THREADS 128
+#endif
+constexpr int SHADE_THREADS = DST_SHADE_THREADS;
+constexpr int TAIL_THREADS = DST_TAIL_THREADS;
 
 // One pinhole camera, reduced on the host to what a pixel needs: inverse intrinsics, rotation,
 // translation and centre (example/utils/ray_utils.py:19-60, 107).
