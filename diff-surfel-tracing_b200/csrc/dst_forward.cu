@@ -12,6 +12,9 @@
 #ifndef DST_ENUM_GRID_PER_SM
 #define DST_ENUM_GRID_PER_SM 12       // blocks per SM of the forward gather and composite kernels (persistent: more blocks than fit just start later)
 #endif
+#ifndef DST_WARP_TAIL_MAX_RAYS
+#define DST_WARP_TAIL_MAX_RAYS 32768   // up to this many rays the tail kernel runs one warp per ray
+#endif
 #ifndef DST_SHADE_GRID_PER_SM
 #define DST_SHADE_GRID_PER_SM 4        // what fits an SM at once at 128 registers (measured: 8 is 2.5 % slower on the headline workload)
 #endif
@@ -377,6 +380,48 @@ __global__ void __launch_bounds__(TAIL_THREADS) k_fwd_tail(const __grid_constant
     if (DIAG) flush_counters(p.a.counters, tc);
 }
 
+// The same for few rays (what the wavefront leaves over, or a small call): one WARP per ray. The warp gathers
+// the chunk together (knearest_warp), lane 0 composites it. The longest ray, whose serial work is what this
+// kernel takes, gets through its walks several times faster than a thread on its own.
+constexpr int WTAIL_THREADS = 128;
+template <bool DIAG>
+__global__ void __launch_bounds__(WTAIL_THREADS) k_fwd_tail_warp(const __grid_constant__ FwdParams p) {
+    __shared__ unsigned long long wstack[WTAIL_THREADS / 32][DST_WARP_STACK];
+    __shared__ unsigned long long wkeys[WTAIL_THREADS / 32][DST_CHUNK];
+    constexpr unsigned int FULL = 0xffffffffu;
+    const int round = first_skipped_round(p.counts, p.rounds, p.min_count);
+    const int n = p.counts[round];
+    const int* list = p.list[round & 1];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int warps = gridDim.x * (WTAIL_THREADS / 32);
+    TraceCounters tc = { 0, 0, 0, 0, 0, 0 };
+    for (int i = blockIdx.x * (WTAIL_THREADS / 32) + w; i < n; i += warps) {
+        const int ray = list[i];
+        if (ray < 0) continue;
+        FwdState s;
+        if (lane == 0) load_state(p.state, ray, s);
+        bool alive = true;
+        while (alive) {
+            EnumReq q;
+            if (lane == 0) fwd_request(s, q);
+            const float ox = __shfl_sync(FULL, q.ox, 0), oy = __shfl_sync(FULL, q.oy, 0), oz = __shfl_sync(FULL, q.oz, 0);
+            const float dx = __shfl_sync(FULL, q.dx, 0), dy = __shfl_sync(FULL, q.dy, 0), dz = __shfl_sync(FULL, q.dz, 0);
+            const float k0 = __shfl_sync(FULL, q.kmax0, 0);
+            unsigned long long key;
+            const int cnt = knearest_warp<DIAG>(p.bvh, ox, oy, oz, dx, dy, dz, k0, wstack[w], key, p.status, tc);
+            if (lane < DST_CHUNK) wkeys[w][lane] = key;
+            __syncwarp();
+            bool go = false;
+            if (lane == 0) {
+                if (DIAG) tc.enums++;
+                go = fwd_shade<DIAG, 1>(p, ray, s, wkeys[w], cnt, tc);
+            }
+            alive = __shfl_sync(FULL, go, 0);
+        }
+    }
+    if (DIAG) flush_counters(p.a.counters, tc);
+}
+
 // one enumeration per ray, for tests of the hierarchy walk against exhaustive testing
 template <bool BRUTE>
 __global__ void __launch_bounds__(TAIL_THREADS) k_knearest(BvhView bvh, const float* __restrict__ ro, const float* __restrict__ rd,
@@ -627,9 +672,17 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
             k_fwd_shade<false><<<g_shade, SHADE_THREADS, 0, st>>>(p, r);
         }
     }
-    const int g_tail = dst_wavefront_grid(h, wave ? p.min_count : slots, TAIL_THREADS, 8);
-    if (diag) k_fwd_tail<false, true><<<g_tail, TAIL_THREADS, 0, st>>>(p);
-    else k_fwd_tail<false, false><<<g_tail, TAIL_THREADS, 0, st>>>(p);
+    // few rays left (or a small call): one warp per ray; many: one thread per ray
+    const long long tail_rays = wave ? p.min_count : slots;
+    if (tail_rays <= DST_WARP_TAIL_MAX_RAYS) {
+        const int g_wtail = dst_wavefront_grid(h, tail_rays * 32, WTAIL_THREADS, 16);
+        if (diag) k_fwd_tail_warp<true><<<g_wtail, WTAIL_THREADS, 0, st>>>(p);
+        else k_fwd_tail_warp<false><<<g_wtail, WTAIL_THREADS, 0, st>>>(p);
+    } else {
+        const int g_tail = dst_wavefront_grid(h, tail_rays, TAIL_THREADS, 8);
+        if (diag) k_fwd_tail<false, true><<<g_tail, TAIL_THREADS, 0, st>>>(p);
+        else k_fwd_tail<false, false><<<g_tail, TAIL_THREADS, 0, st>>>(p);
+    }
     dst_prof_mark(h, 1, 1, st);
     DST_CUDA_TRY(h, cudaGetLastError());
     h->launches += 2 + 2 * p.rounds;       // ray init, the rounds, tail

@@ -559,6 +559,128 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
     if (COUNT && counters) { atomicAdd(counters + 1, tc.enums); atomicAdd(counters + 2, tc.nodes); atomicAdd(counters + 3, tc.quads); }
 }
 
+// The 16 nearest hits of ONE ray, found by a whole warp (same result as knearest()). For the few rays the
+// wavefront leaves to the tail kernel, and for small calls, what counts is the latency of a single walk:
+// a thread on its own pays one dependent memory round trip per box and per quad. Here every step takes up
+// to 16 entries from the top of a stack in shared memory (nearest first); leaf runs among them are tested
+// 16 quads at a time, one quad per lane, and the nodes among them 32 child boxes at a time, one box per
+// lane. The k-buffer lives in registers, one key per lane (lanes 0..15, ascending); an insertion is a
+// ballot and a shuffle. All arguments are warp-uniform. `stack` holds DST_WARP_STACK entries.
+#define DST_WARP_STACK 512
+#define DST_WARP_STEP_LIMIT (1 << 20)      // bound on the steps of one walk (status flag instead of a hang)
+template <bool COUNT>
+__device__ __forceinline__ int knearest_warp(const BvhView& bvh, float ox, float oy, float oz, float dx, float dy, float dz,
+                                             float kmax0, unsigned long long* stack, unsigned long long& mykey,
+                                             unsigned int* status, TraceCounters& tc) {
+    constexpr unsigned int FULL = 0xffffffffu;
+    constexpr unsigned long long EMPTY = ~0ull;
+    const int lane = threadIdx.x & 31;
+    mykey = EMPTY;
+    int n = 0;
+    float kmax = kmax0;
+    if (bvh.nrefs <= 0) return 0;
+    const RaySlab sl = make_slab(ox, oy, oz, dx, dy, dz, __ldg(bvh.header + 6));
+    if (!sl.valid) return 0;
+    // inserts a hit (uniform key) into the sorted keys held by lanes 0..15
+    auto insert = [&](unsigned long long key) {
+        const unsigned long long last = __shfl_sync(FULL, mykey, DST_CHUNK - 1);
+        if (key >= last) return;                                            // not among the 16 nearest (or the buffer is full of nearer ones)
+        if (__any_sync(FULL, lane < DST_CHUNK && mykey == key)) return;
+        const int pos = __popc(__ballot_sync(FULL, lane < DST_CHUNK && mykey < key));
+        const unsigned long long up = __shfl_up_sync(FULL, mykey, 1);
+        if (lane < DST_CHUNK) mykey = lane < pos ? mykey : (lane == pos ? key : up);
+        if (n < DST_CHUNK) n++;
+        if (n == DST_CHUNK) kmax = hitkey_t(__shfl_sync(FULL, mykey, DST_CHUNK - 1));
+    };
+    int sp = 0;
+    if (lane == 0) stack[0] = 0ull;            // the root: nearest possible t 0, link 0
+    sp = 1;
+    __syncwarp();
+    for (int step = 0; sp > 0; step++) {
+        if (step >= DST_WARP_STEP_LIMIT) { if (lane == 0) atomicOr(status, DST_STATUS_STACK_OVERFLOW); break; }
+        // lanes 30/31 take the top entry, lanes 28/29 the next, ...: lane order is then the order in which
+        // surviving children go back onto the stack (farthest first)
+        const int take = sp < 16 ? sp : 16;
+        const int slot = 15 - (lane >> 1);                                  // 0 = top of the stack
+        unsigned long long e = 0ull;
+        bool valid = slot < take;
+        if (valid) e = stack[sp - 1 - slot];
+        sp -= take;
+        __syncwarp();
+        const int link = (int)(unsigned int)e;
+        valid = valid && __uint_as_float((unsigned int)(e >> 32)) <= kmax;
+        // ---- leaf runs among the entries, nearest first ----
+        unsigned int leaves = __ballot_sync(FULL, valid && link < 0 && (lane & 1) == 1);
+        while (leaves) {
+            const int src = 31 - __clz(leaves);                             // highest lane = nearest entry
+            leaves &= ~(1u << src);
+            const int lnk = __shfl_sync(FULL, link, src);
+            const float etn = __uint_as_float((unsigned int)(__shfl_sync(FULL, e, src) >> 32));
+            if (etn > kmax) continue;                                       // the bound has shrunk meanwhile
+            const int first = DST_LEAF_FIRST(lnk), count = DST_LEAF_COUNT(lnk);
+            for (int base = 0; base < count; base += 32) {
+                bool hit = false;
+                unsigned long long key = 0ull;
+                if (base + lane < count) {
+                    const int pos = first + base + lane;
+                    const float4* qp = bvh.quads + 3 * (size_t)pos;
+                    const float4 qa = __ldg(qp), qb = __ldg(qp + 1), qc = __ldg(qp + 2);
+                    float t; int tri;
+                    if (ray_quad(qa, qb, qc, ox, oy, oz, dx, dy, dz, kmax, t, tri)) {
+                        const unsigned int gid = (unsigned int)__ldg(bvh.leaf_gid + pos) >> DST_REF_SHIFT;
+                        key = make_key(t, 2u * gid + (unsigned int)tri);
+                        hit = true;
+                    }
+                }
+                if (COUNT && lane == 0) tc.quads += (unsigned long long)(count - base < 32 ? count - base : 32);
+                unsigned int hits = __ballot_sync(FULL, hit);
+                while (hits) {
+                    const int hl = __ffs(hits) - 1;
+                    hits &= hits - 1u;
+                    insert(__shfl_sync(FULL, key, hl));
+                }
+            }
+        }
+        // ---- nodes among the entries: one child box per lane ----
+        bool h = false;
+        float tn = 0.0f;
+        int clink = 0;
+        if (valid && link >= 0 && __uint_as_float((unsigned int)(e >> 32)) <= kmax) {
+            const float4* np = bvh.nodes + 4 * (size_t)link;
+            const float4 a = __ldg(np), b = __ldg(np + 1), c = __ldg(np + 2);
+            const int4 lk = __ldg(reinterpret_cast<const int4*>(np + 3));
+            float lox, loy, loz, hix, hiy, hiz;
+            if ((lane & 1) == 0) { lox = a.x; loy = a.y; loz = a.z; hix = a.w; hiy = b.x; hiz = b.y; clink = lk.z; }
+            else { lox = b.z; loy = b.w; loz = c.x; hix = c.y; hiy = c.z; hiz = c.w; clink = lk.w; }
+            const float nx = sl.px ? lox : hix, fx = sl.px ? hix : lox;
+            const float ny = sl.py ? loy : hiy, fy = sl.py ? hiy : loy;
+            const float nz = sl.pz ? loz : hiz, fz = sl.pz ? hiz : loz;
+            tn = fmaxf(fmaxf(fmaf(nx, sl.ix, -sl.onx), fmaf(ny, sl.iy, -sl.ony)), fmaxf(fmaf(nz, sl.iz, -sl.onz), 0.0f));
+            const float tf = fminf(fminf(fmaf(fx, sl.ix, -sl.ofx), fmaf(fy, sl.iy, -sl.ofy)), fmaf(fz, sl.iz, -sl.ofz));
+            h = (tn <= tf) && (tn <= kmax);
+            if (COUNT && (lane & 1) == 0) tc.nodes++;
+        }
+        // within a pair the farther child goes first (even lane), the nearer second (odd lane)
+        {
+            const float ptn = __shfl_xor_sync(FULL, tn, 1);
+            const int plink = __shfl_xor_sync(FULL, clink, 1);
+            const bool ph = __shfl_xor_sync(FULL, h, 1);
+            const bool even = (lane & 1) == 0;
+            if (h && ph && (even ? tn < ptn : tn > ptn)) { tn = ptn; clink = plink; }
+        }
+        const unsigned int pushes = __ballot_sync(FULL, h);
+        const int npush = __popc(pushes);
+        if (sp + npush > DST_WARP_STACK) {
+            if (lane == 0) atomicOr(status, DST_STATUS_STACK_OVERFLOW);
+            break;
+        }
+        if (h) stack[sp + __popc(pushes & ((1u << lane) - 1u))] = ((unsigned long long)__float_as_uint(tn) << 32) | (unsigned int)clink;
+        sp += npush;
+        __syncwarp();
+    }
+    return n;
+}
+
 // list entry i of round 0 -> ray index (or -1): image-like grids are walked in 8x4 pixel tiles so
 // that the rays of a warp stay close in the hierarchy, batched ray lists linearly
 __device__ __forceinline__ int ray_of_slot(long long i, int H, int W, bool tiled) {
