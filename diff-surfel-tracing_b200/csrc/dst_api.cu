@@ -60,7 +60,7 @@ int dst_create(int device, dst_handle** out) {
     if (!h) { dst_global_error("dst_create: out of host memory"); return DST_E_NOMEM; }
     memset(h, 0, sizeof(*h));
     h->device = device;
-    h->wf_min_rays = 1 << 17;
+    h->wf_min_rays = 1 << 15;
     h->log_enabled = 1;
     h->refill_mode = -1;
     cudaDeviceProp prop;

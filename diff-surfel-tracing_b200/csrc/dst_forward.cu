@@ -12,6 +12,10 @@
 #ifndef DST_ENUM_GRID_PER_SM
 #define DST_ENUM_GRID_PER_SM 12       // blocks per SM of the forward gather and composite kernels (persistent: more blocks than fit just start later)
 #endif
+#ifndef DST_TAIL_DIV
+#define DST_TAIL_DIV 128             // the wavefront hands over to the tail kernel when fewer than rays / DST_TAIL_DIV
+#define DST_TAIL_MIN 8192            // (but at least DST_TAIL_MIN, at most DST_WARP_TAIL_MAX_RAYS) rays are left
+#endif
 #ifndef DST_WARP_TAIL_MAX_RAYS
 #define DST_WARP_TAIL_MAX_RAYS 32768   // up to this many rays the tail kernel runs one warp per ray
 #endif
@@ -638,7 +642,11 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
     const bool wave = slots >= h->wf_min_rays;
     const int refill = h->refill_mode < 0 ? (a->in.max_trace_depth >= 2) : (h->refill_mode != 0);
     p.rounds = wave ? DST_WF_ROUNDS : 0;
-    p.min_count = wave ? (int)(slots / 512 > 2048 ? slots / 512 : 2048) : 1;
+    {
+        long long hand_over = slots / DST_TAIL_DIV > DST_TAIL_MIN ? slots / DST_TAIL_DIV : DST_TAIL_MIN;
+        if (hand_over > DST_WARP_TAIL_MAX_RAYS) hand_over = DST_WARP_TAIL_MAX_RAYS;       // what the warp-per-ray tail takes
+        p.min_count = wave ? (int)hand_over : 1;
+    }
     // Rounds are enqueued without knowing how many the rays will need; a round on an exhausted list costs a few
     // microseconds per kernel. The list lengths of the previous forward of the same shape (read back without
     // synchronising) say how many were used: enqueue that many plus a margin. Scheduling only: rays that need more

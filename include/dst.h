@@ -207,8 +207,9 @@ int dst_kernel_launches(const dst_handle* h, int64_t* launches);
 int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t* device_bytes);
 
 /* Tunables. DST_OPT_WAVEFRONT_MIN_RAYS: trace calls with at least this many rays run as rounds of
- * separate gather / composite kernels over the live rays (default 131072); smaller calls use one
- * thread per ray for the whole path. Results do not depend on the setting. */
+ * separate gather / composite kernels over the live rays (default 32768); smaller calls run one
+ * kernel that takes every ray through its whole path (one warp per ray in the forward, one thread per
+ * ray in the backward). Results do not depend on the setting. */
 #define DST_OPT_WAVEFRONT_MIN_RAYS 1
 /* DST_OPT_CHUNK_LOG: 1 (default) keeps the chunk log of training forwards for the backward, 0 disables it. */
 #define DST_OPT_CHUNK_LOG 2
