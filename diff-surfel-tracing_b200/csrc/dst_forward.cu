@@ -804,9 +804,15 @@ extern "C" int dst_forward_static(dst_handle* h, const dst_fwd_args* a, void* st
                                                              reinterpret_cast<float4*>(base + ST_OFF_CACHE));
     k_fwd_init<<<(unsigned int)((slots + 255) / 256), 256, 0, st>>>(p, slots);
     const bool diag = a->hit_log || a->hit_cnt || a->counters;
-    const int g_tail = dst_wavefront_grid(h, slots, TAIL_THREADS, 8);
-    if (diag) k_fwd_tail<false, true><<<g_tail, TAIL_THREADS, 0, st>>>(p);
-    else k_fwd_tail<false, false><<<g_tail, TAIL_THREADS, 0, st>>>(p);
+    if (slots <= DST_WARP_TAIL_MAX_RAYS) {
+        const int g_wtail = dst_wavefront_grid(h, slots * 32, WTAIL_THREADS, 16);
+        if (diag) k_fwd_tail_warp<true><<<g_wtail, WTAIL_THREADS, 0, st>>>(p);
+        else k_fwd_tail_warp<false><<<g_wtail, WTAIL_THREADS, 0, st>>>(p);
+    } else {
+        const int g_tail = dst_wavefront_grid(h, slots, TAIL_THREADS, 8);
+        if (diag) k_fwd_tail<false, true><<<g_tail, TAIL_THREADS, 0, st>>>(p);
+        else k_fwd_tail<false, false><<<g_tail, TAIL_THREADS, 0, st>>>(p);
+    }
     DST_CUDA_TRY(h, cudaGetLastError());
     h->launches += 3;
     return DST_OK;
