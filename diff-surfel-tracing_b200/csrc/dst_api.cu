@@ -16,7 +16,7 @@ int dst_set_error(dst_handle* h, int code, const char* fmt, ...) {
 void dst_global_error(const char* msg) { snprintf(g_global_err, sizeof(g_global_err), "%s", msg); }
 
 void dst_prof_mark(dst_handle* h, int kind, int which_end, cudaStream_t st) {
-    if (!h->profiling) return;
+    if (!h->profiling || (kind == 3 && h->profiling < 2)) return;
     if (!h->ev[kind]) {
         h->ev[kind] = new (std::nothrow) cudaEvent_t[2 * DST_PROF_SLOTS];
         if (!h->ev[kind]) return;
@@ -63,6 +63,7 @@ int dst_create(int device, dst_handle** out) {
     h->wf_min_rays = 1 << 15;
     h->log_enabled = 1;
     h->refill_mode = -1;
+    h->stable_lists = 1;
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete h; dst_global_error("dst_create: cudaGetDeviceProperties failed"); return DST_E_CUDA; }
     h->sm_count = prop.multiProcessorCount;
@@ -90,7 +91,8 @@ int dst_destroy(dst_handle* h) {
     if (h->rounds_event) cudaEventDestroy(h->rounds_event);
     cudaFree(h->log_keys); cudaFree(h->log_hdr); cudaFree(h->log_count); cudaFree(h->log_seg_head); cudaFree(h->log_ray_ok);
     cudaFree(h->wf_state); cudaFree(h->wf_req); cudaFree(h->wf_kbuf); cudaFree(h->wf_kcnt); cudaFree(h->wf_list[0]); cudaFree(h->wf_list[1]); cudaFree(h->wf_counts); cudaFree(h->wf_claim);
-    for (int k = 0; k < 3; k++) {
+    cudaFree(h->wf_tmp); cudaFree(h->wf_wcnt); cudaFree(h->wf_bcnt);
+    for (int k = 0; k < 4; k++) {
         if (h->ev[k]) { for (int i = 0; i < 2 * DST_PROF_SLOTS; i++) cudaEventDestroy(h->ev[k][i]); delete[] h->ev[k]; }
     }
     delete h;
@@ -178,7 +180,7 @@ int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t*
     if (surfels) *surfels = h->built ? h->P : 0;
     if (nodes) *nodes = h->built ? (h->P > 1 ? h->P - 1 : 1) : 0;
     if (device_bytes) *device_bytes = h->cap * (64 + 48 + 4 + 4 + 4 + 16 + 8 + 20) + h->hist_cap * 1024 + h->cache_cap * 64 + h->arena_cap * 4 * DST_ARENA_FLOATS +
-                                      h->wf_cap * (long long)(h->wf_state_bytes + 32 + 8 * DST_CHUNK + 4 + 8);
+                                      h->wf_cap * (long long)(h->wf_state_bytes + 32 + 8 * DST_CHUNK + 4 + 8 + 4 + 4);
     return DST_OK;
 }
 
@@ -198,6 +200,7 @@ int dst_set_option(dst_handle* h, int option, int64_t value) {
         case DST_OPT_IMAGE_WIDTH: h->image_width = value < 0 ? 0 : value; h->log_serial = 0; return DST_OK;
         case DST_OPT_GATHER_REFILL: h->refill_mode = value < 0 ? -1 : (value != 0); return DST_OK;
         case DST_OPT_SINGLE_KERNEL_REFIT: h->single_kernel_refit = value != 0; return DST_OK;
+        case DST_OPT_STABLE_LISTS: h->stable_lists = value != 0; return DST_OK;
         case DST_OPT_CHUNK_LOG: h->log_enabled = value != 0; if (!h->log_enabled) h->log_serial = 0; return DST_OK;
         default: return dst_set_error(h, DST_E_ARG, "unknown option %d", option);
     }
@@ -217,12 +220,27 @@ int dst_kernel_launches(const dst_handle* h, int64_t* launches) {
 
 int dst_profile_enable(dst_handle* h, int on) {
     if (!h) return DST_E_ARG;
-    h->profiling = on != 0;
+    h->profiling = on < 0 ? 0 : (on > 2 ? 2 : on);
+    return DST_OK;
+}
+
+int dst_profile_launches(dst_handle* h, int which, float* ms, int32_t cap, int32_t* launches) {
+    if (!h || which < 0 || which > 3 || !ms || !launches || cap < 0) return DST_E_ARG;
+    DeviceGuard g(h->device);
+    const int n = h->ev[which] ? h->ev_n[which] : 0;
+    for (int i = 0; i < n; i++) {
+        float one = 0.f;
+        DST_CUDA_TRY(h, cudaEventSynchronize(h->ev[which][2 * i + 1]));
+        DST_CUDA_TRY(h, cudaEventElapsedTime(&one, h->ev[which][2 * i], h->ev[which][2 * i + 1]));
+        if (i < cap) ms[i] = one;
+    }
+    *launches = n;
+    h->ev_n[which] = 0;
     return DST_OK;
 }
 
 int dst_profile_read(dst_handle* h, int which, float* ms_sum, int32_t* launches) {
-    if (!h || which < 0 || which > 2 || !ms_sum || !launches) return DST_E_ARG;
+    if (!h || which < 0 || which > 3 || !ms_sum || !launches) return DST_E_ARG;
     DeviceGuard g(h->device);
     float sum = 0.f;
     const int n = h->ev[which] ? h->ev_n[which] : 0;
@@ -234,6 +252,17 @@ int dst_profile_read(dst_handle* h, int which, float* ms_sum, int32_t* launches)
     }
     *ms_sum = sum; *launches = n;
     h->ev_n[which] = 0;
+    return DST_OK;
+}
+
+int dst_debug_round_counts(dst_handle* h, int32_t* counts, int32_t cap, void* stream) {
+    if (!h || !counts || cap < 0) return DST_E_ARG;
+    if (!h->wf_counts) return dst_set_error(h, DST_E_STATE, "no trace call has run on this handle");
+    DeviceGuard g(h->device);
+    const int n = cap < 50 ? cap : 50;      // DST_WF_ROUNDS + 2 list lengths
+    DST_CUDA_TRY(h, cudaMemcpyAsync(counts, h->wf_counts, 4 * (size_t)n, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    DST_CUDA_TRY(h, cudaStreamSynchronize((cudaStream_t)stream));
+    for (int i = n; i < cap; i++) counts[i] = 0;
     return DST_OK;
 }
 

@@ -36,6 +36,7 @@ struct BwdParams {
     int* counts;
     int min_count;
     int rounds;
+    LiveLists lv;
     // chunk log of the matching forward call (null: not available)
     const unsigned long long* log_keys; const int2* log_hdr; const int* log_seg_head; const unsigned char* log_ray_ok;
     int log_seg_stride;
@@ -450,6 +451,7 @@ __global__ void __launch_bounds__(BWD_THREADS) k_bwd_shade(const __grid_constant
     for (int i = blockIdx.x * BWD_THREADS + threadIdx.x; i < n_pad; i += gridDim.x * BWD_THREADS) {
         const int ray = i < n ? list[i] : -1;
         bool alive = false;
+        int cls = 0;
         if (ray >= 0) {
             BwdState s;
             bwd_load_state(p.state, ray, s);
@@ -459,9 +461,11 @@ __global__ void __launch_bounds__(BWD_THREADS) k_bwd_shade(const __grid_constant
                 EnumReq q;
                 bwd_request(s, q);
                 p.req[ray] = q;
+                cls = s.seg > 0;
             }
         }
-        append_alive(alive, ray, next_list, p.counts + round + 1);
+        if (p.lv.stable) live_out(p.lv, round, i, alive, ray, cls);
+        else append_alive(alive, ray, next_list, p.counts + round + 1);
     }
     if (DIAG && p.a.counters) {
         atomicAdd(p.a.counters + 0, tc.segs); atomicAdd(p.a.counters + 4, tc.evals); atomicAdd(p.a.counters + 5, tc.contribs);
@@ -607,6 +611,9 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
     const bool wave = slots >= h->wf_min_rays;
     const int refill = h->refill_mode < 0 ? (a->in.max_trace_depth >= 2) : (h->refill_mode != 0);
     if (wave) DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_claim, 0, 4 * (size_t)slots, st));
+    rc = dst_live_lists(h, slots, &p.lv, st);
+    if (rc != DST_OK) return rc;
+    const int g_compact = (int)((slots + DST_LIVE_BLOCK - 1) / DST_LIVE_BLOCK);
     p.rounds = wave ? DST_WF_ROUNDS : 0;
     p.min_count = wave ? (int)(slots / 512 > 2048 ? slots / 512 : 2048) : 1;
     // With the chunk log the rounds only serve rays the log could not hold. When the last completed read-back of a
@@ -626,15 +633,19 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
     }
     const int g_enum = dst_wavefront_grid(h, slots, ENUM_THREADS, 10), g_shade = dst_wavefront_grid(h, slots, BWD_THREADS, 4);
     for (int r = 0; r < p.rounds; r++) {
+        dst_prof_mark(h, 3, 0, st);
         if (diag) {
             if (refill) k_enum<true, true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
             else k_enum<true, false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
+            dst_prof_mark(h, 3, 1, st);
             k_bwd_shade<true><<<g_shade, BWD_THREADS, 0, st>>>(p, r);
         } else {
             if (refill) k_enum<false, true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
             else k_enum<false, false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
+            dst_prof_mark(h, 3, 1, st);
             k_bwd_shade<false><<<g_shade, BWD_THREADS, 0, st>>>(p, r);
         }
+        if (p.lv.stable) k_compact<<<g_compact, 256, 0, st>>>(p.lv, p.counts + r, p.counts + r + 1, p.min_count, p.list[(r + 1) & 1], r);
     }
     const int g_tail = dst_wavefront_grid(h, wave ? p.min_count : slots, BWD_THREADS, 4);
     if (diag) k_bwd_tail<true><<<g_tail, BWD_THREADS, 0, st>>>(p);
@@ -644,6 +655,6 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
     k_unpack<<<(unsigned int)((P + 255) / 256), 256, 0, st>>>((int)P, h->arena, a->dL_drotations, a->dL_dmeans3D, a->dL_dopacities,
                                                               a->dL_dgrads3D, a->dL_dscales, a->dL_dothers, a->dL_dcolors);
     DST_CUDA_TRY(h, cudaGetLastError());
-    h->launches += 3 + 2 * p.rounds;       // logged re-composite or ray init, the rounds, tail, unpack
+    h->launches += 3 + (p.lv.stable ? 3 : 2) * p.rounds;       // logged re-composite or ray init, the rounds, tail, unpack
     return DST_OK;
 }

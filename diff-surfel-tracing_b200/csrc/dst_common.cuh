@@ -83,7 +83,9 @@ struct dst_handle {
     int sm_count;
     // ray scratch of the wavefront trace (grow-only): state records, enumeration requests, hit buffers, live lists
     void* wf_state; size_t wf_state_bytes; void* wf_req; unsigned long long* wf_kbuf; int* wf_kcnt; int* wf_list[2]; int* wf_counts; int* wf_claim;
+    int* wf_tmp; int* wf_wcnt; int* wf_bcnt;      // order-preserving list hand-over (LiveLists in dst_trace.cuh); wf_bcnt holds both counter sets
     long long wf_cap;
+    int stable_lists;             // 1 (default): live lists keep their order from round to round; 0: survivors are appended per warp
     long long wf_min_rays;        // launches with fewer rays skip the wavefront rounds
     // chunk log: the 16-hit chunks every ray composited in the last training forward, chained per ray and segment,
     // so that the backward re-composites them without walking the hierarchy again
@@ -104,8 +106,8 @@ struct dst_handle {
     long long rounds_pending_sig, rounds_known_sig; int rounds_pending_min, rounds_known;
     // optional event timing (dst_profile_enable)
     int profiling;
-    cudaEvent_t* ev[3];           // per kind: 2 * DST_PROF_SLOTS events (start, stop pairs)
-    int ev_n[3];
+    cudaEvent_t* ev[4];           // per kind: 2 * DST_PROF_SLOTS events (start, stop pairs); kind 3 = every gather launch (profiling >= 2)
+    int ev_n[4];
 };
 #define DST_PROF_SLOTS 1024
 // records the start (which_end = 0) or stop (1) event of the current launch of `kind`; no-op unless profiling

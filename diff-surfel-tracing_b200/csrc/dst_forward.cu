@@ -56,6 +56,7 @@ struct FwdParams {
     int* counts;
     int min_count;
     int rounds;
+    LiveLists lv;
     // chunk log (null log_keys: disabled)
     unsigned long long* log_keys; int2* log_hdr; int* log_count; int* log_seg_head; unsigned char* log_ray_ok;
     int log_cap, log_seg_stride;
@@ -342,6 +343,7 @@ __global__ void __launch_bounds__(SHADE_THREADS) k_fwd_shade(const __grid_consta
     for (int i = blockIdx.x * SHADE_THREADS + threadIdx.x; i < n_pad; i += gridDim.x * SHADE_THREADS) {
         const int ray = i < n ? list[i] : -1;
         bool alive = false;
+        int cls = 0;
         if (ray >= 0) {
             FwdState s;
             load_state(p.state, ray, s);
@@ -351,9 +353,11 @@ __global__ void __launch_bounds__(SHADE_THREADS) k_fwd_shade(const __grid_consta
                 EnumReq q;
                 fwd_request(s, q);
                 p.req[ray] = q;
+                cls = s.bounce > 0;
             }
         }
-        append_alive(alive, ray, next_list, p.counts + round + 1);
+        if (p.lv.stable) live_out(p.lv, round, i, alive, ray, cls);
+        else append_alive(alive, ray, next_list, p.counts + round + 1);
     }
     if (DIAG) flush_counters(p.a.counters, tc);
 }
@@ -482,15 +486,17 @@ int dst_prepare_cache(dst_handle* h, const dst_trace_inputs* in, cudaStream_t st
     return DST_OK;
 }
 
-// scratch for `slots` list entries / rays of `state_bytes` each (grow-only)
+// scratch for `slots` list entries / rays of `state_bytes` each (grow-only: a call that needs more slots or a larger
+// state record replaces the buffers with ones that hold the larger of the old and the new value of each)
 int dst_ensure_wavefront(dst_handle* h, long long slots, size_t state_bytes) {
     if (slots <= h->wf_cap && state_bytes <= h->wf_state_bytes) return DST_OK;
-    cudaFree(h->wf_state); cudaFree(h->wf_req); cudaFree(h->wf_kbuf); cudaFree(h->wf_kcnt); cudaFree(h->wf_list[0]); cudaFree(h->wf_list[1]);
-    cudaFree(h->wf_counts); cudaFree(h->wf_claim); h->wf_claim = nullptr;
-    h->wf_state = nullptr; h->wf_req = nullptr; h->wf_kbuf = nullptr; h->wf_kcnt = nullptr; h->wf_list[0] = h->wf_list[1] = nullptr; h->wf_counts = nullptr;
-    h->wf_cap = 0; h->wf_state_bytes = 0;
     const long long cap = slots > h->wf_cap ? slots + slots / 16 + 1024 : h->wf_cap;
     const size_t sb = state_bytes > h->wf_state_bytes ? state_bytes : h->wf_state_bytes;
+    cudaFree(h->wf_state); cudaFree(h->wf_req); cudaFree(h->wf_kbuf); cudaFree(h->wf_kcnt); cudaFree(h->wf_list[0]); cudaFree(h->wf_list[1]);
+    cudaFree(h->wf_counts); cudaFree(h->wf_claim); cudaFree(h->wf_tmp); cudaFree(h->wf_wcnt); cudaFree(h->wf_bcnt);
+    h->wf_state = nullptr; h->wf_req = nullptr; h->wf_kbuf = nullptr; h->wf_kcnt = nullptr; h->wf_list[0] = h->wf_list[1] = nullptr; h->wf_counts = nullptr;
+    h->wf_claim = nullptr; h->wf_tmp = nullptr; h->wf_wcnt = nullptr; h->wf_bcnt = nullptr;
+    h->wf_cap = 0; h->wf_state_bytes = 0;
     cudaError_t e = cudaMalloc(&h->wf_state, sb * (size_t)cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_req, 32 * (size_t)cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_kbuf, 8 * DST_CHUNK * (size_t)cap);
@@ -499,8 +505,21 @@ int dst_ensure_wavefront(dst_handle* h, long long slots, size_t state_bytes) {
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_list[1], 4 * (size_t)cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_counts, 4 * 3 * (DST_WF_ROUNDS + 2));
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_claim, 4 * (size_t)cap);
+    if (e == cudaSuccess) e = cudaMalloc(&h->wf_tmp, 4 * (size_t)(cap + 32));
+    if (e == cudaSuccess) e = cudaMalloc(&h->wf_wcnt, 4 * (size_t)(cap / 32 + 2));
+    if (e == cudaSuccess) e = cudaMalloc(&h->wf_bcnt, 4 * 2 * (size_t)dst_live_blocks(cap));
     if (e != cudaSuccess) { cudaGetLastError(); return dst_set_error(h, DST_E_NOMEM, "ray scratch allocation for %lld rays failed: %s", slots, cudaGetErrorString(e)); }
     h->wf_cap = cap; h->wf_state_bytes = sb;
+    return DST_OK;
+}
+
+// the list hand-over buffers of the handle as the kernels see them; clears both sets of block counters
+int dst_live_lists(dst_handle* h, long long slots, LiveLists* lv, cudaStream_t st) {
+    lv->tmp = h->wf_tmp; lv->wcnt = h->wf_wcnt;
+    lv->bcnt[0] = h->wf_bcnt; lv->bcnt[1] = h->wf_bcnt + dst_live_blocks(h->wf_cap);
+    lv->stable = h->stable_lists;
+    if (lv->stable) DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_bcnt, 0, 4 * 2 * (size_t)dst_live_blocks(h->wf_cap), st));
+    (void)slots;
     return DST_OK;
 }
 
@@ -666,19 +685,26 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
     const bool diag = a->hit_log || a->hit_cnt || a->counters;
     DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 3 * (DST_WF_ROUNDS + 2), st));
     if (wave) DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_claim, 0, 4 * (size_t)slots, st));
+    rc = dst_live_lists(h, slots, &p.lv, st);
+    if (rc != DST_OK) return rc;
+    const int g_compact = (int)((slots + DST_LIVE_BLOCK - 1) / DST_LIVE_BLOCK);
     dst_prof_mark(h, 1, 0, st);
     k_fwd_init<<<(unsigned int)((slots + 255) / 256), 256, 0, st>>>(p, slots);
     const int g_enum = dst_wavefront_grid(h, slots, ENUM_THREADS, DST_ENUM_GRID_PER_SM), g_shade = dst_wavefront_grid(h, slots, SHADE_THREADS, DST_SHADE_GRID_PER_SM);
     for (int r = 0; r < p.rounds; r++) {
+        dst_prof_mark(h, 3, 0, st);
         if (diag) {
             if (refill) k_enum<true, true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
             else k_enum<true, false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
+            dst_prof_mark(h, 3, 1, st);
             k_fwd_shade<true><<<g_shade, SHADE_THREADS, 0, st>>>(p, r);
         } else {
             if (refill) k_enum<false, true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
             else k_enum<false, false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
+            dst_prof_mark(h, 3, 1, st);
             k_fwd_shade<false><<<g_shade, SHADE_THREADS, 0, st>>>(p, r);
         }
+        if (p.lv.stable) k_compact<<<g_compact, 256, 0, st>>>(p.lv, p.counts + r, p.counts + r + 1, p.min_count, p.list[(r + 1) & 1], r);
     }
     // few rays left (or a small call): one warp per ray; many: one thread per ray
     const long long tail_rays = wave ? p.min_count : slots;
@@ -693,7 +719,7 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
     }
     dst_prof_mark(h, 1, 1, st);
     DST_CUDA_TRY(h, cudaGetLastError());
-    h->launches += 2 + 2 * p.rounds;       // ray init, the rounds, tail
+    h->launches += 2 + (p.lv.stable ? 3 : 2) * p.rounds;       // ray init, the rounds, tail
     if (wave) {
         if (!h->rounds_host) {
             if (cudaMallocHost(&h->rounds_host, 4 * (DST_WF_ROUNDS + 2)) != cudaSuccess) { cudaGetLastError(); h->rounds_host = nullptr; }
@@ -795,6 +821,7 @@ extern "C" int dst_forward_static(dst_handle* h, const dst_fwd_args* a, void* st
     p.list[0] = reinterpret_cast<int*>(base + ST_OFF_LIST); p.list[1] = p.list[0];
     p.counts = reinterpret_cast<int*>(base + ST_OFF_COUNTS);
     p.rounds = 0; p.min_count = 1;
+    memset(&p.lv, 0, sizeof(p.lv));                              // no rounds, no list hand-over
     p.log_keys = nullptr; p.log_hdr = nullptr; p.log_count = nullptr; p.log_seg_head = nullptr; p.log_ray_ok = nullptr;
     p.log_cap = 0; p.log_seg_stride = 0;
     // the array keeps the previous call's contents: the round counters must start at zero, everything else is rewritten

@@ -711,6 +711,107 @@ __device__ __forceinline__ void append_alive(bool alive, int ray, int* __restric
     next_list[base + __popc(m & ((1u << lane) - 1u))] = ray;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Order-preserving hand-over of the live list from one round to the next.
+//
+// append_alive() above packs the survivors of every warp behind one atomic counter: cheap, but the
+// warps arrive in whatever order the scheduler ran them, so after a few rounds neighbouring list
+// entries are unrelated rays and the gather kernel's shared walk (one hierarchy walk for 32
+// neighbouring rays) falls apart. The stable form keeps the list in its original order (8x4 pixel
+// tiles, tile after tile) and, within that, puts rays on their primary segment before rays on a
+// reflected one, so that a warp of the next round again holds rays that start close together and
+// are in the same stage:
+//   shade kernel   live_out(): survivor (or -1) of list position i into tmp[i]; survivors per warp
+//                  and class into wcnt[i / 32]; the same added to the counter of the 4096-entry
+//                  block the position lies in (bcnt, two classes packed 16 + 16 bits).
+//   k_compact      one block per 4096 positions: sums the block counters before its own (and all of
+//                  them, for the start of the second class), scans its 128 warp counts and copies
+//                  every survivor to its final position. Block 0 publishes the new list length.
+// The block counters come in two sets used by alternate rounds; k_compact of round r clears the set
+// round r + 1 accumulates into (nothing waits on anything: all of this is ordinary stream order).
+// ---------------------------------------------------------------------------------------------
+#define DST_LIVE_BLOCK 4096
+#define DST_LIVE_CLASS_BIT 30            // ray indices stay below 2^30 (checked on the host)
+struct LiveLists {
+    int* tmp;            // per list position of the current round: ray | class << 30, or -1
+    int* wcnt;           // per 32 positions: survivors of class 0 | survivors of class 1 << 16
+    int* bcnt[2];        // per DST_LIVE_BLOCK positions, same packing; set (round & 1) belongs to the current round
+    int stable;          // 0: append_alive() order (atomic per warp)
+};
+static inline long long dst_live_blocks(long long slots) { return slots / DST_LIVE_BLOCK + 2; }
+int dst_live_lists(dst_handle* h, long long slots, LiveLists* lv, cudaStream_t st);
+
+// called by all 32 lanes of a warp for 32 consecutive list positions (i of lane 0 is a multiple of 32)
+__device__ __forceinline__ void live_out(const LiveLists& lv, int round, int i, bool alive, int ray, int cls) {
+    __syncwarp();
+    const unsigned int m0 = __ballot_sync(0xffffffffu, alive && cls == 0), m1 = __ballot_sync(0xffffffffu, alive && cls != 0);
+    lv.tmp[i] = alive ? (ray | (cls != 0 ? (1 << DST_LIVE_CLASS_BIT) : 0)) : -1;
+    if ((threadIdx.x & 31) == 0) {
+        const int packed = __popc(m0) | (__popc(m1) << 16);
+        lv.wcnt[i >> 5] = packed;
+        if (packed) atomicAdd(lv.bcnt[round & 1] + i / DST_LIVE_BLOCK, packed);
+    }
+}
+
+static __global__ void __launch_bounds__(256) k_compact(LiveLists lv, const int* __restrict__ count_ptr, int* next_count, int min_count,
+                                                        int* __restrict__ next_list, int round) {
+    __shared__ int red[4][8];
+    __shared__ int woff[DST_LIVE_BLOCK / 32];
+    const int n = *count_ptr;
+    if (n < min_count) return;
+    const int nb = (n + DST_LIVE_BLOCK - 1) / DST_LIVE_BLOCK;
+    const int b = blockIdx.x;
+    if (b >= nb) return;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int* bc = lv.bcnt[round & 1];
+    // survivors per class in the blocks before this one, and in all blocks
+    int before0 = 0, before1 = 0, all0 = 0, all1 = 0;
+    for (int j = threadIdx.x; j < nb; j += 256) {
+        const int c = bc[j], c0 = c & 0xffff, c1 = c >> 16;
+        all0 += c0; all1 += c1;
+        if (j < b) { before0 += c0; before1 += c1; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        before0 += __shfl_xor_sync(0xffffffffu, before0, o); before1 += __shfl_xor_sync(0xffffffffu, before1, o);
+        all0 += __shfl_xor_sync(0xffffffffu, all0, o); all1 += __shfl_xor_sync(0xffffffffu, all1, o);
+    }
+    if (lane == 0) { red[0][w] = before0; red[1][w] = before1; red[2][w] = all0; red[3][w] = all1; }
+    // exclusive scan of this block's 128 warp counts (both classes in one packed add: sums stay below 2^16)
+    const int wpos = b * (DST_LIVE_BLOCK / 32) + threadIdx.x;
+    int x = 0;
+    if (threadIdx.x < DST_LIVE_BLOCK / 32 && wpos * 32 < n) x = lv.wcnt[wpos];
+    int incl = x;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += y; }
+    __shared__ int wsum[8];
+    if (lane == 31) wsum[w] = incl;
+    __syncthreads();
+    before0 = before1 = all0 = all1 = 0;
+#pragma unroll
+    for (int k = 0; k < 8; k++) { before0 += red[0][k]; before1 += red[1][k]; all0 += red[2][k]; all1 += red[3][k]; }
+    if (threadIdx.x < DST_LIVE_BLOCK / 32) {
+        int carry = 0;
+        for (int k = 0; k < w; k++) carry += wsum[k];
+        woff[threadIdx.x] = carry + incl - x;
+    }
+    __syncthreads();
+    if (b == 0 && threadIdx.x == 0) *next_count = all0 + all1;
+    if (threadIdx.x == 0) lv.bcnt[(round + 1) & 1][b] = 0;          // the set the next round accumulates into
+    // every warp copies 16 groups of 32 positions
+    for (int g = w; g < DST_LIVE_BLOCK / 32; g += 8) {
+        const int i = (b * (DST_LIVE_BLOCK / 32) + g) * 32 + lane;
+        const int v = i < n ? lv.tmp[i] : -1;          // positions up to the next multiple of 32 were written, the rest is dead
+        const bool alive = v >= 0;
+        const bool second = alive && ((v >> DST_LIVE_CLASS_BIT) & 1);
+        const unsigned int m0 = __ballot_sync(0xffffffffu, alive && !second), m1 = __ballot_sync(0xffffffffu, second);
+        if (!alive) continue;
+        const int off = woff[g], below = (1u << lane) - 1u;
+        const int pos = second ? all0 + before1 + (off >> 16) + __popc(m1 & below) : before0 + (off & 0xffff) + __popc(m0 & below);
+        next_list[pos] = v & ((1 << DST_LIVE_CLASS_BIT) - 1);
+    }
+}
+
 // first round the wavefront kernels left alone (list shorter than min_count)
 __device__ __forceinline__ int first_skipped_round(const int* __restrict__ counts, int rounds, int min_count) {
     for (int r = 0; r < rounds; r++) if (counts[r] < min_count) return r;

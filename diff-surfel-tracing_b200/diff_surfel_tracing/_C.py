@@ -80,6 +80,8 @@ def lib():
         l.dst_kernel_launches.argtypes = [C.c_void_p, C.POINTER(C.c_int64)]
         l.dst_profile_enable.argtypes = [C.c_void_p, C.c_int]
         l.dst_profile_read.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_int32)]
+        l.dst_profile_launches.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_float), C.c_int32, C.POINTER(C.c_int32)]
+        l.dst_debug_round_counts.argtypes = [C.c_void_p, C.POINTER(C.c_int32), C.c_int32, C.c_void_p]
         l.dst_debug_quad_frames.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         _lib = l
     return _lib
@@ -176,9 +178,22 @@ class OptiXStateWrapper:
         _check(self, lib().dst_kernel_launches(self.handle, C.byref(n)))
         return n.value
 
+    def set_stable_lists(self, on):
+        """Wavefront rounds keep the live-ray list in its original (pixel tile) order (default) or append survivors
+        warp by warp as they finish. Scheduling only."""
+        _check(self, lib().dst_set_option(self.handle, 7, int(bool(on))))
+
     def profile(self, on=True):
-        """Records CUDA events around the build, forward and backward kernels of later calls."""
+        """Records CUDA events around the build, forward and backward kernels of later calls; on=2 also around
+        every launch of the gather kernel."""
         _check(self, lib().dst_profile_enable(self.handle, int(on)))
+
+    def profile_launches(self, kind="gather", cap=1024):
+        """Milliseconds of every recorded launch of `kind` since the last read (waits for the events)."""
+        which = ("build", "forward", "backward", "gather").index(kind)
+        buf, n = (C.c_float * cap)(), C.c_int32(0)
+        _check(self, lib().dst_profile_launches(self.handle, which, buf, cap, C.byref(n)))
+        return [buf[i] for i in range(min(n.value, cap))]
 
     def profile_read(self):
         """{kind: (summed ms, launches)} since the last read; waits for the recorded events."""
@@ -187,6 +202,15 @@ class OptiXStateWrapper:
             ms, n = C.c_float(0), C.c_int32(0)
             _check(self, lib().dst_profile_read(self.handle, i, C.byref(ms), C.byref(n)))
             out[k] = (ms.value, n.value)
+        return out
+
+    def round_counts(self):
+        """Live-list length of every wavefront round of the last trace call (synchronises)."""
+        buf = (C.c_int32 * 50)()
+        _check(self, lib().dst_debug_round_counts(self.handle, buf, 50, _stream()))
+        out = list(buf)
+        while out and out[-1] == 0:
+            out.pop()
         return out
 
     def info(self):

@@ -229,6 +229,11 @@ int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t*
  * launch, no re-read of the vertices); zero (default) runs the expansion kernel and then the refit,
  * which is faster on large scenes because the expansion's writes are coalesced. Same results. */
 #define DST_OPT_SINGLE_KERNEL_REFIT 4
+/* Order of the live-ray lists of the wavefront rounds (results are not affected): 1 (default) keeps every
+ * list in the order of the first one (8x4 pixel tiles, tile after tile; within a round, rays on their primary
+ * segment before rays on a reflected one), so that the 32 rays a warp of the gather kernel takes keep
+ * starting close to each other; 0 appends the survivors warp by warp in the order the warps happen to finish. */
+#define DST_OPT_STABLE_LISTS 7
 int dst_set_option(dst_handle* h, int option, int64_t value);
 
 /* Timing of the main kernels with CUDA events on the launching stream. While enabled, every
@@ -237,8 +242,13 @@ int dst_set_option(dst_handle* h, int option, int64_t value);
  * kernel). dst_profile_read waits for the recorded events, returns the summed milliseconds and the
  * number of launches since the last read, and resets the counters. At most 1024 launches per kind
  * are kept between reads. */
+/* on = 2 additionally records a pair around every launch of the gather kernel (which = 3), the kernel that
+ * dominates a trace call; meant for a separate measuring pass, since two event records per wavefront round
+ * are not free. dst_profile_launches is dst_profile_read with the milliseconds of every launch (the first
+ * `cap` of them) instead of their sum. */
 int dst_profile_enable(dst_handle* h, int on);
 int dst_profile_read(dst_handle* h, int which, float* ms_sum, int32_t* launches);
+int dst_profile_launches(dst_handle* h, int which, float* ms, int32_t cap, int32_t* launches);
 
 /* Diagnostics: the DST_CHUNK nearest hits of each ray (one enumeration from the given origins),
  * keys = (bits of t) << 32 | primitive id, ascending; counts = hits found (<= DST_CHUNK).
@@ -247,6 +257,9 @@ int dst_profile_read(dst_handle* h, int which, float* ms_sum, int32_t* launches)
 int dst_debug_knearest(dst_handle* h, const float* ray_o, const float* ray_d, int64_t n_rays,
                        unsigned long long* keys, int32_t* counts, int brute, const float* t_cut,
                        unsigned long long* counters, void* stream);
+/* Diagnostics: synchronises `stream` and copies the live-list length of every wavefront round of the last trace
+ * call (host array of `cap` ints; round r of the call saw counts[r] rays, 0 from the first unused round on). */
+int dst_debug_round_counts(dst_handle* h, int32_t* counts, int32_t cap, void* stream);
 /* Diagnostics: copies the per-quad plane frames (12 floats each, surfel order) to `out`. */
 int dst_debug_quad_frames(dst_handle* h, float* out, void* stream);
 
