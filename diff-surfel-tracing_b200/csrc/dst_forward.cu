@@ -844,3 +844,12 @@ extern "C" int dst_forward_static(dst_handle* h, const dst_fwd_args* a, void* st
     h->launches += 3;
     return DST_OK;
 }
+
+#ifdef DST_ROUND_STATS
+// build-time diagnostic (see dst_trace.cuh): copies and clears the per-round gather statistics of this translation unit
+extern "C" int dst_debug_round_stats(unsigned long long* out) {
+    if (cudaMemcpyFromSymbol(out, g_round_stats, sizeof(unsigned long long) * 64 * 8) != cudaSuccess) return DST_E_CUDA;
+    static unsigned long long zero[64 * 8];
+    return cudaMemcpyToSymbol(g_round_stats, zero, sizeof(zero)) == cudaSuccess ? DST_OK : DST_E_CUDA;
+}
+#endif

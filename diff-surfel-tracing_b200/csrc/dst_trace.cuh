@@ -342,6 +342,15 @@ __device__ __forceinline__ RaySlab make_slab(float ox, float oy, float oz, float
 #ifndef DST_STEAL_MIN_BUSY
 #define DST_STEAL_MIN_BUSY 26    // idle lanes take extra rays only while this many lanes of the warp are still walking
 #endif
+#ifdef DST_ROUND_STATS
+// build-time diagnostic: per wavefront round [0] batches, [1] shared node steps, [2] shared quad steps, [3] private
+// node-phase warp steps, [4] private leaf-phase warp steps (quads), [5] batches that gave the shared walk up,
+// [6] lane tests wanted in the shared phase, [7] lanes active at batch start
+static __device__ unsigned long long g_round_stats[64][8];
+#define RSTAT(i, v) do { const unsigned long long v_ = (v); if (lane == 0) rs[i] += v_; } while (0)      // v may hold a warp vote: every lane evaluates it
+#else
+#define RSTAT(i, v) do { } while (0)
+#endif
 template <bool COUNT, bool REFILL>
 __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumReq* __restrict__ req, const int* __restrict__ list,
                                                        const int* __restrict__ count_ptr, int* cursor, int min_count,
@@ -359,6 +368,9 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const float absmax = __ldg(bvh.header + 6);
     TraceCounters tc = { 0, 0, 0, 0, 0, 0 };
+#ifdef DST_ROUND_STATS
+    unsigned long long rs[8] = { 0, 0, 0, 0, 0, 0, 0, 0 };
+#endif
     unsigned long long stack[DST_ENUM_STACK];
     int sp = 0, n = 0;
     float kmax = -1.0f;
@@ -449,6 +461,7 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
             ray = -1;
         };
         begin_ray();
+        RSTAT(0, 1); RSTAT(7, __popc(__ballot_sync(FULL, active)));
         bool bailed = false, dry = false;      // warp gave up the shared walk / the back of the list is used up (per lane)
         int ssp = 0, scur = __any_sync(FULL, active) ? 0 : DONE;     // shared walk: stack pointer and current link (uniform)
         int s_tests = 0, s_wanted = 0;                                // child tests made together / of them wanted by their lane
@@ -466,6 +479,7 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
                     }
                     ssp = 0; scur = DONE;
                     bailed = true;
+                    RSTAT(5, 1);
                     break;
                 }
                 if (scur >= 0) {
@@ -475,6 +489,7 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
                     const bool w0 = active && h0, w1 = active && h1;
                     const unsigned int m0 = __ballot_sync(FULL, w0), m1 = __ballot_sync(FULL, w1);
                     s_tests += 64; s_wanted += __popc(m0) + __popc(m1);
+                    RSTAT(1, 1); RSTAT(6, __popc(m0) + __popc(m1));
                     const bool s0 = __popc(m0) >= DST_SHARE_VOTE, s1 = __popc(m1) >= DST_SHARE_VOTE;
                     int next = DONE;
                     if (s0 && s1) {
@@ -499,6 +514,7 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
                     const int first = DST_LEAF_FIRST(scur), count = DST_LEAF_COUNT(scur);
                     for (int lq = 0; lq < count; lq++) {
                         if (COUNT && lane == 0) tc.quads++;
+                        RSTAT(2, 1);
                         if (active) offer(first + lq);
                     }
                 }
@@ -532,6 +548,7 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
                 const unsigned int m = __ballot_sync(FULL, is_node);
                 if (m == 0u) break;
                 if (__popc(m) < DST_NODE_VOTE && __any_sync(FULL, cur < 0)) break;
+                RSTAT(3, 1);
                 if (!is_node) continue;
                 float tn0, tn1; bool h0, h1; int l0, l1;
                 test_node(cur, tn0, tn1, h0, h1, l0, l1);
@@ -545,6 +562,11 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
                 else cur = pop();
             }
             // leaf phase
+#ifdef DST_ROUND_STATS
+            { int mx = cur < 0 ? DST_LEAF_COUNT(cur) : 0;
+              for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(FULL, mx, o));
+              RSTAT(4, mx); }
+#endif
             if (cur < 0) {
                 const int first = DST_LEAF_FIRST(cur), count = DST_LEAF_COUNT(cur);
                 for (int lq = 0; lq < count; lq++) { if (COUNT) tc.quads++; offer(first + lq); }
@@ -557,6 +579,9 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
         publish();
     }
     if (COUNT && counters) { atomicAdd(counters + 1, tc.enums); atomicAdd(counters + 2, tc.nodes); atomicAdd(counters + 3, tc.quads); }
+#ifdef DST_ROUND_STATS
+    if (lane == 0) for (int k = 0; k < 8; k++) if (rs[k]) atomicAdd(&g_round_stats[tag & 63][k], rs[k]);
+#endif
 }
 
 // The 16 nearest hits of ONE ray, found by a whole warp (same result as knearest()). For the few rays the

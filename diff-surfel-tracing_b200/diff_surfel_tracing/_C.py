@@ -87,8 +87,9 @@ def lib():
     return _lib
 
 
-def _stream():
-    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+def _stream(state=None):
+    """torch's current stream on the state's GPU (the device the library switches to for the call)."""
+    return C.c_void_p(torch.cuda.current_stream(None if state is None else state.device).cuda_stream)
 
 
 def _check(state, rc):
@@ -97,10 +98,18 @@ def _check(state, rc):
         raise RuntimeError((msg or b"unknown error").decode())
 
 
-def _cuda_f32(t, name):
-    """Contiguous float32 CUDA storage of `t`, 16-byte aligned (the kernels use vector loads)."""
+def _on_device(state, t, name):
+    """Every tensor of a call must live on the GPU the state was created on: the library runs its kernels
+    there, and a pointer into another GPU's memory would fault inside a kernel instead of raising here."""
     if not t.is_cuda:
         raise RuntimeError(f"{name} must be a CUDA tensor")          # CHECK_INPUT, trace_surfels.cpp:23-24
+    if state is not None and t.device.index != state.device:
+        raise RuntimeError(f"{name} is on cuda:{t.device.index} but this tracer state was created on cuda:{state.device}")
+
+
+def _cuda_f32(t, name, state=None):
+    """Contiguous float32 CUDA storage of `t`, 16-byte aligned (the kernels use vector loads)."""
+    _on_device(state, t, name)
     if t.dtype != torch.float32:
         raise RuntimeError(f"{name} must be float32")
     t = t.contiguous()
@@ -131,6 +140,7 @@ class OptiXStateWrapper:
         self.handle = h
         self._keep = None
         self.last_forward_serial = 0
+        self._logged_mid = None
         self.grad_bucket = None     # flat buffer holding the per-surfel gradients of the last backward call
 
     def __del__(self):
@@ -144,7 +154,7 @@ class OptiXStateWrapper:
     def status(self):
         """Synchronises and returns (then clears) the device status bits (DST_STATUS_* of dst.h)."""
         f = C.c_uint32(0)
-        _check(self, lib().dst_status(self.handle, C.byref(f), _stream()))
+        _check(self, lib().dst_status(self.handle, C.byref(f), _stream(self)))
         return f.value
 
     def set_wavefront_min_rays(self, n):
@@ -207,7 +217,7 @@ class OptiXStateWrapper:
     def round_counts(self):
         """Live-list length of every wavefront round of the last trace call (synchronises)."""
         buf = (C.c_int32 * 50)()
-        _check(self, lib().dst_debug_round_counts(self.handle, buf, 50, _stream()))
+        _check(self, lib().dst_debug_round_counts(self.handle, buf, 50, _stream(self)))
         out = list(buf)
         while out and out[-1] == 0:
             out.pop()
@@ -225,17 +235,31 @@ def build_acceleration_structure(state, vertices, triangles, rebuild):
         raise RuntimeError("vertices must have dimensions (num_vertices, 3)")
     if triangles is not None and (triangles.dim() != 2 or triangles.size(1) != 3):
         raise RuntimeError("triangles must have dimensions (num_triangles, 3)")
-    v = _cuda_f32(vertices, "vertices")
+    v = _cuda_f32(vertices, "vertices", state)
     if triangles is not None:
-        if not triangles.is_cuda:
-            raise RuntimeError("triangles must be a CUDA tensor")
+        _on_device(state, triangles, "triangles")
         if triangles.dtype != torch.int32:
             raise RuntimeError("triangles must be int32")
         triangles = triangles.contiguous()
     nt = 0 if triangles is None else triangles.size(0)
-    rc = lib().dst_build(state.handle, v.data_ptr(), v.size(0), _ptr(triangles), nt, int(rebuild), _stream())
+    rc = lib().dst_build(state.handle, v.data_ptr(), v.size(0), _ptr(triangles), nt, int(rebuild), _stream(state))
     _check(state, rc)
     state._keep = (v, triangles)      # the build kernels read them asynchronously on the current stream
+
+
+def _check_element_counts(P, t):
+    """Element counts the kernels rely on (a wrong-sized tensor would be read out of bounds on the device).
+    t: name -> tensor; empty tensors stand for absent optional inputs."""
+    want = dict(vertices=12 * P, background=3, opacities=P, scales=2 * P, rotations=4 * P)
+    if t["colors_precomp"].numel() != 0:
+        want["colors_precomp"] = 3 * P
+    if t["others_precomp"].numel() != 0:
+        want["others_precomp"] = 2 * P
+    for n, cnt in want.items():
+        if t[n].numel() != cnt:
+            raise RuntimeError(f"{n} has {t[n].numel()} elements, expected {cnt} for {P} surfels")
+    if t["shs"].numel() != 0 and (t["shs"].dim() != 3 or t["shs"].size(0) != P or t["shs"].size(2) != 3):
+        raise RuntimeError(f"shs must have dimensions ({P}, coefficients, 3)")
 
 
 def _inputs(state, start_from_first, ray_o, ray_d, vertices, background, means3D, shs, degree, colors_precomp,
@@ -244,13 +268,13 @@ def _inputs(state, start_from_first, ray_o, ray_d, vertices, background, means3D
         raise RuntimeError("means3D must have dimensions (num_points, 3)")
     if ray_o.dim() != 3 or ray_o.size(2) != 3 or ray_o.shape != ray_d.shape:
         raise RuntimeError("ray_o and ray_d must have dimensions (H, W, 3)")
-    keep = dict(ray_o=_cuda_f32(ray_o, "ray_o"), ray_d=_cuda_f32(ray_d, "ray_d"), vertices=_cuda_f32(vertices, "vertices"),
-                background=_cuda_f32(background, "background"), means3D=_cuda_f32(means3D, "means3D"),
-                shs=_cuda_f32(shs, "shs"), colors_precomp=_cuda_f32(colors_precomp, "colors_precomp"),
-                others_precomp=_cuda_f32(others_precomp, "others_precomp"), opacities=_cuda_f32(opacities, "opacities"),
-                scales=_cuda_f32(scales, "scales"), rotations=_cuda_f32(rotations, "rotations"))
+    keep = {n: _cuda_f32(t, n, state) for n, t in (
+        ("ray_o", ray_o), ("ray_d", ray_d), ("vertices", vertices), ("background", background), ("means3D", means3D), ("shs", shs),
+        ("colors_precomp", colors_precomp), ("others_precomp", others_precomp), ("opacities", opacities), ("scales", scales),
+        ("rotations", rotations))}
     if keep["scales"].numel() == 0 or keep["rotations"].numel() == 0:
         raise RuntimeError("scales and rotations are required (a precomputed covariance is never read by the tracer)")
+    _check_element_counts(means3D.size(0), keep)
     i = _TraceInputs()
     i.H, i.W, i.P = ray_o.size(0), ray_o.size(1), means3D.size(0)
     i.sh_degree = int(degree)
@@ -307,12 +331,15 @@ def trace_surfels(state, training, start_from_first, ray_o, ray_d, vertices, bac
     if cam is not None:       # the rays are generated by the first kernel of the call, into ray_o / ray_d
         if keep["ray_o"].data_ptr() != ray_o.data_ptr() or keep["ray_d"].data_ptr() != ray_d.data_ptr():
             raise RuntimeError("with a camera, ray_o and ray_d must be contiguous 16-byte aligned buffers")
-        _check(state, lib().dst_forward_camera(state.handle, C.byref(a), C.byref(cam), _stream()))
+        _check(state, lib().dst_forward_camera(state.handle, C.byref(a), C.byref(cam), _stream(state)))
     else:
-        _check(state, lib().dst_forward(state.handle, C.byref(a), _stream()))
+        _check(state, lib().dst_forward(state.handle, C.byref(a), _stream(state)))
     ser = C.c_uint64(0)
     _check(state, lib().dst_forward_serial(state.handle, C.byref(ser)))
     state.last_forward_serial = ser.value       # names the chunk log this call left in the handle (0: none)
+    # the saved tensor that identifies this call to a backward that is not told the serial (a caller written against
+    # the reference's extension module passes exactly the reference's arguments)
+    state._logged_mid = (mid_val.data_ptr(), tuple(mid_val.shape)) if ser.value else None
     return out_rgb, out_dpt, out_acc, out_norm, out_dist, out_aux, mid_val, a_weights
 
 
@@ -320,14 +347,19 @@ def trace_surfels_backward(state, start_from_first, ray_o, ray_d, vertices, back
                            others_precomp, opacities, scales, scale_modifier, rotations, transMat_precomp, viewmatrix,
                            projmatrix, campos, prefiltered, debug, max_trace_depth, specular_threshold,
                            out_rgb, out_dpt, out_acc, out_norm, out_dist, out_aux, mid_val,
-                           dL_drgb, dL_ddpt, dL_dacc, dL_dnorm, dL_ddist, dL_daux, _diag=None, _forward_serial=0):
+                           dL_drgb, dL_ddpt, dL_dacc, dL_dnorm, dL_ddist, dL_daux, _diag=None, _forward_serial=None):
     """trace_surfels.cpp:307-464. Returns the 12 gradients in the reference's order:
     ray_o, ray_d, means3D, grads3D, grads3D_abs (zeros), shs, colors_precomp, others_precomp,
     opacities, scales, rotations, transMat_precomp (zeros).
 
     `_forward_serial`: `state.last_forward_serial` as it was right after the forward call these saved
     tensors come from; when it still names the handle's chunk log the backward re-composites the logged
-    chunks instead of walking the hierarchy again (same result)."""
+    chunks instead of walking the hierarchy again (same result). When it is not given (None), the call is
+    recognised by its `mid_val` tensor: if that is the one the state's last training forward returned, its
+    serial is used. Pass 0 to force a re-trace."""
+    if _forward_serial is None:
+        key = (mid_val.data_ptr(), tuple(mid_val.shape))
+        _forward_serial = state.last_forward_serial if getattr(state, "_logged_mid", None) == key else 0
     i, keep = _inputs(state, start_from_first, ray_o, ray_d, vertices, background, means3D, shs, degree, colors_precomp,
                       others_precomp, opacities, scales, scale_modifier, rotations, max_trace_depth, specular_threshold)
     H, W, P, M = i.H, i.W, i.P, i.sh_coeffs
@@ -335,13 +367,13 @@ def trace_surfels_backward(state, start_from_first, ray_o, ray_d, vertices, back
         raise RuntimeError(f"mid_val must have {i.mid_stride} channels for max_trace_depth={max_trace_depth}")
     dev = means3D.device
     f32 = dict(dtype=torch.float32, device=dev)
-    sv = [_cuda_f32(t, n) for t, n in ((out_rgb, "out_rgb"), (out_dpt, "out_dpt"), (out_acc, "out_acc"), (out_norm, "out_norm"),
+    sv = [_cuda_f32(t, n, state) for t, n in ((out_rgb, "out_rgb"), (out_dpt, "out_dpt"), (out_acc, "out_acc"), (out_norm, "out_norm"),
                                          (out_dist, "out_dist"), (out_aux, "out_aux"), (mid_val, "mid_val"))]
 
     def up(g, shape, name):
         if g is None:
             return torch.zeros(shape, **f32)
-        return _cuda_f32(g.expand(shape) if g.shape != torch.Size(shape) else g, name)
+        return _cuda_f32(g.expand(shape) if g.shape != torch.Size(shape) else g, name, state)
 
     ug = [up(dL_drgb, (H, W, 3), "dL_drgb"), up(dL_ddpt, (H, W, 1), "dL_ddpt"), up(dL_dacc, (H, W, 1), "dL_dacc"),
           up(dL_dnorm, (H, W, 3), "dL_dnorm"), up(dL_ddist, (H, W, 1), "dL_ddist"), up(dL_daux, (H, W, 2), "dL_daux")]
@@ -380,19 +412,19 @@ def trace_surfels_backward(state, start_from_first, ray_o, ray_d, vertices, back
     if _diag is not None:
         _diag["counters"] = torch.zeros((8,), dtype=torch.int64, device=dev)
         a.counters = _diag["counters"].data_ptr()
-    _check(state, lib().dst_backward(state.handle, C.byref(a), _stream()))
+    _check(state, lib().dst_backward(state.handle, C.byref(a), _stream(state)))
     return g_ray_o, g_ray_d, g_means, g_g3d, g_g3d_abs, g_shs, g_colors, g_others, g_opac, g_scales, g_rot, g_trans
 
 
 def debug_knearest(state, ray_o, ray_d, brute=False, t_cut=None, counters=None):
     """The 16 nearest hits of each ray (one enumeration): (keys (n,16) int64 bit patterns, counts (n,)).
     t_cut: optional (n,) float bound per ray; counters: optional int64 tensor of 8 (nodes -> [2], quads -> [3])."""
-    ro, rd = _cuda_f32(ray_o.reshape(-1, 3), "ray_o"), _cuda_f32(ray_d.reshape(-1, 3), "ray_d")
+    ro, rd = _cuda_f32(ray_o.reshape(-1, 3), "ray_o", state), _cuda_f32(ray_d.reshape(-1, 3), "ray_d", state)
     n = ro.size(0)
     keys = torch.zeros((n, 16), dtype=torch.int64, device=ro.device)
     counts = torch.zeros((n,), dtype=torch.int32, device=ro.device)
     _check(state, lib().dst_debug_knearest(state.handle, ro.data_ptr(), rd.data_ptr(), n, keys.data_ptr(), counts.data_ptr(),
-                                           int(brute), _ptr(t_cut), _ptr(counters), _stream()))
+                                           int(brute), _ptr(t_cut), _ptr(counters), _stream(state)))
     return keys, counts
 
 
@@ -400,7 +432,7 @@ def debug_quad_frames(state):
     """Per-quad plane frames (P, 12) in surfel order, as the build kernels computed them."""
     info = state.info()
     out = torch.zeros((info["surfels"], 12), dtype=torch.float32, device=f"cuda:{state.device}")
-    _check(state, lib().dst_debug_quad_frames(state.handle, out.data_ptr(), _stream()))
+    _check(state, lib().dst_debug_quad_frames(state.handle, out.data_ptr(), _stream(state)))
     return out
 
 
@@ -429,17 +461,21 @@ def trace_surfels_static(state, training, start_from_first, ray_o, ray_d, vertic
     a.training = int(bool(training))
     (a.out_rgb, a.out_dpt, a.out_acc, a.out_norm, a.out_dist, a.out_aux, a.mid_val) = [t.data_ptr() for t in outs]
     a.a_weights = _ptr(a_weights)
-    _check(state, lib().dst_forward_static(state.handle, C.byref(a), _stream()))
+    _check(state, lib().dst_forward_static(state.handle, C.byref(a), _stream(state)))
+    # this entry point keeps no chunk log: a backward of these outputs must re-trace, never reuse the log of an earlier call
+    state.last_forward_serial = 0
+    state._logged_mid = None
     return (*outs, a_weights)
 
 
-def _surfel_params(means3D, scales, rotations):
+def _surfel_params(state, means3D, scales, rotations):
     if means3D.dim() != 2 or means3D.size(1) != 3:
         raise RuntimeError("means3D must have dimensions (num_points, 3)")
     P = means3D.size(0)
     if tuple(scales.shape) != (P, 2) or tuple(rotations.shape) != (P, 4):
         raise RuntimeError("scales must have dimensions (num_points, 2) and rotations (num_points, 4)")
-    return _cuda_f32(means3D.detach(), "means3D"), _cuda_f32(scales.detach(), "scales"), _cuda_f32(rotations.detach(), "rotations")
+    return (_cuda_f32(means3D.detach(), "means3D", state), _cuda_f32(scales.detach(), "scales", state),
+            _cuda_f32(rotations.detach(), "rotations", state))
 
 
 def surfel_quads(state, means3D, scales, rotations, with_triangles=True):
@@ -447,11 +483,11 @@ def surfel_quads(state, means3D, scales, rotations, with_triangles=True):
     v (4P,3) float32 and f (2P,3) int32 (None unless with_triangles) from the activated surfel
     parameters the tracer also receives. No gradient flows to the parameters (the reference detaches
     the vertices before use, example/render.py:62)."""
-    m, s, r = _surfel_params(means3D, scales, rotations)
+    m, s, r = _surfel_params(state, means3D, scales, rotations)
     P = m.size(0)
     v = torch.empty((4 * P, 3), dtype=torch.float32, device=m.device)
     f = torch.empty((2 * P, 3), dtype=torch.int32, device=m.device) if with_triangles else None
-    _check(state, lib().dst_surfel_quads(state.handle, m.data_ptr(), s.data_ptr(), r.data_ptr(), P, v.data_ptr(), _ptr(f), _stream()))
+    _check(state, lib().dst_surfel_quads(state.handle, m.data_ptr(), s.data_ptr(), r.data_ptr(), P, v.data_ptr(), _ptr(f), _stream(state)))
     return v, f
 
 
@@ -459,15 +495,15 @@ def build_from_surfels(state, means3D, scales, rotations, rebuild, vertices=None
     """get_triangles + build_acceleration_structure in one call; returns the vertex tensor (4P,3) to pass
     to the tracer.
     `vertices`, if given, is the (4P,3) buffer to fill (so a training loop can reuse one tensor)."""
-    m, s, r = _surfel_params(means3D, scales, rotations)
+    m, s, r = _surfel_params(state, means3D, scales, rotations)
     P = m.size(0)
     if vertices is None:
         vertices = torch.empty((4 * P, 3), dtype=torch.float32, device=m.device)
     elif tuple(vertices.shape) != (4 * P, 3) or vertices.dtype != torch.float32 or not vertices.is_cuda or \
-            not vertices.is_contiguous() or vertices.data_ptr() % 16:
+            vertices.device.index != state.device or not vertices.is_contiguous() or vertices.data_ptr() % 16:
         raise RuntimeError("vertices must be a contiguous 16-byte aligned float32 CUDA tensor of shape (4 * num_points, 3)")
     _check(state, lib().dst_build_from_surfels(state.handle, m.data_ptr(), s.data_ptr(), r.data_ptr(), P, vertices.data_ptr(),
-                                               int(rebuild), _stream()))
+                                               int(rebuild), _stream(state)))
     state._keep = (m, s, r, vertices)
     return vertices
 
@@ -503,9 +539,12 @@ def pinhole_rays(state, H, W, K, R, T, correct_pix=True, z_depth=False, device=N
     cams = (_Camera * B)()
     for b in range(B):
         cams[b] = make_camera(Kt[b], Rt[b], Tt[b], correct_pix, z_depth)
-    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    dev = torch.device("cuda", state.device) if device is None else torch.device(device)
+    if dev.type != "cuda" or (dev.index is not None and dev.index != state.device):
+        raise RuntimeError(f"rays can only be generated on cuda:{state.device}, the GPU of this tracer state")
+    dev = torch.device("cuda", state.device)
     shape = (B, H, W, 3) if batched else (H, W, 3)
     ray_o = torch.empty(shape, dtype=torch.float32, device=dev)
     ray_d = torch.empty(shape, dtype=torch.float32, device=dev)
-    _check(state, lib().dst_pinhole_rays(state.handle, cams, B, int(H), int(W), ray_o.data_ptr(), ray_d.data_ptr(), _stream()))
+    _check(state, lib().dst_pinhole_rays(state.handle, cams, B, int(H), int(W), ray_o.data_ptr(), ray_d.data_ptr(), _stream(state)))
     return ray_o, ray_d

@@ -83,14 +83,34 @@ def test_enumerator_hierarchy_equals_exhaustive(oracle_mod):
         assert total > 0
 
 
-def test_portable_exp_accuracy(oracle_mod):
-    """The reproducible exp used for the Gaussian falloff stays within 2 ulp of libm on its domain."""
-    w = hp.reduced_workload(1)
-    o_p = oracle_mod.Oracle(oracle_mod.Scene(w["v"]), portable_exp=True).forward(w)
-    o_l = oracle_mod.Oracle(oracle_mod.Scene(w["v"]), portable_exp=False).forward(w)
-    ok = (o_p["fragile"] == 0) & (o_l["fragile"] == 0)
+@pytest.mark.parametrize("config", [1, 3, 5])
+def test_portable_exp_accuracy(oracle_mod, config, record_property):
+    """The reproducible exp used for the Gaussian falloff is about 1 ulp from libm's expf. How far swapping one for
+    the other moves the colour, per configuration. The oracle marks rays that take a decision within rounding of a
+    threshold (alpha within 3e-8 of 1/255, transmittance within 2e-8 of 1e-4, specular weight within 1e-5 of its
+    threshold) as fragile; their number is reported and they are left out of the tight bounds.
+      no bounce   every ray below 1e-5
+      one bounce  every ray below 3e-5 (the reflected segment starts from accumulated sums)
+      two bounces ill-conditioned in the reference's own arithmetic: the second reflected segment starts at
+                  origin + D * direction with D a sum of weighted depths of up to 50 scene units, so a 1-ulp change
+                  of a weight moves that origin by ~1e-4, enough to change which quads a few rays cross. Bounded
+                  statistically: median below 1e-6, 99 % of the rays below 1e-4, every ray below 0.5."""
+    w = hp.reduced_workload(config)
+    sc = oracle_mod.Scene(w["v"])
+    o_p = oracle_mod.Oracle(sc, portable_exp=True, nthreads=4).forward(w)
+    o_l = oracle_mod.Oracle(sc, portable_exp=False, nthreads=4).forward(w)
+    fragile = (o_p["fragile"] != 0) | (o_l["fragile"] != 0)
+    n = fragile.size
     d = np.abs(o_p["rgb"] - o_l["rgb"]).reshape(-1, 3).max(-1)
-    assert d[ok].max() < 1e-5
+    record_property("fragile_rays", int(fragile.sum()))
+    record_property("max_abs_rgb_difference", float(d.max()))
+    print(f"config {config}: {int(fragile.sum())} of {n} rays fragile; rgb difference median {np.median(d):.2e}, "
+          f"99 % {np.quantile(d, 0.99):.2e}, max {d.max():.2e}, rays above 1e-4: {int((d > 1e-4).sum())}")
+    assert fragile.sum() <= max(2, n // 500)
+    if config == 5:
+        assert np.median(d) < 1e-6 and np.quantile(d, 0.99) < 1e-4 and d.max() < 0.5
+    else:
+        assert d[~fragile].max() < (1e-5 if config == 1 else 3e-5)
 
 
 @pytest.mark.parametrize("config", [1, 2, 3, 4, 5])
@@ -200,11 +220,34 @@ def test_binding_rejects_bad_arguments_before_touching_the_gpu():
     from diff_surfel_tracing import _C
     m, s, r = torch.zeros((5, 3)), torch.ones((5, 2)), torch.ones((5, 4))
     with pytest.raises(RuntimeError, match="dimensions"):
-        _C._surfel_params(m.reshape(-1), s, r)
+        _C._surfel_params(None, m.reshape(-1), s, r)
     with pytest.raises(RuntimeError, match="dimensions"):
-        _C._surfel_params(m, s[:, :1], r)
+        _C._surfel_params(None, m, s[:, :1], r)
     with pytest.raises(RuntimeError, match="CUDA tensor"):
-        _C._surfel_params(m, s, r)                       # CPU tensors: CHECK_INPUT of the reference (trace_surfels.cpp:23-24)
+        _C._surfel_params(None, m, s, r)                 # CPU tensors: CHECK_INPUT of the reference (trace_surfels.cpp:23-24)
+    # tensors on another GPU than the tracer state's are refused on the host (a kernel would fault on their pointers)
+    class FakeState:
+        device = 0
+    class FakeTensor:
+        is_cuda = True
+        class device:
+            index = 1
+    with pytest.raises(RuntimeError, match="cuda:1 but this tracer state was created on cuda:0"):
+        _C._on_device(FakeState(), FakeTensor(), "means3D")
+    FakeTensor.device.index = 0
+    _C._on_device(FakeState(), FakeTensor(), "means3D")
+    # element counts of the per-surfel tensors
+    e = torch.empty((0,))
+    good = dict(vertices=torch.zeros((20, 3)), background=torch.zeros(3), opacities=torch.zeros((5, 1)), scales=s, rotations=r,
+                colors_precomp=e, others_precomp=e, shs=torch.zeros((5, 16, 3)))
+    _C._check_element_counts(5, good)
+    for name, bad in (("vertices", torch.zeros((16, 3))), ("background", torch.zeros(1)), ("opacities", torch.zeros((4, 1))),
+                      ("scales", torch.ones((5, 3))), ("rotations", torch.ones((5, 3))), ("colors_precomp", torch.zeros((4, 3))),
+                      ("others_precomp", torch.zeros((5, 1)))):
+        with pytest.raises(RuntimeError, match=name):
+            _C._check_element_counts(5, dict(good, **{name: bad}))
+    with pytest.raises(RuntimeError, match="shs must have dimensions"):
+        _C._check_element_counts(5, dict(good, shs=torch.zeros((4, 16, 3))))
     with pytest.raises(RuntimeError, match="elements"):
         _C.make_camera(np.eye(2), np.eye(3), np.zeros(3))
     cam = _C.make_camera(np.arange(9.0).reshape(3, 3), np.eye(3), np.array([[1.0], [2.0], [3.0]]), correct_pix=False, z_depth=True)

@@ -1,10 +1,12 @@
-"""Full-size checks on the headline workload (3,000,000 surfels, 1080x1920 rays, one bounce).
+"""Checks at the stated sizes of the benchmark configurations.
 
-The CPU oracle cannot finish these sizes, so the checks are size-independent properties:
-the wavefront pipeline and the one-thread-per-ray kernel give identical bits, a refit on unchanged
-vertices reproduces the build, the backward over the forward's chunk log equals the re-tracing
-backward, gradients are linear in the upstream gradient, and a seeded subset of the rays agrees
-with the oracle.
+The CPU oracle cannot trace millions of rays, so at full size the checks are (a) size-independent properties on the
+headline workload (3,000,000 surfels, 1080x1920 rays, one bounce): the wavefront pipeline and the per-ray kernel
+give identical bits, a refit on unchanged vertices reproduces the build, the backward over the forward's chunk log
+equals the re-tracing backward, gradients are linear in the upstream gradient; and (b), on every configuration larger
+than the oracle can finish (2, 3, 4 and 5), a seeded batch of 256 rays of the FULL scene traced by the CUDA path as a
+call of its own and by the oracle: contributing hit sequences and forward outputs bit for bit, every gradient of
+that batch within 1e-3 relative L2.
 """
 import numpy as np
 import pytest
@@ -72,3 +74,47 @@ def test_full_size_properties(full, oracle_mod):
         # the two routes add the same addends in very different orders: at this size float32 atomics differ by
         # a few 1e-4 between routes (1e-5 between two runs of one route); the bar is the usual 1e-3
         assert e1 < 1e-3 and e2 < 1e-3, (k, e1, e2)
+
+
+@pytest.mark.parametrize("config", [2, 3, 4, 5])
+def test_full_scene_ray_sample_against_oracle(oracle_mod, config):
+    """256 seeded rays of the full-size scene, forward and backward, against the CPU oracle."""
+    from diff_surfel_tracing import _C as C
+    w = hp.workloads.make_workload(config)
+    H, W = w["ray_o"].shape[:2]
+    gen = torch.Generator().manual_seed(40 + config)
+    ii, jj = torch.randint(0, H, (256,), generator=gen), torch.randint(0, W, (256,), generator=gen)
+    ws = dict(w, ray_o=w["ray_o"][ii, jj].reshape(16, 16, 3).contiguous(), ray_d=w["ray_d"][ii, jj].reshape(16, 16, 3).contiguous())
+    del w
+    wc = hp.to_cuda(ws)
+    st = C.OptiXStateWrapper("")
+    C.build_acceleration_structure(st, wc["v"], wc["f"], 1)
+    diag = dict(hit_cap=600)
+    got = hp.cuda_forward(C, st, wc, training=True, diag=diag)
+    torch.cuda.synchronize()
+    assert st.status() == 0
+    orc = oracle_mod.Oracle(oracle_mod.Scene(ws["v"]), impl="restatement", hit_cap=600, portable_exp=True)
+    want = orc.forward(ws, training=True)
+    cnt = diag["hit_cnt"].cpu().numpy()
+    assert np.array_equal(cnt, want["hit_cnt"]) and cnt.max() > 0 and cnt.max() <= 600
+    assert np.array_equal(diag["hit_log"].cpu().numpy(), want["hit_log"])
+    for k in ("rgb", "dpt", "acc", "norm", "aux", "mid"):
+        g = got[k].cpu().numpy().reshape(want[k].shape)
+        assert np.array_equal(g.view(np.uint32), want[k].view(np.uint32)), f"config {config}: {k} not bit-identical"
+    wet = got["wet"].cpu().numpy()
+    assert np.abs(wet - want["wet"]).max() <= 1e-4 * max(1.0, float(np.abs(want["wet"]).max()))
+    print(f"config {config}: {int(want['fragile'].sum())} of 256 sampled rays marked fragile by the oracle, "
+          f"{int(cnt.sum())} contributions, longest ray {int(cnt.max())}")
+    up = {k: torch.randn((16, 16, c), generator=gen) for k, c in (("rgb", 3), ("dpt", 1), ("acc", 1), ("norm", 3), ("aux", 2))}
+    ob = orc.backward(ws, want, {k: v.numpy() for k, v in up.items()})
+    assert st.last_forward_serial != 0
+    for serial in (st.last_forward_serial, 0):          # over the chunk log, and re-tracing
+        gb = hp.cuda_backward(C, st, wc, got, {k: v.cuda() for k, v in up.items()}, serial=serial)
+        torch.cuda.synchronize()
+        assert st.status() == 0
+        for k in hp.GRAD_KEYS:
+            g, o = gb[k].cpu().numpy().reshape(ob[k].shape), ob[k]
+            m = np.isfinite(o)
+            assert np.array_equal(np.isfinite(g), m), k
+            e = hp.rel_l2(g[m], o[m])
+            assert e <= 1e-3, f"config {config} grad {k}: rel L2 {e}"
