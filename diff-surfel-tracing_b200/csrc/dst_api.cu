@@ -3,6 +3,7 @@
 #include <stdarg.h>
 #include <string.h>
 #include <new>
+#include <nvtx3/nvToolsExt.h>       // header-only: ranges cost nothing unless a profiler is attached
 
 static char g_global_err[512] = "";
 
@@ -34,6 +35,25 @@ void dst_prof_mark(dst_handle* h, int kind, int which_end, cudaStream_t st) {
 }
 
 namespace {
+// NVTX range around the host side of one entry point (the kernels it enqueues are attributed to it by profilers)
+struct NvtxRange {
+    explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+    ~NvtxRange() { nvtxRangePop(); }
+};
+
+// streaming read of a buffer that fits the L2 cache, for the L2 bandwidth figure reports quote beside the HBM one
+__global__ void __launch_bounds__(256) k_stream_read(const float4* __restrict__ buf, long long n_vec, int reps, float* sink) {
+    float acc = 0.0f;
+    for (int r = 0; r < reps; r++) {
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (long long)gridDim.x * blockDim.x) {
+            float4 v;
+            asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(buf + i));      // L2 only: every repetition really goes to the L2
+            acc += v.x + v.y + v.z + v.w;
+        }
+    }
+    if (acc == 123456.789f) *sink = acc;     // never true for a zeroed buffer; keeps the loads alive
+}
+
 struct DeviceGuard {
     int prev = -1; bool ok = true;
     explicit DeviceGuard(int dev) { if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; } if (prev != dev && cudaSetDevice(dev) != cudaSuccess) ok = false; }
@@ -62,7 +82,6 @@ int dst_create(int device, dst_handle** out) {
     h->device = device;
     h->wf_min_rays = 1 << 15;
     h->log_enabled = 1;
-    h->refill_mode = -1;
     h->stable_lists = 1;
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete h; dst_global_error("dst_create: cudaGetDeviceProperties failed"); return DST_E_CUDA; }
@@ -90,7 +109,7 @@ int dst_destroy(dst_handle* h) {
     if (h->rounds_host) cudaFreeHost(h->rounds_host);
     if (h->rounds_event) cudaEventDestroy(h->rounds_event);
     cudaFree(h->log_keys); cudaFree(h->log_hdr); cudaFree(h->log_count); cudaFree(h->log_seg_head); cudaFree(h->log_ray_ok);
-    cudaFree(h->wf_state); cudaFree(h->wf_req); cudaFree(h->wf_kbuf); cudaFree(h->wf_kcnt); cudaFree(h->wf_list[0]); cudaFree(h->wf_list[1]); cudaFree(h->wf_counts); cudaFree(h->wf_claim);
+    cudaFree(h->wf_state); cudaFree(h->wf_req); cudaFree(h->wf_kbuf); cudaFree(h->wf_kcnt); cudaFree(h->wf_list[0]); cudaFree(h->wf_list[1]); cudaFree(h->wf_counts);
     cudaFree(h->wf_tmp); cudaFree(h->wf_wcnt); cudaFree(h->wf_bcnt);
     for (int k = 0; k < 4; k++) {
         if (h->ev[k]) { for (int i = 0; i < 2 * DST_PROF_SLOTS; i++) cudaEventDestroy(h->ev[k][i]); delete[] h->ev[k]; }
@@ -103,6 +122,7 @@ const char* dst_last_error(const dst_handle* h) { return h ? h->err : g_global_e
 
 int dst_build(dst_handle* h, const float* vertices, int64_t n_vertices, const int32_t* triangles, int64_t n_triangles,
               int rebuild, void* stream) {
+    NvtxRange range("dst_build");
     if (!h) return DST_E_ARG;
     if (!vertices) return dst_set_error(h, DST_E_ARG, "vertices is null");
     if (n_vertices <= 0 || (n_vertices & 3)) return dst_set_error(h, DST_E_ARG, "vertices must hold 4 vertices per surfel, got %lld", (long long)n_vertices);
@@ -125,6 +145,7 @@ int dst_surfel_quads(dst_handle* h, const float* means3D, const float* scales, c
 
 int dst_build_from_surfels(dst_handle* h, const float* means3D, const float* scales, const float* rotations, int64_t n_surfels,
                            float* vertices, int rebuild, void* stream) {
+    NvtxRange range("dst_build_from_surfels");
     if (!h) return DST_E_ARG;
     if (!means3D || !scales || !rotations || !vertices) return dst_set_error(h, DST_E_ARG, "a required pointer is null");
     DeviceGuard g(h->device);
@@ -142,6 +163,7 @@ int dst_pinhole_rays(dst_handle* h, const dst_camera* cameras, int n_cameras, in
 }
 
 int dst_forward_camera(dst_handle* h, const dst_fwd_args* args, const dst_camera* camera, void* stream) {
+    NvtxRange range("dst_forward_camera");
     if (!h) return DST_E_ARG;
     if (!args || !camera) return dst_set_error(h, DST_E_ARG, "args or camera is null");
     DeviceGuard g(h->device);
@@ -150,6 +172,7 @@ int dst_forward_camera(dst_handle* h, const dst_fwd_args* args, const dst_camera
 }
 
 int dst_forward(dst_handle* h, const dst_fwd_args* args, void* stream) {
+    NvtxRange range("dst_forward");
     if (!h) return DST_E_ARG;
     if (!args) return dst_set_error(h, DST_E_ARG, "args is null");
     DeviceGuard g(h->device);
@@ -158,6 +181,7 @@ int dst_forward(dst_handle* h, const dst_fwd_args* args, void* stream) {
 }
 
 int dst_backward(dst_handle* h, const dst_bwd_args* args, void* stream) {
+    NvtxRange range("dst_backward");
     if (!h) return DST_E_ARG;
     if (!args) return dst_set_error(h, DST_E_ARG, "args is null");
     DeviceGuard g(h->device);
@@ -198,7 +222,6 @@ int dst_set_option(dst_handle* h, int option, int64_t value) {
         case DST_OPT_WAVEFRONT_MIN_RAYS: h->wf_min_rays = value < 0 ? 0 : value; return DST_OK;
         case DST_OPT_CHUNK_LOG_MAX_RECORDS: h->log_max_records = value < 0 ? 0 : value; h->log_serial = 0; return DST_OK;
         case DST_OPT_IMAGE_WIDTH: h->image_width = value < 0 ? 0 : value; h->log_serial = 0; return DST_OK;
-        case DST_OPT_GATHER_REFILL: h->refill_mode = value < 0 ? -1 : (value != 0); return DST_OK;
         case DST_OPT_SINGLE_KERNEL_REFIT: h->single_kernel_refit = value != 0; return DST_OK;
         case DST_OPT_STABLE_LISTS: h->stable_lists = value != 0; return DST_OK;
         case DST_OPT_CHUNK_LOG: h->log_enabled = value != 0; if (!h->log_enabled) h->log_serial = 0; return DST_OK;
@@ -263,6 +286,41 @@ int dst_debug_round_counts(dst_handle* h, int32_t* counts, int32_t cap, void* st
     DST_CUDA_TRY(h, cudaMemcpyAsync(counts, h->wf_counts, 4 * (size_t)n, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     DST_CUDA_TRY(h, cudaStreamSynchronize((cudaStream_t)stream));
     for (int i = n; i < cap; i++) counts[i] = 0;
+    return DST_OK;
+}
+
+int dst_debug_read_bandwidth(dst_handle* h, int64_t bytes, int reps, float* gb_per_s, void* stream) {
+    if (!h || !gb_per_s || bytes < (1 << 20) || reps < 1) return DST_E_ARG;
+    DeviceGuard g(h->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    float4* buf = nullptr; float* sink = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    const long long n_vec = bytes / 16;
+    int rc = DST_OK;
+    if (cudaMalloc(&buf, (size_t)n_vec * 16) != cudaSuccess || cudaMalloc(&sink, 4) != cudaSuccess) { cudaGetLastError(); rc = dst_set_error(h, DST_E_NOMEM, "bandwidth probe allocation failed"); }
+    if (rc == DST_OK && (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess)) rc = dst_set_error(h, DST_E_CUDA, "event creation failed");
+    if (rc == DST_OK) {
+        cudaMemsetAsync(buf, 0, (size_t)n_vec * 16, st);
+        const int grid = h->sm_count * 8;
+        k_stream_read<<<grid, 256, 0, st>>>(buf, n_vec, 2, sink);          // warm the cache
+        cudaEventRecord(e0, st);
+        k_stream_read<<<grid, 256, 0, st>>>(buf, n_vec, reps, sink);
+        cudaEventRecord(e1, st);
+        float ms = 0.f;
+        if (cudaEventSynchronize(e1) != cudaSuccess || cudaEventElapsedTime(&ms, e0, e1) != cudaSuccess || !(ms > 0.f)) rc = dst_set_error(h, DST_E_CUDA, "bandwidth probe failed: %s", cudaGetErrorString(cudaGetLastError()));
+        else *gb_per_s = (float)((double)n_vec * 16.0 * reps / (ms * 1e-3) / 1e9);
+    }
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+    cudaFree(buf); cudaFree(sink);
+    return rc;
+}
+
+int dst_debug_chunk_log(const dst_handle* h, int64_t* records_wanted, int64_t* records_held, int64_t* bytes_per_record) {
+    if (!h) return DST_E_ARG;
+    if (records_wanted) *records_wanted = (h->log_needed_host && h->log_needed_event && cudaEventQuery(h->log_needed_event) == cudaSuccess) ? *h->log_needed_host : -1;
+    if (records_held) *records_held = h->log_cap;
+    if (bytes_per_record) *bytes_per_record = 8 * DST_CHUNK + (int64_t)sizeof(int2);
     return DST_OK;
 }
 

@@ -607,10 +607,8 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
                          h->log_depth == a->in.max_trace_depth;
     p.log_keys = h->log_keys; p.log_hdr = h->log_hdr; p.log_seg_head = h->log_seg_head; p.log_ray_ok = h->log_ray_ok;
     p.log_seg_stride = a->in.max_trace_depth + 1;
-    DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 3 * (DST_WF_ROUNDS + 2), st));
+    DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 2 * (DST_WF_ROUNDS + 2), st));
     const bool wave = slots >= h->wf_min_rays;
-    const int refill = h->refill_mode < 0 ? (a->in.max_trace_depth >= 2) : (h->refill_mode != 0);
-    if (wave) DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_claim, 0, 4 * (size_t)slots, st));
     rc = dst_live_lists(h, slots, &p.lv, st);
     if (rc != DST_OK) return rc;
     const int g_compact = (int)((slots + DST_LIVE_BLOCK - 1) / DST_LIVE_BLOCK);
@@ -634,17 +632,11 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
     const int g_enum = dst_wavefront_grid(h, slots, ENUM_THREADS, 10), g_shade = dst_wavefront_grid(h, slots, BWD_THREADS, 4);
     for (int r = 0; r < p.rounds; r++) {
         dst_prof_mark(h, 3, 0, st);
-        if (diag) {
-            if (refill) k_enum<true, true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
-            else k_enum<true, false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
-            dst_prof_mark(h, 3, 1, st);
-            k_bwd_shade<true><<<g_shade, BWD_THREADS, 0, st>>>(p, r);
-        } else {
-            if (refill) k_enum<false, true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
-            else k_enum<false, false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
-            dst_prof_mark(h, 3, 1, st);
-            k_bwd_shade<false><<<g_shade, BWD_THREADS, 0, st>>>(p, r);
-        }
+        launch_gather(diag, g_enum, st, p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt,
+                      p.status, a->counters, r + 1);
+        dst_prof_mark(h, 3, 1, st);
+        if (diag) k_bwd_shade<true><<<g_shade, BWD_THREADS, 0, st>>>(p, r);
+        else k_bwd_shade<false><<<g_shade, BWD_THREADS, 0, st>>>(p, r);
         if (p.lv.stable) k_compact<<<g_compact, 256, 0, st>>>(p.lv, p.counts + r, p.counts + r + 1, p.min_count, p.list[(r + 1) & 1], r);
     }
     const int g_tail = dst_wavefront_grid(h, wave ? p.min_count : slots, BWD_THREADS, 4);

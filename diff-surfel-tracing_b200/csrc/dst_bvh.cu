@@ -253,7 +253,22 @@ __global__ void k_single_leaf(BvhNode* nodes, int* leaf_parent, int* node_parent
 #ifndef DST_COST_NODE
 #define DST_COST_NODE 1.2f
 #endif
+// Cost of testing a leaf run of `count` quads, in units of one child-box test. The gather kernel tests a run of more
+// than DST_HULL_MIN quads with one quad per lane against the hull of its batch of rays (a fixed cost of a few node
+// steps for up to 32 quads) and hands only the survivors to all lanes for the exact test; shorter runs are tested
+// exactly right away. Where boxes overlap heavily (quads crossing each other in all directions) descending costs
+// far more than that and subtrees collapse into runs of up to DST_LEAF_MAX quads; where the children of a node
+// share little space (quads tiling a surface) the tree is kept down to single quads.
+#ifndef DST_RUN_FIXED
+#define DST_RUN_FIXED 3.5f
+#endif
+#ifndef DST_RUN_PER_QUAD
+#define DST_RUN_PER_QUAD 0.25f
+#endif
 #define DST_COST_QUAD 1.0f
+__device__ __forceinline__ float run_cost(int count) {
+    return count <= DST_HULL_MIN ? DST_COST_QUAD * (float)count : DST_RUN_FIXED + DST_RUN_PER_QUAD * (float)count;
+}
 __device__ __forceinline__ float box_area(const float* lo, const float* hi) {
     const float dx = hi[0] - lo[0], dy = hi[1] - lo[1], dz = hi[2] - lo[2];
     const float a = dx * dy + dy * dz + dz * dx;
@@ -333,7 +348,7 @@ __global__ void __launch_bounds__(256) k_refit(const float* __restrict__ verts, 
     quads[3 * (size_t)pos + 0] = make_float4(q.p0x, q.p0y, q.p0z, q.nx);
     quads[3 * (size_t)pos + 1] = make_float4(q.ny, q.nz, q.wux, q.wuy);
     quads[3 * (size_t)pos + 2] = make_float4(q.wuz, q.wvx, q.wvy, q.wvz);
-    leaf_gid[pos] = gid << 4;       // reference = surfel id << 4 | sub-rectangle
+    leaf_gid[pos] = gid;
     float lo[3], hi[3];
     quad_box(v, lo, hi);
     int child = ~pos;                           // topology id of the subtree being carried up
@@ -372,7 +387,7 @@ __global__ void __launch_bounds__(256) k_refit(const float* __restrict__ verts, 
         const float p_me = a_all > 0.0f ? fminf(a_me / a_all, 1.0f) : 1.0f, p_sib = a_all > 0.0f ? fminf(a_sib / a_all, 1.0f) : 1.0f;
         const float cost_split = DST_COST_NODE + p_me * cost + p_sib * sib_cost;
         const int count = node_count[parent];
-        const float cost_run = DST_COST_QUAD * (float)count;
+        const float cost_run = run_cost(count);
         if (count <= DST_LEAF_MAX && cost_run <= cost_split) { link = DST_LEAF_LINK(node_first[parent], count); cost = cost_run; }
         else { link = parent; cost = cost_split; }
         child = parent;
@@ -386,7 +401,7 @@ __global__ void __launch_bounds__(256) k_export_frames(int P, const float4* __re
     const int pos = blockIdx.x * blockDim.x + threadIdx.x;
     if (pos >= P) return;
     const float4 a = quads[3 * (size_t)pos], b = quads[3 * (size_t)pos + 1], c = quads[3 * (size_t)pos + 2];
-    float* o = out + 12 * (size_t)(leaf_gid[pos] >> 4);
+    float* o = out + 12 * (size_t)leaf_gid[pos];
     o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
     o[8] = c.x; o[9] = c.y; o[10] = c.z; o[11] = c.w;
 }
@@ -485,7 +500,7 @@ int dst_bvh_build_impl(dst_handle* h, const float* v, int64_t P, int rebuild, cu
         }
         // 8 passes: the sorted data is back in keys / vals
         if (n > 1) k_karras<<<(n - 1 + tpb - 1) / tpb, tpb, 0, st>>>(h->keys, n, h->nodes, h->leaf_parent, h->node_parent, h->node_first, h->node_count);
-        h->P = P; h->nrefs = P;
+        h->P = P;
     } else if (from_surfels && !h->single_kernel_refit) {
         // measured at 3M surfels: the coalesced expansion pass (0.07 ms) plus the refit's gathered re-read of the
         // vertices is faster than one kernel that scatters 48-byte vertex writes in Morton order (0.57 vs 0.64 ms)

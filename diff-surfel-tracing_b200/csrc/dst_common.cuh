@@ -22,8 +22,9 @@ struct __align__(16) BvhNode {
 #define DST_LEAF_FLAG 0x80000000u
 #define DST_LEAF_POS_BITS 26
 #ifndef DST_LEAF_MAX
-#define DST_LEAF_MAX 16               // most quads in one run (at most 32: five count bits)
+#define DST_LEAF_MAX 32               // most quads in one run (five count bits; the gather kernel tests a run with one quad per lane)
 #endif
+#define DST_HULL_MIN 2                 // runs of at most this many quads are tested exactly by every lane, longer ones go through the hull test first
 #define DST_LEAF_LINK(first, count) ((int)(DST_LEAF_FLAG | ((unsigned int)((count) - 1) << DST_LEAF_POS_BITS) | (unsigned int)(first)))
 #define DST_LEAF_FIRST(link) ((int)((unsigned int)(link) & ((1u << DST_LEAF_POS_BITS) - 1u)))
 #define DST_LEAF_COUNT(link) ((int)(((unsigned int)(link) >> DST_LEAF_POS_BITS) & 31u) + 1)
@@ -37,8 +38,7 @@ struct BvhView {
     const float4* quads;
     const int* leaf_gid;
     const float* header;
-    int P;          // surfels
-    int nrefs;      // leaves (>= P when large quads are split into several references)
+    int P;          // surfels = leaves
 };
 
 // Per-surfel shading record rebuilt at the start of every trace call (parameters change each
@@ -57,7 +57,6 @@ struct dst_handle {
     char err[512];
     bool built;
     int64_t P;            // surfels of the current hierarchy
-    int64_t nrefs;        // leaves of the current hierarchy
     int64_t cap;          // surfels the build buffers can hold
     BvhNode* nodes;
     float4* quads;
@@ -78,11 +77,10 @@ struct dst_handle {
     float* arena;  int64_t arena_cap;
     void* cam_dev;      // camera constants of the last ray-generation call
     long long image_width;     // hint: rays given as (B, h*w, 3) are whole images of this width (0: unknown)
-    int refill_mode;           // gather kernel: idle lanes take extra reflected-segment rays (-1: when max_trace_depth >= 2, 0: never, 1: always)
     int single_kernel_refit;   // dst_build_from_surfels(rebuild = 0): expand the quads inside the refit kernel
     int sm_count;
     // ray scratch of the wavefront trace (grow-only): state records, enumeration requests, hit buffers, live lists
-    void* wf_state; size_t wf_state_bytes; void* wf_req; unsigned long long* wf_kbuf; int* wf_kcnt; int* wf_list[2]; int* wf_counts; int* wf_claim;
+    void* wf_state; size_t wf_state_bytes; void* wf_req; unsigned long long* wf_kbuf; int* wf_kcnt; int* wf_list[2]; int* wf_counts;
     int* wf_tmp; int* wf_wcnt; int* wf_bcnt;      // order-preserving list hand-over (LiveLists in dst_trace.cuh); wf_bcnt holds both counter sets
     long long wf_cap;
     int stable_lists;             // 1 (default): live lists keep their order from round to round; 0: survivors are appended per warp

@@ -452,7 +452,7 @@ __global__ void __launch_bounds__(TAIL_THREADS) k_knearest(BvhView bvh, const fl
 BvhView dst_bvh_view(const dst_handle* h) {
     BvhView b;
     b.nodes = reinterpret_cast<const float4*>(h->nodes);
-    b.quads = h->quads; b.leaf_gid = h->leaf_gid; b.header = h->header; b.P = (int)h->P; b.nrefs = (int)h->nrefs;
+    b.quads = h->quads; b.leaf_gid = h->leaf_gid; b.header = h->header; b.P = (int)h->P;
     return b;
 }
 
@@ -493,9 +493,9 @@ int dst_ensure_wavefront(dst_handle* h, long long slots, size_t state_bytes) {
     const long long cap = slots > h->wf_cap ? slots + slots / 16 + 1024 : h->wf_cap;
     const size_t sb = state_bytes > h->wf_state_bytes ? state_bytes : h->wf_state_bytes;
     cudaFree(h->wf_state); cudaFree(h->wf_req); cudaFree(h->wf_kbuf); cudaFree(h->wf_kcnt); cudaFree(h->wf_list[0]); cudaFree(h->wf_list[1]);
-    cudaFree(h->wf_counts); cudaFree(h->wf_claim); cudaFree(h->wf_tmp); cudaFree(h->wf_wcnt); cudaFree(h->wf_bcnt);
+    cudaFree(h->wf_counts); cudaFree(h->wf_tmp); cudaFree(h->wf_wcnt); cudaFree(h->wf_bcnt);
     h->wf_state = nullptr; h->wf_req = nullptr; h->wf_kbuf = nullptr; h->wf_kcnt = nullptr; h->wf_list[0] = h->wf_list[1] = nullptr; h->wf_counts = nullptr;
-    h->wf_claim = nullptr; h->wf_tmp = nullptr; h->wf_wcnt = nullptr; h->wf_bcnt = nullptr;
+    h->wf_tmp = nullptr; h->wf_wcnt = nullptr; h->wf_bcnt = nullptr;
     h->wf_cap = 0; h->wf_state_bytes = 0;
     cudaError_t e = cudaMalloc(&h->wf_state, sb * (size_t)cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_req, 32 * (size_t)cap);
@@ -503,8 +503,7 @@ int dst_ensure_wavefront(dst_handle* h, long long slots, size_t state_bytes) {
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_kcnt, 4 * (size_t)cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_list[0], 4 * (size_t)cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_list[1], 4 * (size_t)cap);
-    if (e == cudaSuccess) e = cudaMalloc(&h->wf_counts, 4 * 3 * (DST_WF_ROUNDS + 2));
-    if (e == cudaSuccess) e = cudaMalloc(&h->wf_claim, 4 * (size_t)cap);
+    if (e == cudaSuccess) e = cudaMalloc(&h->wf_counts, 4 * 2 * (DST_WF_ROUNDS + 2));
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_tmp, 4 * (size_t)(cap + 32));
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_wcnt, 4 * (size_t)(cap / 32 + 2));
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_bcnt, 4 * 2 * (size_t)dst_live_blocks(cap));
@@ -659,7 +658,6 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
     }
     // small launches go straight to the per-ray kernel; large ones run wavefront rounds until few rays are left
     const bool wave = slots >= h->wf_min_rays;
-    const int refill = h->refill_mode < 0 ? (a->in.max_trace_depth >= 2) : (h->refill_mode != 0);
     p.rounds = wave ? DST_WF_ROUNDS : 0;
     {
         long long hand_over = slots / DST_TAIL_DIV > DST_TAIL_MIN ? slots / DST_TAIL_DIV : DST_TAIL_MIN;
@@ -683,8 +681,7 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
         }
     }
     const bool diag = a->hit_log || a->hit_cnt || a->counters;
-    DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 3 * (DST_WF_ROUNDS + 2), st));
-    if (wave) DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_claim, 0, 4 * (size_t)slots, st));
+    DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 2 * (DST_WF_ROUNDS + 2), st));
     rc = dst_live_lists(h, slots, &p.lv, st);
     if (rc != DST_OK) return rc;
     const int g_compact = (int)((slots + DST_LIVE_BLOCK - 1) / DST_LIVE_BLOCK);
@@ -693,17 +690,11 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
     const int g_enum = dst_wavefront_grid(h, slots, ENUM_THREADS, DST_ENUM_GRID_PER_SM), g_shade = dst_wavefront_grid(h, slots, SHADE_THREADS, DST_SHADE_GRID_PER_SM);
     for (int r = 0; r < p.rounds; r++) {
         dst_prof_mark(h, 3, 0, st);
-        if (diag) {
-            if (refill) k_enum<true, true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
-            else k_enum<true, false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, a->counters, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
-            dst_prof_mark(h, 3, 1, st);
-            k_fwd_shade<true><<<g_shade, SHADE_THREADS, 0, st>>>(p, r);
-        } else {
-            if (refill) k_enum<false, true><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
-            else k_enum<false, false><<<g_enum, ENUM_THREADS, 0, st>>>(p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt, p.status, nullptr, p.counts + 2 * (DST_WF_ROUNDS + 2) + r, h->wf_claim, r + 1);
-            dst_prof_mark(h, 3, 1, st);
-            k_fwd_shade<false><<<g_shade, SHADE_THREADS, 0, st>>>(p, r);
-        }
+        launch_gather(diag, g_enum, st, p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt,
+                      p.status, a->counters, r + 1);
+        dst_prof_mark(h, 3, 1, st);
+        if (diag) k_fwd_shade<true><<<g_shade, SHADE_THREADS, 0, st>>>(p, r);
+        else k_fwd_shade<false><<<g_shade, SHADE_THREADS, 0, st>>>(p, r);
         if (p.lv.stable) k_compact<<<g_compact, 256, 0, st>>>(p.lv, p.counts + r, p.counts + r + 1, p.min_count, p.list[(r + 1) & 1], r);
     }
     // few rays left (or a small call): one warp per ray; many: one thread per ray
@@ -792,12 +783,13 @@ extern "C" int dst_forward_static(dst_handle* h, const dst_fwd_args* a, void* st
         return dst_set_error(h, DST_E_ARG, "a forward output pointer is null");
     if ((reinterpret_cast<uintptr_t>(a->mid_val) & 15) != 0) return dst_set_error(h, DST_E_ARG, "mid_val must be 16-byte aligned");
     const long long R = (long long)a->in.H * a->in.W;
-    const bool tiled = a->in.H >= 16;
-    const long long slots = slots_of_grid(a->in.H, a->in.W, tiled);
     if (a->in.P > DST_STATIC_MAX_SURFELS)
         return dst_set_error(h, DST_E_ARG, "dst_forward_static handles at most %d surfels per call, got %d (use dst_forward)", DST_STATIC_MAX_SURFELS, a->in.P);
-    if (R > DST_STATIC_MAX_RAYS || slots > ST_SLOTS)
+    if (R > DST_STATIC_MAX_RAYS)
         return dst_set_error(h, DST_E_ARG, "dst_forward_static handles at most %d rays per call, got %lld (use dst_forward)", DST_STATIC_MAX_RAYS, R);
+    // 8x4 pixel tiles round the grid up; a narrow grid whose tiled form would not fit the list is walked in ray order instead
+    const bool tiled = a->in.H >= 16 && slots_of_grid(a->in.H, a->in.W, true) <= ST_SLOTS;
+    const long long slots = slots_of_grid(a->in.H, a->in.W, tiled);
     if (h->device < 0 || h->device >= 64) return dst_set_error(h, DST_E_ARG, "device index %d out of range", h->device);
     // one-time set-up per device, with that device current: the device address of the scratch array
     if (!g_static_ptr[h->device]) {

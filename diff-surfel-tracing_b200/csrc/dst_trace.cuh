@@ -7,14 +7,13 @@
 #define DST_STACK 96                 // >= depth bound of a Karras tree over 63-bit keys + 32-bit index tie-breaks
 #define DST_MAX_CHUNKS 4096          // bound on enumerations per ray segment (the reference loops without one)
 #define DST_MAX_INTERSECTION 256     // optix_tracer/config.h:23
-#define DST_REF_SHIFT 4                // leaf reference = surfel id << 4 | sub-rectangle (iu << 2 | iv)
-#define DST_NODE_VOTE 10
+#define DST_NODE_VOTE 10                // lanes with node work needed to stay in the node phase of k_enum
 #ifndef DST_SHARE_MIN_PCT
 #define DST_SHARE_MIN_PCT 25              // the warp gives up walking together when fewer than this % of the lane tests are wanted
 #endif
 #ifndef DST_SHARE_VOTE
 #define DST_SHARE_VOTE 1                // lanes that must want a subtree for the warp to walk it together (k_enum)
-#endif               // lanes with node work needed to stay in the node phase of k_enum
+#endif
 #define DST_PAD_FACTOR 4e-6f         // box padding per unit of coordinate magnitude, see knearest()
 
 struct TraceCounters { unsigned long long segs, enums, nodes, quads, evals, contribs; };
@@ -50,12 +49,11 @@ __device__ __forceinline__ int knearest(const BvhView& bvh, float ox, float oy, 
         if (COUNT) tc.quads++;
         float t; int tri;
         if (!ray_quad(qa, qb, qc, ox, oy, oz, dx, dy, dz, kmax, t, tri)) return;
-        const unsigned int gid = (unsigned int)__ldg(bvh.leaf_gid + pos) >> DST_REF_SHIFT;
+        const unsigned int gid = (unsigned int)__ldg(bvh.leaf_gid + pos);
         const unsigned long long key = make_key(t, 2u * gid + (unsigned int)tri);
         if (n == DST_CHUNK && key >= kb[(DST_CHUNK - 1) * KS]) return;
         int j = n;
         while (j > 0 && kb[(j - 1) * KS] > key) j--;
-        if (j > 0 && kb[(j - 1) * KS] == key) return;       // the same hit reached through another leaf of a split quad
         if (n == DST_CHUNK) n = DST_CHUNK - 1;
         for (int i = n; i > j; i--) kb[i * KS] = kb[(i - 1) * KS];
         kb[j * KS] = key;
@@ -64,7 +62,7 @@ __device__ __forceinline__ int knearest(const BvhView& bvh, float ox, float oy, 
     };
 
     if (BRUTE) {
-        for (int pos = 0; pos < bvh.nrefs; pos++) offer(pos);
+        for (int pos = 0; pos < bvh.P; pos++) offer(pos);
         return n;
     }
 
@@ -311,37 +309,84 @@ __device__ __forceinline__ RaySlab make_slab(float ox, float oy, float oz, float
 
 // Gather kernel: per live ray, the 16 nearest hits from the requested origin (same result as knearest()).
 //
-// A warp takes 32 consecutive entries of the live list: neighbouring pixels, whose rays start close to
-// each other. Large overlapping quads put hundreds of boxes around any origin, and every one of the
-// 32 rays has to open them, so the walk is split in two:
-//   shared phase   the warp walks the hierarchy TOGETHER from the root with one stack; a node is
-//                  fetched once (one broadcast load instead of 32 scattered ones) and every lane tests
-//                  its own ray against both child boxes. A child wanted by at least DST_SHARE_VOTE
-//                  lanes (1: any lane, measured best) stays in the shared walk; a child wanted by fewer
-//                  goes onto the private stacks of those lanes. Leaf runs reached here are tested by
-//                  all lanes. When most lanes sit out most tests (after 32 nodes, under
-//                  DST_SHARE_MIN_PCT % of the lane x test slots wanted) the warp gives the shared walk
-//                  up: every lane takes the pending subtrees onto its own stack.
-//   private phase  every lane drains its own stack as in knearest(), lanes alternating between a
-//                  node phase (kept while at least DST_NODE_VOTE lanes have node work) and a leaf phase.
-// Pruning uses each lane's own 16th-nearest distance throughout, so the hit set is exactly that of
-// an independent walk per ray. Blocks are persistent and take batches from a shared cursor.
-//   refill         a batch that gave up the shared walk (incoherent rays, typically after a bounce) runs
-//                  lane by lane, and lanes finish at very different times. While at least DST_STEAL_MIN_BUSY
-//                  lanes are still walking, a lane that is done publishes its chunk and takes one more
-//                  ray from the BACK of the list (second cursor) for a walk of its own from the root.
-//                  List positions are claimed with atomicMax(claim[pos], tag) (tag = round + 1; the
-//                  claim words are zeroed once per call), so front batches and refills never share a ray.
-//                  Only rays on reflected segments are taken, and only in the REFILL instantiation, which the
-//                  host picks per call: a ray walked alone pays for every box around its origin by itself, which
-//                  the shared start of a batch spreads over 32 rays. Measured: with two bounces on 6M
-//                  surfels the forward gets a third faster, with one bounce on 3M surfels 7 % slower.
+// A warp takes 32 consecutive entries of the live list: neighbouring pixels in the same stage (the lists keep their
+// tile order, see k_compact), whose rays start close to each other. Large overlapping quads put hundreds of boxes
+// around any origin, and every one of the 32 rays has to open them, so the walk is split in two:
+//   shared phase   the warp walks the hierarchy TOGETHER from the root with one stack; a node is fetched once (one
+//                  broadcast load instead of 32 scattered ones) and every lane tests its own ray against both
+//                  child boxes. A child wanted by at least DST_SHARE_VOTE lanes (1: any lane, measured best) stays
+//                  in the shared walk; a child wanted by fewer goes onto the private stacks of those lanes.
+//                  A leaf run reached here is NOT tested quad by quad by every lane: lane q fetches quad q and
+//                  decides, against the hull of the batch's rays (hull_quad), whether any ray of the batch can hit
+//                  it; only the survivors (a few of 32 for neighbouring rays) are handed round and tested exactly
+//                  by every lane. When most lanes sit out most tests (after 64 nodes, under DST_SHARE_MIN_PCT % of
+//                  the lane x test slots wanted) the warp gives the shared walk up: every lane takes the pending
+//                  subtrees onto its own stack.
+//   private phase  every lane drains its own stack as in knearest(), lanes alternating between a node phase (kept
+//                  while at least DST_NODE_VOTE lanes have node work) and a leaf phase.
+// Pruning uses each lane's own 16th-nearest distance throughout and the hull test is conservative, so the hit set is
+// exactly that of an independent walk per ray. Blocks are persistent and take batches from a shared cursor.
 #define DST_SHARED_STACK 64
 #define DST_ENUM_STACK 160       // private stack of k_enum: subtrees deferred by the shared walk + one depth-first descent
 #define DST_ENUM_DEFER 64        // the shared walk pauses to drain the private stacks when a lane holds this many entries
-#ifndef DST_STEAL_MIN_BUSY
-#define DST_STEAL_MIN_BUSY 26    // idle lanes take extra rays only while this many lanes of the warp are still walking
-#endif
+// Hull of the rays of one batch (origins and directions, component by component), kept in shared memory per warp.
+struct BeamQ { float omin[3], omax[3], dmin[3], dmax[3]; };
+
+__device__ __forceinline__ unsigned int f2ord_q(float f) {
+    const unsigned int u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float ord2f_q(unsigned int u) { return __uint_as_float((u & 0x80000000u) ? (u & 0x7fffffffu) : ~u); }
+__device__ __forceinline__ float wmin_f(float v) { return ord2f_q(__reduce_min_sync(0xffffffffu, f2ord_q(v))); }
+__device__ __forceinline__ float wmax_f(float v) { return ord2f_q(__reduce_max_sync(0xffffffffu, f2ord_q(v))); }
+
+__device__ __forceinline__ void ivmul(float c, float lo, float hi, float& rl, float& rh) {
+    const float a = c * lo, b = c * hi;
+    rl += fminf(a, b); rh += fmaxf(a, b);
+}
+// Conservative test of one quad against the hull of a batch of rays, in interval arithmetic over the hull's origins
+// and directions: can ANY ray of the batch pass ray_quad() with a hit no farther than kmaxb? The steps are those of
+// ray_quad(): t = n.(p0 - o) / n.d, h = t d - (p0 - o), u = wu.h, v = wv.h, accepted iff 0 <= t <= kmax and u, v in
+// [0, 1]. Every interval is widened by margins orders of magnitude above the rounding of either computation, so a
+// quad some ray hits is never rejected. For neighbouring rays (close origins, directions a degree apart) the
+// intervals are narrow: nearly every quad that no ray hits is rejected here by ONE lane, and the lanes of a warp
+// do that for 32 quads at a time, instead of every lane testing every quad against its own ray.
+__device__ __forceinline__ bool hull_quad(const BeamQ& bm, const float4 qa, const float4 qb, const float4 qc, float kmaxb) {
+    const float p0[3] = { qa.x, qa.y, qa.z }, nn[3] = { qa.w, qb.x, qb.y }, wu[3] = { qb.z, qb.w, qc.x }, wv[3] = { qc.y, qc.z, qc.w };
+    float rl[3], rh[3];
+    float bl = 0.f, bh = 0.f, al = 0.f, ah = 0.f, scale = 0.f, dsum = 0.f;
+#pragma unroll
+    for (int a = 0; a < 3; a++) {
+        rl[a] = p0[a] - bm.omax[a]; rh[a] = p0[a] - bm.omin[a];
+        ivmul(nn[a], bm.dmin[a], bm.dmax[a], bl, bh);
+        ivmul(nn[a], rl[a], rh[a], al, ah);
+        scale = fmaxf(scale, fmaxf(fabsf(rl[a]), fabsf(rh[a])));
+        dsum += fmaxf(fabsf(bm.dmin[a]), fabsf(bm.dmax[a]));
+    }
+    const float nmag = fabsf(nn[0]) + fabsf(nn[1]) + fabsf(nn[2]);
+    const float eb = 4e-6f * nmag * dsum, ea = 12e-6f * nmag * scale;
+    bl -= eb; bh += eb; al -= ea; ah += ea;
+    if (!(bl > 0.f || bh < 0.f)) return true;               // some direction of the hull is parallel to the plane: no bound
+    const float t1 = al / bl, t2 = al / bh, t3 = ah / bl, t4 = ah / bh;
+    float tl = fminf(fminf(t1, t2), fminf(t3, t4)), th = fmaxf(fmaxf(t1, t2), fmaxf(t3, t4));
+    tl -= 1e-5f * fabsf(tl) + 1e-30f; th += 1e-5f * fabsf(th) + 1e-30f;
+    if (th < 0.f || tl > kmaxb) return false;
+    tl = fmaxf(tl, 0.f); th = fminf(th, kmaxb);
+    float ul = 0.f, uh = 0.f, vl = 0.f, vh = 0.f, hmag = 0.f;
+#pragma unroll
+    for (int a = 0; a < 3; a++) {
+        const float c1 = tl * bm.dmin[a], c2 = tl * bm.dmax[a], c3 = th * bm.dmin[a], c4 = th * bm.dmax[a];
+        const float hl = fminf(fminf(c1, c2), fminf(c3, c4)) - rh[a], hh = fmaxf(fmaxf(c1, c2), fmaxf(c3, c4)) - rl[a];
+        ivmul(wu[a], hl, hh, ul, uh);
+        ivmul(wv[a], hl, hh, vl, vh);
+        hmag = fmaxf(hmag, fmaxf(fabsf(hl), fabsf(hh)) + scale + th * fmaxf(fabsf(bm.dmin[a]), fabsf(bm.dmax[a])));
+    }
+    // u and v are of order 1; their rounding error is that of h (cancellation of t d against p0 - o) times |w|
+    const float eu = 1e-5f + 8e-6f * hmag * (fabsf(wu[0]) + fabsf(wu[1]) + fabsf(wu[2]));
+    const float ev = 1e-5f + 8e-6f * hmag * (fabsf(wv[0]) + fabsf(wv[1]) + fabsf(wv[2]));
+    return !(uh < -eu || ul > 1.f + eu || vh < -ev || vl > 1.f + ev);
+}
+
 #ifdef DST_ROUND_STATS
 // build-time diagnostic: per wavefront round [0] batches, [1] shared node steps, [2] shared quad steps, [3] private
 // node-phase warp steps, [4] private leaf-phase warp steps (quads), [5] batches that gave the shared walk up,
@@ -351,16 +396,16 @@ static __device__ unsigned long long g_round_stats[64][8];
 #else
 #define RSTAT(i, v) do { } while (0)
 #endif
-template <bool COUNT, bool REFILL>
+template <bool COUNT>
 __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumReq* __restrict__ req, const int* __restrict__ list,
                                                        const int* __restrict__ count_ptr, int* cursor, int min_count,
                                                        unsigned long long* __restrict__ kbuf, int* __restrict__ kcnt,
-                                                       unsigned int* status, unsigned long long* counters,
-                                                       int* back_cursor, int* claim, int tag) {
+                                                       unsigned int* status, unsigned long long* counters, int tag) {
     __shared__ unsigned long long kshared[DST_CHUNK * ENUM_THREADS];
     __shared__ int sstack[ENUM_THREADS / 32][DST_SHARED_STACK];
+    __shared__ BeamQ sbeam[ENUM_THREADS / 32];
     const int total = *count_ptr;
-    if (total < min_count || bvh.nrefs <= 0) return;
+    if (total < min_count || bvh.P <= 0) return;
     constexpr int KS = ENUM_THREADS;
     constexpr int DONE = 0x7fffffff;
     constexpr unsigned int FULL = 0xffffffffu;
@@ -408,22 +453,22 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
         l0 = lk.z; l1 = lk.w;
     };
     // exact test of one quad and insertion into this lane's k-buffer
-    auto offer = [&](int pos) {
-        const float4* qp = bvh.quads + 3 * (size_t)pos;
-        const float4 qa = __ldg(qp), qb = __ldg(qp + 1), qc = __ldg(qp + 2);
+    auto offer_quad = [&](const float4 qa, const float4 qb, const float4 qc, unsigned int gid) {
         float t; int tri;
         if (!ray_quad(qa, qb, qc, ox, oy, oz, dx, dy, dz, kmax, t, tri)) return;
-        const unsigned int gid = (unsigned int)__ldg(bvh.leaf_gid + pos) >> DST_REF_SHIFT;
         const unsigned long long key = make_key(t, 2u * gid + (unsigned int)tri);
         if (n == DST_CHUNK && key >= kb[(DST_CHUNK - 1) * KS]) return;
         int j = n;
         while (j > 0 && kb[(j - 1) * KS] > key) j--;
-        if (j > 0 && kb[(j - 1) * KS] == key) return;
         if (n == DST_CHUNK) n = DST_CHUNK - 1;
         for (int i = n; i > j; i--) kb[i * KS] = kb[(i - 1) * KS];
         kb[j * KS] = key;
         n++;
         if (n == DST_CHUNK) kmax = hitkey_t(kb[(DST_CHUNK - 1) * KS]);
+    };
+    auto offer = [&](int pos) {
+        const float4* qp = bvh.quads + 3 * (size_t)pos;
+        offer_quad(__ldg(qp), __ldg(qp + 1), __ldg(qp + 2), (unsigned int)__ldg(bvh.leaf_gid + pos));
     };
 
     for (;;) {
@@ -433,7 +478,7 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
         base = __shfl_sync(FULL, base, 0);
         if (base >= total) break;
         const int idx = base + lane;
-        int ray = (idx < total && (!REFILL || atomicMax(claim + idx, tag) < tag)) ? list[idx] : -1;
+        int ray = idx < total ? list[idx] : -1;
         bool active = false;
         // takes up `ray`: request, slab constants, empty k-buffer and stack
         auto begin_ray = [&]() {
@@ -462,7 +507,16 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
         };
         begin_ray();
         RSTAT(0, 1); RSTAT(7, __popc(__ballot_sync(FULL, active)));
-        bool bailed = false, dry = false;      // warp gave up the shared walk / the back of the list is used up (per lane)
+        {   // hull of the batch's rays, for culling the quads of leaf runs the warp reaches together
+            const float o3[3] = { ox, oy, oz }, d3[3] = { dx, dy, dz };
+#pragma unroll
+            for (int a = 0; a < 3; a++) {
+                const float lo = wmin_f(active ? o3[a] : INFINITY), hi = wmax_f(active ? o3[a] : -INFINITY);
+                const float dl = wmin_f(active ? d3[a] : INFINITY), dh = wmax_f(active ? d3[a] : -INFINITY);
+                if (lane == 0) { sbeam[wid].omin[a] = lo; sbeam[wid].omax[a] = hi; sbeam[wid].dmin[a] = dl; sbeam[wid].dmax[a] = dh; }
+            }
+            __syncwarp();
+        }
         int ssp = 0, scur = __any_sync(FULL, active) ? 0 : DONE;     // shared walk: stack pointer and current link (uniform)
         int s_tests = 0, s_wanted = 0;                                // child tests made together / of them wanted by their lane
         for (;;) {
@@ -478,7 +532,6 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
                         for (int e = 0; e < ssp; e++) push(sstack[wid][e], 0.0f);
                     }
                     ssp = 0; scur = DONE;
-                    bailed = true;
                     RSTAT(5, 1);
                     break;
                 }
@@ -510,12 +563,39 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
                     }
                     if (next != DONE) { scur = next; continue; }
                 } else {
-                    // a run of leaves reached together: one broadcast fetch per quad, every lane tests its own ray
+                    // A run of leaves reached together. Lane q fetches quad q of the run and decides for the whole batch whether
+                    // any of its rays can hit it (hull_quad); the few quads that pass are handed round and tested exactly
+                    // by every lane against its own ray.
                     const int first = DST_LEAF_FIRST(scur), count = DST_LEAF_COUNT(scur);
-                    for (int lq = 0; lq < count; lq++) {
+                    if (count <= DST_HULL_MIN) {
+                        for (int lq = 0; lq < count; lq++) {
+                            if (COUNT && lane == 0) tc.quads++;
+                            RSTAT(2, 1);
+                            if (active) offer(first + lq);
+                        }
+                    } else {
+                    const bool mine = lane < count;
+                    float4 qa = make_float4(0.f, 0.f, 0.f, 0.f), qb = qa, qc = qa;
+                    unsigned int qgid = 0u;
+                    if (mine) {
+                        const float4* qp = bvh.quads + 3 * (size_t)(first + lane);
+                        qa = __ldg(qp); qb = __ldg(qp + 1); qc = __ldg(qp + 2);
+                        qgid = (unsigned int)__ldg(bvh.leaf_gid + first + lane);
+                    }
+                    const float krun = wmax_f(active ? kmax : -1.0f);
+                    unsigned int maybe = __ballot_sync(FULL, mine && hull_quad(sbeam[wid], qa, qb, qc, krun));
+                    RSTAT(4, count);
+                    while (maybe) {
+                        const int src = __ffs(maybe) - 1;
+                        maybe &= maybe - 1u;
+                        const float4 sa = make_float4(__shfl_sync(FULL, qa.x, src), __shfl_sync(FULL, qa.y, src), __shfl_sync(FULL, qa.z, src), __shfl_sync(FULL, qa.w, src));
+                        const float4 sb = make_float4(__shfl_sync(FULL, qb.x, src), __shfl_sync(FULL, qb.y, src), __shfl_sync(FULL, qb.z, src), __shfl_sync(FULL, qb.w, src));
+                        const float4 sc = make_float4(__shfl_sync(FULL, qc.x, src), __shfl_sync(FULL, qc.y, src), __shfl_sync(FULL, qc.z, src), __shfl_sync(FULL, qc.w, src));
+                        const unsigned int sg = __shfl_sync(FULL, qgid, src);
                         if (COUNT && lane == 0) tc.quads++;
                         RSTAT(2, 1);
-                        if (active) offer(first + lq);
+                        if (active) offer_quad(sa, sb, sc, sg);
+                    }
                     }
                 }
                 if (ssp == 0) { scur = DONE; break; }
@@ -529,19 +609,6 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
         for (;;) {
             const unsigned int busy = __ballot_sync(FULL, cur != DONE);
             if (busy == 0u) break;
-            if (REFILL && bailed && scur == DONE && __popc(busy) >= DST_STEAL_MIN_BUSY && cur == DONE && !dry) {
-                // this lane is done while most of the warp still walks: publish and take a ray from the back of the list
-                publish();
-                const int pos = total - 1 - atomicAdd(back_cursor, 1);
-                // only rays on a reflected segment are taken: primary rays of neighbouring pixels are far cheaper walked together
-                const int cand = pos >= 0 ? list[pos] : -1;
-                const bool take = pos >= 0 && (cand < 0 || __ldg(&req[cand].pad) != 0.0f);
-                if (take && atomicMax(claim + pos, tag) < tag) {
-                    ray = cand;
-                    begin_ray();
-                    if (active) cur = 0;        // walk of its own from the root
-                } else dry = true;              // a primary ray, or the front batches have reached this position
-            }
             // node phase: kept while at least DST_NODE_VOTE lanes have node work or nobody holds a leaf
             for (;;) {
                 const bool is_node = (unsigned int)cur < (unsigned int)DONE;
@@ -562,11 +629,6 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
                 else cur = pop();
             }
             // leaf phase
-#ifdef DST_ROUND_STATS
-            { int mx = cur < 0 ? DST_LEAF_COUNT(cur) : 0;
-              for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(FULL, mx, o));
-              RSTAT(4, mx); }
-#endif
             if (cur < 0) {
                 const int first = DST_LEAF_FIRST(cur), count = DST_LEAF_COUNT(cur);
                 for (int lq = 0; lq < count; lq++) { if (COUNT) tc.quads++; offer(first + lq); }
@@ -582,6 +644,14 @@ __global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumRe
 #ifdef DST_ROUND_STATS
     if (lane == 0) for (int k = 0; k < 8; k++) if (rs[k]) atomicAdd(&g_round_stats[tag & 63][k], rs[k]);
 #endif
+}
+
+// one gather launch of a wavefront round (diag: with traversal counters)
+static inline void launch_gather(bool diag, int grid, cudaStream_t st, const BvhView& bvh, const EnumReq* req, const int* list,
+                                 const int* count_ptr, int* cursor, int min_count, unsigned long long* kbuf, int* kcnt, unsigned int* status,
+                                 unsigned long long* counters, int tag) {
+    if (diag) k_enum<true><<<grid, ENUM_THREADS, 0, st>>>(bvh, req, list, count_ptr, cursor, min_count, kbuf, kcnt, status, counters, tag);
+    else k_enum<false><<<grid, ENUM_THREADS, 0, st>>>(bvh, req, list, count_ptr, cursor, min_count, kbuf, kcnt, status, nullptr, tag);
 }
 
 // The 16 nearest hits of ONE ray, found by a whole warp (same result as knearest()). For the few rays the
@@ -603,14 +673,13 @@ __device__ __forceinline__ int knearest_warp(const BvhView& bvh, float ox, float
     mykey = EMPTY;
     int n = 0;
     float kmax = kmax0;
-    if (bvh.nrefs <= 0) return 0;
+    if (bvh.P <= 0) return 0;
     const RaySlab sl = make_slab(ox, oy, oz, dx, dy, dz, __ldg(bvh.header + 6));
     if (!sl.valid) return 0;
     // inserts a hit (uniform key) into the sorted keys held by lanes 0..15
     auto insert = [&](unsigned long long key) {
         const unsigned long long last = __shfl_sync(FULL, mykey, DST_CHUNK - 1);
         if (key >= last) return;                                            // not among the 16 nearest (or the buffer is full of nearer ones)
-        if (__any_sync(FULL, lane < DST_CHUNK && mykey == key)) return;
         const int pos = __popc(__ballot_sync(FULL, lane < DST_CHUNK && mykey < key));
         const unsigned long long up = __shfl_up_sync(FULL, mykey, 1);
         if (lane < DST_CHUNK) mykey = lane < pos ? mykey : (lane == pos ? key : up);
@@ -652,7 +721,7 @@ __device__ __forceinline__ int knearest_warp(const BvhView& bvh, float ox, float
                     const float4 qa = __ldg(qp), qb = __ldg(qp + 1), qc = __ldg(qp + 2);
                     float t; int tri;
                     if (ray_quad(qa, qb, qc, ox, oy, oz, dx, dy, dz, kmax, t, tri)) {
-                        const unsigned int gid = (unsigned int)__ldg(bvh.leaf_gid + pos) >> DST_REF_SHIFT;
+                        const unsigned int gid = (unsigned int)__ldg(bvh.leaf_gid + pos);
                         key = make_key(t, 2u * gid + (unsigned int)tri);
                         hit = true;
                     }

@@ -82,6 +82,8 @@ def lib():
         l.dst_profile_read.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_int32)]
         l.dst_profile_launches.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_float), C.c_int32, C.POINTER(C.c_int32)]
         l.dst_debug_round_counts.argtypes = [C.c_void_p, C.POINTER(C.c_int32), C.c_int32, C.c_void_p]
+        l.dst_debug_read_bandwidth.argtypes = [C.c_void_p, C.c_int64, C.c_int, C.POINTER(C.c_float), C.c_void_p]
+        l.dst_debug_chunk_log.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
         l.dst_debug_quad_frames.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         _lib = l
     return _lib
@@ -141,6 +143,8 @@ class OptiXStateWrapper:
         self._keep = None
         self.last_forward_serial = 0
         self._logged_mid = None
+        self.reduce_gradients = False   # sum the per-surfel gradients over `process_group` inside every backward call
+        self.process_group = None
         self.grad_bucket = None     # flat buffer holding the per-surfel gradients of the last backward call
 
     def __del__(self):
@@ -169,10 +173,6 @@ class OptiXStateWrapper:
     def set_image_width(self, width):
         """Hint for (B, h*w, 3) ray batches of whole images: the image width (0: unknown). Scheduling only."""
         _check(self, lib().dst_set_option(self.handle, 6, int(width)))
-
-    def set_gather_refill(self, mode):
-        """Gather kernel scheduling: 1 idle lanes take extra reflected-segment rays, 0 never, -1 automatic (default)."""
-        _check(self, lib().dst_set_option(self.handle, 5, int(mode)))
 
     def set_single_kernel_refit(self, on):
         """build_from_surfels(rebuild=0): expand the quads inside the refit kernel (one launch) instead of before it."""
@@ -222,6 +222,18 @@ class OptiXStateWrapper:
         while out and out[-1] == 0:
             out.pop()
         return out
+
+    def read_bandwidth(self, nbytes=64 << 20, reps=50):
+        """GB/s of repeated streaming reads of an `nbytes` buffer (64 MB fits the L2 cache: the L2 read bandwidth)."""
+        v = C.c_float(0)
+        _check(self, lib().dst_debug_read_bandwidth(self.handle, int(nbytes), int(reps), C.byref(v), _stream(self)))
+        return v.value
+
+    def chunk_log(self):
+        """dict(records_wanted, records_held, bytes_per_record) of the chunk log (records_wanted -1: not known yet)."""
+        a, b, c = C.c_int64(), C.c_int64(), C.c_int64()
+        _check(self, lib().dst_debug_chunk_log(self.handle, C.byref(a), C.byref(b), C.byref(c)))
+        return dict(records_wanted=a.value, records_held=b.value, bytes_per_record=c.value)
 
     def info(self):
         a, b, c = C.c_int64(), C.c_int64(), C.c_int64()
@@ -379,16 +391,27 @@ def trace_surfels_backward(state, start_from_first, ray_o, ray_d, vertices, back
           up(dL_dnorm, (H, W, 3), "dL_dnorm"), up(dL_ddist, (H, W, 1), "dL_ddist"), up(dL_daux, (H, W, 2), "dL_daux")]
     g_ray_o = torch.empty((H, W, 3), **f32)
     g_ray_d = torch.empty((H, W, 3), **f32)
-    # all per-surfel gradients live in ONE flat buffer (16-byte aligned views), so that a multi-GPU
-    # caller sums them with a single all-reduce (shard.allreduce_surfel_gradients)
-    sizes = [("rot", P * 4), ("means", P * 3), ("g3d", P * 3), ("shs", P * M * 3), ("colors", P * NUM_CHANNELS),
-             ("others", P * AUX_CHANNELS), ("opac", P), ("scales", P * 2)]
-    offs, total = {}, 0
-    for name, n in sizes:
-        offs[name] = total
-        total += (n + 3) // 4 * 4
+    # The per-surfel gradients a caller can use live in ONE flat buffer (16-byte aligned views), so that a multi-GPU
+    # run sums them with a single all-reduce. Gradients nobody receives (of the colour or auxiliary tensor that was
+    # not given) are computed as the reference computes them, but kept out of that buffer.
+    has_colors, has_others = keep["colors_precomp"].numel() != 0, keep["others_precomp"].numel() != 0
+    sizes = [("rot", P * 4, True), ("means", P * 3, True), ("g3d", P * 3, True), ("shs", P * M * 3, True),
+             ("colors", P * NUM_CHANNELS, has_colors), ("others", P * AUX_CHANNELS, has_others), ("opac", P, True), ("scales", P * 2, True)]
+    offs, total, side_total = {}, 0, 0
+    for name, n, shared in sizes:
+        if shared:
+            offs[name] = (True, total)
+            total += (n + 3) // 4 * 4
+        else:
+            offs[name] = (False, side_total)
+            side_total += (n + 3) // 4 * 4
     bucket = torch.empty((total,), **f32)
-    view = lambda name, n, shape: bucket[offs[name]:offs[name] + n].view(shape)
+    side = torch.empty((side_total,), **f32)
+
+    def view(name, n, shape):
+        shared, off = offs[name]
+        return (bucket if shared else side)[off:off + n].view(shape)
+
     g_rot = view("rot", P * 4, (P, 4))
     g_means = view("means", P * 3, (P, 3))
     g_g3d = view("g3d", P * 3, (P, 3))
@@ -413,6 +436,13 @@ def trace_surfels_backward(state, start_from_first, ray_o, ray_d, vertices, back
         _diag["counters"] = torch.zeros((8,), dtype=torch.int64, device=dev)
         a.counters = _diag["counters"].data_ptr()
     _check(state, lib().dst_backward(state.handle, C.byref(a), _stream(state)))
+    if getattr(state, "reduce_gradients", False):
+        # multi-GPU: rays are sharded, surfels replicated; the sum over the ranks happens here, before autograd hands
+        # the views on, so that leaf gradients behind any chain of activations are the global ones
+        import torch.distributed as dist
+        torch.cuda.nvtx.range_push("dst_gradient_allreduce")
+        dist.all_reduce(bucket, op=dist.ReduceOp.SUM, group=state.process_group)
+        torch.cuda.nvtx.range_pop()
     return g_ray_o, g_ray_d, g_means, g_g3d, g_g3d_abs, g_shs, g_colors, g_others, g_opac, g_scales, g_rot, g_trans
 
 

@@ -121,6 +121,13 @@ class SurfelTracer(nn.Module):
     def build_acceleration_structure(self, vertices: torch.Tensor, triangles: torch.Tensor, rebuild: bool = 1):
         return _C.build_acceleration_structure(self.optix_context, vertices, triangles, rebuild)
 
+    def set_gradient_group(self, enabled: bool = True, group=None):
+        """Multi-GPU training with sharded rays and replicated surfels (the reference is single-GPU): when enabled,
+        every backward call sums the per-surfel gradients over the ranks of `group` (None: the default process
+        group) with one all-reduce of one flat buffer before autograd receives them. Ray gradients stay local."""
+        self.optix_context.reduce_gradients = bool(enabled)
+        self.optix_context.process_group = group
+
     def forward(self, ray_o: torch.Tensor, ray_d: torch.Tensor, vertices: torch.Tensor, means3D: torch.Tensor,
                 grads3D: torch.Tensor, shs: torch.Tensor = None, colors_precomp: torch.Tensor = None,
                 others_precomp: torch.Tensor = None, opacities: torch.Tensor = None, scales: torch.Tensor = None,

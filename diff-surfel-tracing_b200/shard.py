@@ -28,13 +28,22 @@ def shard_rays(ray_o: torch.Tensor, ray_d: torch.Tensor, world: int, rank: int):
 def allreduce_bucket(bucket: torch.Tensor, group=None):
     """In-place sum of a flat gradient buffer over the ranks of `group` (no-op without a process group)."""
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        if bucket.is_cuda:
+            torch.cuda.nvtx.range_push("dst_gradient_allreduce")
         dist.all_reduce(bucket, op=dist.ReduceOp.SUM, group=group)
+        if bucket.is_cuda:
+            torch.cuda.nvtx.range_pop()
     return bucket
 
 
 def allreduce_surfel_gradients(state, group=None):
     """Sums the per-surfel gradients of the last backward call of `state` (the tracer's state object)
-    over all ranks, in place and on the current stream: one collective over one flat buffer."""
+    over all ranks, in place and on the current stream: one collective over one flat buffer.
+
+    For callers of the extension-level functions (`_C.trace_surfels_backward`), whose returned tensors are
+    views of that buffer. Training code that goes through `SurfelTracer` and autograd should use
+    `SurfelTracer.set_gradient_group()` instead: by the time `loss.backward()` returns, autograd has already
+    consumed the views, and leaf gradients behind activations would stay rank-local."""
     if state.grad_bucket is None:
         raise RuntimeError("no backward call has been made on this tracer state")
     return allreduce_bucket(state.grad_bucket, group)

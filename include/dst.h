@@ -221,10 +221,6 @@ int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t*
  * warp holds neighbouring pixels. 0 (default): unknown, batched rays are walked in the order given. Results are
  * not affected. */
 #define DST_OPT_IMAGE_WIDTH 6
-/* Gather kernel scheduling (results are not affected): 1 lets lanes whose ray is finished take further
- * rays on reflected segments while the rest of their warp is still walking, 0 never does, -1
- * (default) does it for calls with max_trace_depth >= 2, where it was measured to pay. */
-#define DST_OPT_GATHER_REFILL 5
 /* dst_build_from_surfels with rebuild == 0: non-zero expands the quads inside the refit kernel (one
  * launch, no re-read of the vertices); zero (default) runs the expansion kernel and then the refit,
  * which is faster on large scenes because the expansion's writes are coalesced. Same results. */
@@ -260,6 +256,14 @@ int dst_debug_knearest(dst_handle* h, const float* ray_o, const float* ray_d, in
 /* Diagnostics: synchronises `stream` and copies the live-list length of every wavefront round of the last trace
  * call (host array of `cap` ints; round r of the call saw counts[r] rays, 0 from the first unused round on). */
 int dst_debug_round_counts(dst_handle* h, int32_t* counts, int32_t cap, void* stream);
+/* Diagnostics: bandwidth of repeated streaming reads (16-byte loads that bypass L1) of a zeroed scratch buffer of
+ * `bytes` bytes, `reps` passes, timed with CUDA events on `stream` after a warming pass; allocates and frees
+ * the buffer. With a buffer that fits the L2 cache this is the L2 read bandwidth quoted beside the HBM figure. */
+int dst_debug_read_bandwidth(dst_handle* h, int64_t bytes, int reps, float* gb_per_s, void* stream);
+/* Diagnostics: the chunk log of the last training forward whose read-back has completed: records it wanted
+ * (-1: not known yet), records the log can hold, bytes per record. Rays whose records did not fit are re-traced
+ * by the backward. */
+int dst_debug_chunk_log(const dst_handle* h, int64_t* records_wanted, int64_t* records_held, int64_t* bytes_per_record);
 /* Diagnostics: copies the per-quad plane frames (12 floats each, surfel order) to `out`. */
 int dst_debug_quad_frames(dst_handle* h, float* out, void* stream);
 

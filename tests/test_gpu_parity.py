@@ -197,18 +197,24 @@ def test_full_chunk_log_falls_back_to_retrace(C, oracle_mod):
 
 
 @pytest.mark.parametrize("config", [3, 5])
-def test_gather_refill_does_not_change_results(C, config):
-    """Scheduling option of the gather kernel (idle lanes take extra reflected-segment rays): same bits either way."""
+def test_list_order_does_not_change_results(C, config):
+    """Scheduling option of the wavefront rounds (live lists kept in tile order, or appended warp by warp): same bits."""
     wc = hp.to_cuda(hp.reduced_workload(config))
     outs = []
     for mode in (0, 1):
         st = _build(C, wc, wave=True)
-        st.set_gather_refill(mode)
-        outs.append(hp.cuda_forward(C, st, wc))
+        st.set_stable_lists(mode)
+        f = hp.cuda_forward(C, st, wc)
+        g = hp.cuda_backward(C, st, wc, f, dict(rgb=torch.ones_like(f["rgb"])), serial=0)       # re-tracing backward: its rounds use the lists too
         torch.cuda.synchronize()
         assert st.status() == 0
+        outs.append((f, g))
     for k in ("rgb", "dpt", "acc", "norm", "aux", "mid"):
-        assert torch.equal(outs[0][k], outs[1][k]), k
+        assert torch.equal(outs[0][0][k], outs[1][0][k]), k
+    for k in ("ray_o", "ray_d"):
+        assert torch.equal(outs[0][1][k], outs[1][1][k]), k
+    for k in ("means3D", "shs", "opacities", "scales", "rotations"):
+        assert hp.rel_l2(outs[0][1][k].cpu().numpy(), outs[1][1][k].cpu().numpy()) < 1e-4, k
 
 
 def test_image_width_hint_does_not_change_results(C):
@@ -343,3 +349,33 @@ def test_module_api_and_autograd(C):
                  scales=wc["scales"], rotations=wc["rotations"], tracer_settings=settings)
     assert out[7].shape == (10000,) and float(out[7].abs().max()) == 0.0
     assert torch.equal(out[0], rgb.detach())
+
+
+def test_ray_scratch_grows_once_per_larger_call(C):
+    """The handle's per-ray scratch is grow-only: a call larger than any before replaces it once (keeping the larger
+    of the old and new record size), repeated and smaller calls allocate nothing."""
+    w = hp.workloads.make_workload(1, P=3000, H=96, W=96)
+    wc = hp.to_cuda(w)
+    st = _build(C, wc)
+    st.set_chunk_log(False)               # the chunk log sizes itself from the previous call; this test watches the ray scratch
+
+    def sub(n):
+        return dict(wc, ray_o=wc["ray_o"][:n, :n].contiguous(), ray_d=wc["ray_d"][:n, :n].contiguous())
+
+    def pair(n):
+        s = sub(n)
+        f = hp.cuda_forward(C, st, s)
+        b_f = st.info()["device_bytes"]
+        hp.cuda_backward(C, st, s, f, dict(rgb=torch.ones((n, n, 3), device="cuda")))
+        return b_f, st.info()["device_bytes"]
+
+    pair(32)                              # first use: the forward sizes the records, the backward enlarges them
+    base = st.info()["device_bytes"]
+    assert pair(32) == (base, base) and pair(16) == (base, base)
+    f64, b64 = pair(64)
+    assert f64 > base and b64 == f64      # one growth, at the forward; the backward finds its record size already there
+    assert pair(64) == (f64, f64) and pair(32) == (f64, f64)
+    f96, b96 = pair(96)
+    assert f96 > f64 and b96 == f96
+    torch.cuda.synchronize()
+    assert st.status() == 0

@@ -29,8 +29,9 @@ def _call_static(C, st, wc):
 def test_static_forward_matches_regular_forward_twice():
     from diff_surfel_tracing import _C as C
     assert torch.cuda.is_available()
-    # two different workloads back to back: the shared scratch keeps the first call's contents during the second
-    for config, kw in ((3, dict(P=30_000, H=48, W=64)), (1, dict(P=10_000, H=128, W=128))):
+    # different workloads back to back: the shared scratch keeps the previous call's contents during the next. The
+    # third has 51,200 rays: above 32,768 the entry point runs one thread per ray instead of one warp per ray.
+    for config, kw in ((3, dict(P=30_000, H=48, W=64)), (1, dict(P=10_000, H=128, W=128)), (1, dict(P=20_000, H=200, W=256))):
         w = hp.workloads.make_workload(config, **kw)
         wc = hp.to_cuda(w)
         st = C.OptiXStateWrapper("")
@@ -45,6 +46,43 @@ def test_static_forward_matches_regular_forward_twice():
             tol = 1e-4 * max(1.0, float(want["wet"].abs().max()))
             assert float((got[7] - want["wet"]).abs().max()) <= tol
         assert float(want["acc"].max()) > 0.5
+
+
+def test_static_forward_on_a_narrow_grid_and_backward_after_it(oracle_mod):
+    """A tall one-column grid (its 8x4 pixel tiling would not fit the fixed ray list, so the rays are walked in the
+    order given) equals the regular forward; and a backward of the static call's outputs re-traces: it must not
+    re-composite the chunk log an earlier regular forward left in the handle (the static call keeps none)."""
+    from diff_surfel_tracing import _C as C
+    w = hp.workloads.make_workload(1, P=4_000, H=64, W=64)
+    wc = hp.to_cuda(w)
+    st = C.OptiXStateWrapper("")
+    C.build_acceleration_structure(st, wc["v"], wc["f"], 1)
+    tall = dict(wc, ray_o=wc["ray_o"].reshape(4096, 1, 3).repeat(8, 1, 1).contiguous(), ray_d=wc["ray_d"].reshape(4096, 1, 3).repeat(8, 1, 1).contiguous())
+    want = hp.cuda_forward(C, st, tall, training=True)
+    got = _call_static(C, st, tall)
+    torch.cuda.synchronize()
+    assert st.status() == 0
+    for name, g in zip(hp.FWD_KEYS[:7], got[:7]):
+        assert torch.equal(g, want[name]), name
+    # regular training forward on inputs A (leaves a chunk log), static forward on inputs B, then the backward of B
+    wa = wc
+    wb = dict(wc, ray_o=wc["ray_o"].flip(1).contiguous(), ray_d=wc["ray_d"].flip(1).contiguous())
+    hp.cuda_forward(C, st, wa, training=True)
+    assert st.last_forward_serial != 0
+    fb = dict(zip(hp.FWD_KEYS, _call_static(C, st, wb)))
+    assert st.last_forward_serial == 0
+    up = {"rgb": torch.ones((64, 64, 3), device="cuda")}
+    gb = hp.cuda_backward(C, st, wb, fb, up, serial=st.last_forward_serial)
+    torch.cuda.synchronize()
+    assert st.status() == 0
+    import numpy as np
+    wbh = dict(w, ray_o=w["ray_o"].flip(1).contiguous(), ray_d=w["ray_d"].flip(1).contiguous())
+    o = oracle_mod.Oracle(oracle_mod.Scene(w["v"]), impl="restatement", portable_exp=True)
+    fo = o.forward(wbh, training=True)
+    assert np.array_equal(fb["rgb"].cpu().numpy().view(np.uint32), fo["rgb"].view(np.uint32))
+    bo = o.backward(wbh, fo, dict(rgb=np.ones_like(fo["rgb"])))
+    for k in ("means3D", "opacities", "scales", "rotations", "shs", "ray_o"):
+        assert hp.rel_l2(gb[k].cpu().numpy().reshape(bo[k].shape), bo[k]) <= 1e-3, k
 
 
 def test_static_forward_rejects_oversized_calls():
