@@ -141,7 +141,7 @@ def ring_camera(index, count=8, radius=4.0):
 def config_block(w, P, rays_per_gpu, world, scale_out=False):
     return {"workload": w["name"], "surfels": P, "rays_per_gpu": rays_per_gpu, "sh_degree": w["sh_degree"],
             "max_trace_depth": w["max_trace_depth"], "specular_threshold": w["specular_threshold"],
-            "parallelism": (f"8 cameras split over {world} GPUs, hierarchy replicated and rebuilt every step, 1 all-reduce/step" if scale_out
+            "parallelism": (f"rows of 8 cameras dealt over {world} GPUs, hierarchy replicated and rebuilt every step, 1 all-reduce/step" if scale_out
                             else f"one camera of a ring of 8 per GPU x{world}, hierarchy replicated, 1 all-reduce/step" if world > 1 else "1 GPU"),
             "l2": "inputs larger than L2 (hierarchy + surfel records + SH rows > 126 MB), no flush"}
 
@@ -331,8 +331,9 @@ def scale_out_record(dev, rank, world, steps=3, warmup=1):
     w = workloads.make_workload(5)
     total_rays = w["ray_o"].shape[0] * w["ray_o"].shape[1]
     if world > 1:
-        ro, rd = shard.shard_rays(w["ray_o"], w["ray_d"], world, rank)
-        w = dict(w, ray_o=ro.contiguous(), ray_d=rd.contiguous())
+        # every rank takes 4-row blocks of every camera round-robin: equal shares of every camera and every part of the frame
+        ro, rd = shard.shard_image_rows(w["ray_o"], w["ray_d"], world, rank, 1080, 1920)
+        w = dict(w, ray_o=ro, ray_d=rd)
     wc = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in w.items()}
     tracer = SurfelTracer().to(dev)
     st = tracer.optix_context
@@ -360,7 +361,8 @@ def scale_out_record(dev, rank, world, steps=3, warmup=1):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     log_info = st.chunk_log()
-    rec = {"workload": w["name"], "surfels": w["means3D"].shape[0], "total_rays": total_rays, "cameras_per_gpu": w["ray_o"].shape[0],
+    rec = {"workload": w["name"], "surfels": w["means3D"].shape[0], "total_rays": total_rays, "rays_per_gpu": w["ray_o"].shape[0] * w["ray_o"].shape[1],
+           "split": "4-row blocks of every camera dealt round-robin over the ranks" if world > 1 else "none",
            "steps": steps, "warmup": warmup, "scaling": "strong", "value": total_rays / (ms * 1e-3) / 1e6, "unit": "Mrays/s", "ms_per_step": ms,
            "build_ms": rank_spread(pr["build"][0] / max(pr["build"][1], 1), world, dev),
            "forward_ms": rank_spread(pr["forward"][0] / max(pr["forward"][1], 1), world, dev),
@@ -414,8 +416,8 @@ def main():
     total_rays = w["ray_o"].shape[0] * w["ray_o"].shape[1]
     if scale_out and world > 1:
         import shard
-        ro, rd = shard.shard_rays(w["ray_o"], w["ray_d"], world, rank)
-        w = dict(w, ray_o=ro.contiguous(), ray_d=rd.contiguous())
+        ro, rd = shard.shard_image_rows(w["ray_o"], w["ray_d"], world, rank, 1080, 1920)
+        w = dict(w, ray_o=ro, ray_d=rd)
     elif args.config == 3 and world > 1 and rank > 0:
         ro, rd = workloads.pinhole_rays(w["ray_o"].shape[0], w["ray_o"].shape[1], 50.0, ring_camera(rank))
         w = dict(w, ray_o=ro, ray_d=rd)

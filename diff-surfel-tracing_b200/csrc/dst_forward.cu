@@ -6,8 +6,9 @@
 // flattened into a state machine: a ray's state is {segment, running sums, depth bookkeeping}, and
 // one step is "gather the 16 nearest hits from the moved origin" followed by "composite them and
 // decide": continue the segment, start the reflected segment, or finish. Large launches run the
-// steps as a wavefront (k_enum / k_fwd_shade rounds over the list of live rays, state in scratch
-// memory); the stragglers and small launches run in k_fwd_tail, one thread per ray to completion.
+// steps as a wavefront (k_enum / k_fwd_shade / k_compact rounds over the list of live rays, state in
+// scratch memory); the stragglers and small launches run in k_fwd_tail_warp, one warp per ray to
+// completion (k_fwd_tail, one thread per ray, above 32,768 rays).
 #include "dst_trace.cuh"
 #ifndef DST_ENUM_GRID_PER_SM
 #define DST_ENUM_GRID_PER_SM 12       // blocks per SM of the forward gather and composite kernels (persistent: more blocks than fit just start later)

@@ -25,6 +25,23 @@ def shard_rays(ray_o: torch.Tensor, ray_d: torch.Tensor, world: int, rank: int):
     return ray_o[a:b], ray_d[a:b]
 
 
+def shard_image_rows(ray_o: torch.Tensor, ray_d: torch.Tensor, world: int, rank: int, image_h: int, image_w: int, block: int = 4):
+    """This rank's share of a (B, image_h * image_w, 3) batch of whole images: blocks of `block` image rows dealt
+    out round-robin (rank r takes blocks r, r + world, ...) from every image, so that every rank samples every
+    camera and every part of the frame (the cost of a ray depends on both). Returns contiguous (B, rows * image_w, 3)
+    tensors whose rows keep their order; 4-row blocks stay whole, which is the height of the pixel tiles the
+    kernels walk (pass the image width to the tracer as usual)."""
+    if ray_o.dim() != 3 or ray_o.shape[1] != image_h * image_w:
+        raise ValueError("expected (B, image_h * image_w, 3) ray tensors")
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError("bad rank / world size")
+    n_blocks = (image_h + block - 1) // block
+    rows = torch.cat([torch.arange(b * block, min((b + 1) * block, image_h)) for b in range(rank, n_blocks, world)]).to(ray_o.device)
+    B = ray_o.shape[0]
+    pick = lambda t: t.reshape(B, image_h, image_w, 3).index_select(1, rows).reshape(B, -1, 3).contiguous()
+    return pick(ray_o), pick(ray_d)
+
+
 def allreduce_bucket(bucket: torch.Tensor, group=None):
     """In-place sum of a flat gradient buffer over the ranks of `group` (no-op without a process group)."""
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:

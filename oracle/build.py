@@ -5,15 +5,15 @@
   _ref/libref_{fwd,bwd}{1,2}.so   the reference's own shader sources compiled for the host
                           (ref_driver.cpp), only where the reference tree is present
 
-Run as `python oracle/build.py`. The reference tree is taken from $DST_REFERENCE_DIR or the
-default location used when this repository was developed; it is read in place, never copied.
+Run as `python oracle/build.py`. The reference tree is taken from $DST_REFERENCE_DIR, else from a
+directory `reference` next to this repository; it is read in place, never copied.
 """
 import os
 import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("DST_REFERENCE_DIR", "/root/reference")
+REF = os.environ.get("DST_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 CUDA_INC = os.environ.get("CUDA_HOME", "/usr/local/cuda") + "/include"
 COMMON = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-fopenmp", "-ffp-contract=off", "-mfma", "-fno-fast-math"]
 

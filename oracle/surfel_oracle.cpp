@@ -15,7 +15,7 @@
 //
 // Pinning: the reference ships no tests, golden vectors or fixtures for this path. This file is
 // pinned against the reference's own shader sources compiled for the host (ref_driver.cpp ->
-// oracle/_ref/*.so, same enumerator) by tests/test_oracle_pin.py, and against vectors generated
+// oracle/_ref/*.so, same enumerator) by tests/test_cpu_host.py, and against vectors generated
 // from that build and committed under tests/golden/. The enumeration step itself stays unpinned.
 //
 // Semantics are the "clean" ones: every enumeration starts from an empty 16-slot buffer. The

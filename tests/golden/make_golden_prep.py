@@ -17,7 +17,7 @@ import types
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("DST_REFERENCE_DIR", "/root/reference")
+REF = os.environ.get("DST_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference")
 
 P_GOLDEN = 517
 CAMERAS = 3

@@ -265,6 +265,19 @@ def test_split_rows_covers_everything():
             assert max(sizes) - min(sizes) <= 1
     with pytest.raises(ValueError):
         shard.split_rows(10, 2, 2)
+    # image batches: 4-row blocks of every image dealt round-robin; all ranks together hold every ray exactly once
+    B, h, w = 3, 26, 7
+    o = torch.arange(B * h * w * 3, dtype=torch.float32).reshape(B, h * w, 3)
+    for world in (1, 2, 3, 8):
+        parts = [shard.shard_image_rows(o, -o, world, r, h, w) for r in range(world)]
+        got = torch.cat([p[0].reshape(B, -1) for p in parts], dim=1)
+        assert torch.equal(got.sort(dim=1).values, o.reshape(B, -1).sort(dim=1).values)
+        for po, pd in parts:
+            assert torch.equal(pd, -po) and po.is_contiguous() and po.shape[1] % w == 0
+        sizes = [p[0].shape[1] // w for p in parts]
+        assert max(sizes) - min(sizes) <= 4
+    first = shard.shard_image_rows(o, o, 2, 1, h, w)[0].reshape(B, -1, w, 3)
+    assert torch.equal(first[:, :4], o.reshape(B, h, w, 3)[:, 4:8])          # rank 1 starts with image rows 4..7
 
 
 _WORKER = r'''
