@@ -223,6 +223,7 @@ int dst_set_option(dst_handle* h, int option, int64_t value) {
         case DST_OPT_CHUNK_LOG_MAX_RECORDS: h->log_max_records = value < 0 ? 0 : value; h->log_serial = 0; return DST_OK;
         case DST_OPT_IMAGE_WIDTH: h->image_width = value < 0 ? 0 : value; h->log_serial = 0; return DST_OK;
         case DST_OPT_SINGLE_KERNEL_REFIT: h->single_kernel_refit = value != 0; return DST_OK;
+        case DST_OPT_DISTORTION: h->distortion = value != 0; return DST_OK;
         case DST_OPT_STABLE_LISTS: h->stable_lists = value != 0; return DST_OK;
         case DST_OPT_CHUNK_LOG: h->log_enabled = value != 0; if (!h->log_enabled) h->log_serial = 0; return DST_OK;
         default: return dst_set_error(h, DST_E_ARG, "unknown option %d", option);

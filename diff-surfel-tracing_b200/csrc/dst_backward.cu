@@ -27,6 +27,7 @@ struct BwdParams {
     float* arena;
     unsigned int* status;
     int tiled, grid_h, grid_w;      // ray order, as in the forward
+    int dist_on;                    // depth-distortion extension
     // wavefront scratch
     void* state;
     EnumReq* req;
@@ -55,7 +56,8 @@ struct __align__(16) BwdState {
     float dir_g1, dir_g2, dro_x, dro_y;
     float dro_z, drd_x, drd_y, drd_z;
     int last_gidx, contributor, chunk, seg;
-    int dir_gidx, pad0, pad1, pad2;
+    int dir_gidx;
+    float dm0, dvs, dws;        // distortion term on the primary segment: mapped depth of the first contribution, running sums of w c^2 and w
 };
 static_assert(sizeof(BwdState) == 208, "ray state is thirteen 16-byte words");
 
@@ -189,6 +191,7 @@ __device__ __forceinline__ bool bwd_next_segment(const BwdParams& p, int ray, Bw
         s.offset = 0.f; s.dpt = 0.f; s.T_prev = 1.f;
         s.C0 = s.C1 = s.C2 = 0.f; s.D = 0.f; s.Nx = s.Ny = s.Nz = 0.f; s.O0 = s.O1 = 0.f;
         s.last_gidx = -1; s.contributor = 0; s.chunk = 0; s.seg = i; s.dir_gidx = -1;
+        s.dm0 = s.dvs = s.dws = 0.f;
         return true;
     }
     p.a.dL_dray_o[3 * (size_t)ray] = s.dro_x; p.a.dL_dray_o[3 * (size_t)ray + 1] = s.dro_y; p.a.dL_dray_o[3 * (size_t)ray + 2] = s.dro_z;
@@ -211,7 +214,7 @@ __device__ __forceinline__ bool bwd_init_state(const BwdParams& p, int ray, BwdS
         s.s_prod *= m2.w;
     }
     s.dro_x = s.dro_y = s.dro_z = 0.f; s.drd_x = s.drd_y = s.drd_z = 0.f;
-    s.dir_g0 = s.dir_g1 = s.dir_g2 = 0.f; s.pad0 = s.pad1 = s.pad2 = 0;
+    s.dir_g0 = s.dir_g1 = s.dir_g2 = 0.f; s.dm0 = s.dvs = s.dws = 0.f;
     return bwd_next_segment(p, ray, s, in.max_trace_depth);
 }
 
@@ -225,7 +228,7 @@ __device__ __forceinline__ float basis_at(const float* b, int j) {
 
 // Re-composites one gathered chunk of segment s.seg and accumulates the gradients of every
 // contributing hit (backward.cu:429-655). Returns true while the ray needs another enumeration.
-template <bool DIAG, int KS>
+template <bool DIAG, int KS, bool DIST>
 __device__ __forceinline__ bool bwd_shade(const BwdParams& p, int ray, BwdState& s, const unsigned long long* kb, int cnt, TraceCounters& tc) {
     const dst_trace_inputs& in = p.a.in;
     const bool use_sh = in.colors_precomp == nullptr;
@@ -255,6 +258,15 @@ __device__ __forceinline__ bool bwd_shade(const BwdParams& p, int ray, BwdState&
     float sb[16];
     if (use_sh) sh_basis(in.sh_degree, sdx, sdy, sdz, sb);
     if (DIAG) { if (s.chunk == 0) tc.segs++; }
+    // Distortion extension (primary segment only; see fwd_shade): upstream gradient, the totals the forward saved, the
+    // running sums. With W = sum w (the accumulated opacity), mu = M1 / W, c_k = m_k - mu, V = M2 - M1^2 / W = sum w c^2:
+    // d dist / d m_k = 2 w_k W c_k, d dist / d w_k = W c_k^2 + V, and what lies behind hit k enters through the
+    // transmittance: sum_{i>k} (d dist / d w_i) w_i = W (V - V_k) + V (W - W_k) with the running sums through k.
+    const bool dist_on = DIST && s.seg == 0 && p.a.dL_ddist && p.a.out_dist && tot_acc > 0.0f;
+    const float t_dist = dist_on ? __ldg(p.a.dL_ddist + ray) : 0.f;
+    const float dist_mu = dist_on ? __ldg(p.a.out_dist + 3 * (size_t)ray + 1) / tot_acc : 0.f;
+    const float dist_V = dist_on ? __ldg(p.a.out_dist + 3 * (size_t)ray + 2) - __ldg(p.a.out_dist + 3 * (size_t)ray + 1) * dist_mu : 0.f;
+    float dm0 = s.dm0, dvs = s.dvs, dws = s.dws;
 
     bool stop = false;
     for (int sl = 0; sl < cnt; sl++) {
@@ -307,6 +319,17 @@ __device__ __forceinline__ bool bwd_shade(const BwdParams& p, int ray, BwdState&
         dL_dalpha += t_norm.x * (T_prev * normal.x - (tot_n.x - N.x) * inv) + t_norm.y * (T_prev * normal.y - (tot_n.y - N.y) * inv) +
                      t_norm.z * (T_prev * normal.z - (tot_n.z - N.z) * inv);
         dL_dalpha += t_acc * (T_prev - tot_acc * inv);      // the reference's running weight sum stays 0 (backward.cu:359, 568)
+        float dist_dd = 0.f;       // gradient of the distortion with respect to this hit's depth
+        if (DIST && dist_on) {
+            const float m_abs = DST_DIST_K * (1.0f - DST_DIST_NEAR / dpt);
+            if (contributor == 1) dm0 = m_abs;
+            const float cm = (m_abs - dm0) - dist_mu;
+            dws += w; dvs += w * cm * cm;
+            const float d_dw = tot_acc * cm * cm + dist_V;
+            const float behind = tot_acc * (dist_V - dvs) + dist_V * (tot_acc - dws);
+            dL_dalpha += t_dist * (d_dw * T_prev - behind * inv);
+            dist_dd = t_dist * 2.0f * w * tot_acc * cm * DST_DIST_K * DST_DIST_NEAR / (dpt * dpt);
+        }
 
         const float opac = e.r2.w, G = e.G;
         const float dL_dG = dL_dalpha * opac;
@@ -326,7 +349,7 @@ __device__ __forceinline__ bool bwd_shade(const BwdParams& p, int ray, BwdState&
         V3 dmean = (kk * G) * ((u / sx) * R0 + (v / sy) * R1);
         const V3 dxyz = (dL_du / sx) * R0 + (dL_dv / sy) * R1;
         const V3 rd = v3(sdx, sdy, sdz), ro = v3(sox, soy, soz);
-        const float dL_dd = t_dpt * w + dot(dxyz, rd);
+        const float dL_dd = t_dpt * w + dist_dd + dot(dxyz, rd);
         V3 p1, p2, p3; float h1x, h1y, h2x, h2y, h3x, h3y;
         {
             const float4* vq = reinterpret_cast<const float4*>(in.vertices + 12 * (size_t)gidx);
@@ -402,6 +425,7 @@ __device__ __forceinline__ bool bwd_shade(const BwdParams& p, int ray, BwdState&
     s.dro_x = dL_dray_o.x; s.dro_y = dL_dray_o.y; s.dro_z = dL_dray_o.z;
     s.drd_x = dL_dray_d.x; s.drd_y = dL_dray_d.y; s.drd_z = dL_dray_d.z;
     s.dir_gidx = dir_gidx; s.dir_g0 = dir_g0; s.dir_g1 = dir_g1; s.dir_g2 = dir_g2;
+    s.dm0 = dm0; s.dvs = dvs; s.dws = dws;
     s.chunk++;
     bool seg_done = stop || T_next < T_threshold || cnt < DST_CHUNK || contributor > DST_MAX_INTERSECTION;
     if (!seg_done && s.chunk >= DST_MAX_CHUNKS) { atomicOr(p.status, DST_STATUS_CHUNK_LIMIT); seg_done = true; }
@@ -440,7 +464,7 @@ __global__ void __launch_bounds__(256) k_bwd_init(const __grid_constant__ BwdPar
     p.list[0][i] = ray;
 }
 
-template <bool DIAG>
+template <bool DIAG, bool DIST>
 __global__ void __launch_bounds__(BWD_THREADS) k_bwd_shade(const __grid_constant__ BwdParams p, int round) {
     const int n = p.counts[round];
     if (n < p.min_count) return;
@@ -455,7 +479,7 @@ __global__ void __launch_bounds__(BWD_THREADS) k_bwd_shade(const __grid_constant
         if (ray >= 0) {
             BwdState s;
             bwd_load_state(p.state, ray, s);
-            alive = bwd_shade<DIAG, 1>(p, ray, s, p.kbuf + (size_t)ray * DST_CHUNK, p.kcnt[ray], tc);
+            alive = bwd_shade<DIAG, 1, DIST>(p, ray, s, p.kbuf + (size_t)ray * DST_CHUNK, p.kcnt[ray], tc);
             if (alive) {
                 bwd_store_state(p.state, ray, s);
                 EnumReq q;
@@ -472,7 +496,7 @@ __global__ void __launch_bounds__(BWD_THREADS) k_bwd_shade(const __grid_constant
     }
 }
 
-template <bool DIAG>
+template <bool DIAG, bool DIST>
 __global__ void __launch_bounds__(BWD_THREADS) k_bwd_tail(const __grid_constant__ BwdParams p) {
     __shared__ unsigned long long kshared[DST_CHUNK * BWD_THREADS];
     const int round = first_skipped_round(p.counts, p.rounds, p.min_count);
@@ -491,7 +515,7 @@ __global__ void __launch_bounds__(BWD_THREADS) k_bwd_tail(const __grid_constant_
             bwd_request(s, q);
             const int cnt = knearest<false, DIAG, BWD_THREADS>(p.bvh, q.ox, q.oy, q.oz, q.dx, q.dy, q.dz, kb, p.status, tc, q.kmax0);
             if (DIAG) tc.enums++;
-            alive = bwd_shade<DIAG, BWD_THREADS>(p, ray, s, kb, cnt, tc);
+            alive = bwd_shade<DIAG, BWD_THREADS, DIST>(p, ray, s, kb, cnt, tc);
         }
     }
     if (DIAG && p.a.counters) {
@@ -514,7 +538,7 @@ __device__ __forceinline__ void bwd_flush_counters(unsigned long long* counters,
 // forward composited (chained per segment), so no hierarchy walk is needed; one thread per ray, all
 // segments. Rays whose log is incomplete (log full during the forward) are initialised and queued
 // for k_bwd_tail, which re-traces them.
-template <bool DIAG>
+template <bool DIAG, bool DIST>
 __global__ void __launch_bounds__(BWD_THREADS, DST_BWD_LOGGED_BLOCKS) k_bwd_logged(const __grid_constant__ BwdParams p, long long slots) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const int ray = i < slots ? ray_of_slot(i, p.grid_h, p.grid_w, p.tiled != 0) : -1;
@@ -536,7 +560,7 @@ __global__ void __launch_bounds__(BWD_THREADS, DST_BWD_LOGGED_BLOCKS) k_bwd_logg
                     if (idx < 0) { atomicOr(p.status, DST_STATUS_LOG_MISMATCH); break; }
                     const int2 hdr = __ldg(p.log_hdr + idx);
                     if (DIAG) tc.enums++;
-                    if (!bwd_shade<DIAG, 1>(p, ray, s, p.log_keys + (size_t)idx * DST_CHUNK, hdr.y, tc)) break;
+                    if (!bwd_shade<DIAG, 1, DIST>(p, ray, s, p.log_keys + (size_t)idx * DST_CHUNK, hdr.y, tc)) break;
                     idx = (s.chunk == 0) ? heads[s.seg] : hdr.x;      // chunk == 0: an earlier segment has begun
                 }
             }
@@ -595,6 +619,7 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
     if (a->dL_dshs) DST_CUDA_TRY(h, cudaMemsetAsync(a->dL_dshs, 0, 12 * (size_t)P * a->in.sh_coeffs, st));
     BwdParams p;
     p.a = *a; p.bvh = dst_bvh_view(h); p.cache = h->cache; p.arena = h->arena; p.status = h->status;
+    p.dist_on = h->distortion;
     dst_slot_grid(h, &a->in, &p.grid_h, &p.grid_w);
     p.tiled = p.grid_h >= 16;
     const long long slots = slots_of_grid(p.grid_h, p.grid_w, p.tiled != 0);
@@ -603,6 +628,7 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
     p.state = h->wf_state; p.req = static_cast<EnumReq*>(h->wf_req); p.kbuf = h->wf_kbuf; p.kcnt = h->wf_kcnt;
     p.list[0] = h->wf_list[0]; p.list[1] = h->wf_list[1]; p.counts = h->wf_counts;
     const bool diag = a->counters != nullptr;
+    const bool dist = h->distortion != 0 && a->dL_ddist != nullptr && a->out_dist != nullptr;
     const bool use_log = a->forward_serial != 0 && a->forward_serial == h->log_serial && h->log_H == a->in.H && h->log_W == a->in.W &&
                          h->log_depth == a->in.max_trace_depth;
     p.log_keys = h->log_keys; p.log_hdr = h->log_hdr; p.log_seg_head = h->log_seg_head; p.log_ray_ok = h->log_ray_ok;
@@ -624,8 +650,8 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
         // the forward kept its chunks: re-composite them; rays the log could not hold are queued as round 0 of the
         // re-trace below (normally none: the rounds then find an empty list and return at once)
         const unsigned int blocks = (unsigned int)((slots + BWD_THREADS - 1) / BWD_THREADS);
-        if (diag) k_bwd_logged<true><<<blocks, BWD_THREADS, 0, st>>>(p, slots);
-        else k_bwd_logged<false><<<blocks, BWD_THREADS, 0, st>>>(p, slots);
+        if (dist) { if (diag) k_bwd_logged<true, true><<<blocks, BWD_THREADS, 0, st>>>(p, slots); else k_bwd_logged<false, true><<<blocks, BWD_THREADS, 0, st>>>(p, slots); }
+        else { if (diag) k_bwd_logged<true, false><<<blocks, BWD_THREADS, 0, st>>>(p, slots); else k_bwd_logged<false, false><<<blocks, BWD_THREADS, 0, st>>>(p, slots); }
     } else {
         k_bwd_init<<<(unsigned int)((slots + 255) / 256), 256, 0, st>>>(p, slots);
     }
@@ -635,13 +661,13 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
         launch_gather(diag, g_enum, st, p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt,
                       p.status, a->counters, r + 1);
         dst_prof_mark(h, 3, 1, st);
-        if (diag) k_bwd_shade<true><<<g_shade, BWD_THREADS, 0, st>>>(p, r);
-        else k_bwd_shade<false><<<g_shade, BWD_THREADS, 0, st>>>(p, r);
+        if (dist) { if (diag) k_bwd_shade<true, true><<<g_shade, BWD_THREADS, 0, st>>>(p, r); else k_bwd_shade<false, true><<<g_shade, BWD_THREADS, 0, st>>>(p, r); }
+        else { if (diag) k_bwd_shade<true, false><<<g_shade, BWD_THREADS, 0, st>>>(p, r); else k_bwd_shade<false, false><<<g_shade, BWD_THREADS, 0, st>>>(p, r); }
         if (p.lv.stable) k_compact<<<g_compact, 256, 0, st>>>(p.lv, p.counts + r, p.counts + r + 1, p.min_count, p.list[(r + 1) & 1], r);
     }
     const int g_tail = dst_wavefront_grid(h, wave ? p.min_count : slots, BWD_THREADS, 4);
-    if (diag) k_bwd_tail<true><<<g_tail, BWD_THREADS, 0, st>>>(p);
-    else k_bwd_tail<false><<<g_tail, BWD_THREADS, 0, st>>>(p);
+    if (dist) { if (diag) k_bwd_tail<true, true><<<g_tail, BWD_THREADS, 0, st>>>(p); else k_bwd_tail<false, true><<<g_tail, BWD_THREADS, 0, st>>>(p); }
+    else { if (diag) k_bwd_tail<true, false><<<g_tail, BWD_THREADS, 0, st>>>(p); else k_bwd_tail<false, false><<<g_tail, BWD_THREADS, 0, st>>>(p); }
     dst_prof_mark(h, 2, 1, st);
     DST_CUDA_TRY(h, cudaGetLastError());
     k_unpack<<<(unsigned int)((P + 255) / 256), 256, 0, st>>>((int)P, h->arena, a->dL_drotations, a->dL_dmeans3D, a->dL_dopacities,

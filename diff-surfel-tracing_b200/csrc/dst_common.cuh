@@ -83,6 +83,7 @@ struct dst_handle {
     void* wf_state; size_t wf_state_bytes; void* wf_req; unsigned long long* wf_kbuf; int* wf_kcnt; int* wf_list[2]; int* wf_counts;
     int* wf_tmp; int* wf_wcnt; int* wf_bcnt;      // order-preserving list hand-over (LiveLists in dst_trace.cuh); wf_bcnt holds both counter sets
     long long wf_cap;
+    int distortion;               // 1: the depth-distortion output and its gradient are computed (default 0: zeros, as the reference)
     int stable_lists;             // 1 (default): live lists keep their order from round to round; 0: survivors are appended per warp
     long long wf_min_rays;        // launches with fewer rays skip the wavefront rounds
     // chunk log: the 16-hit chunks every ray composited in the last training forward, chained per ray and segment,
@@ -182,6 +183,10 @@ __device__ __forceinline__ QuadFrame make_quad_frame(const float* v) {
 }
 
 #define DST_T_MAX 1e16f
+// mapped depth of the distortion term, m = DST_DIST_K (1 - DST_DIST_NEAR / depth): far / (far - near) with the near = 0.2 and
+// far = 100 the reference defines for it (optix_tracer/auxiliary.h:20-21)
+#define DST_DIST_NEAR 0.2f
+#define DST_DIST_K (100.0f / (100.0f - 0.2f))
 
 // Ray/quad predicate. Returns true with t in [0, 1e16) and tri = 0/1 (which triangle of the quad,
 // by the side of the shared diagonal). `tcut`: hits with t > tcut are of no interest to the caller

@@ -44,6 +44,7 @@ struct FwdParams {
     dst_fwd_args a;
     CamConst cam;       // used when cam_on: rays are generated, not loaded
     int cam_on;
+    int dist_on;        // depth-distortion extension (dst.h, DST_OPT_DISTORTION)
     BvhView bvh;
     const float4* cache;
     unsigned int* status;
@@ -70,9 +71,9 @@ struct __align__(16) FwdState {
     float D, Nx, Ny, Nz;
     float O0, O1, s_prod, rgb0;
     float rgb1, rgb2; int last_gidx, contributor;
-    int bounce, chunk, hit_count, pad0;
+    int bounce, chunk, hit_count; float m0;      // m0: mapped depth of the first contribution (distortion extension)
     int log_prev;       // last chunk-log record of the current segment, -1 at a segment start
-    float pad1[3];
+    float dist, m1, m2; // depth distortion of the primary segment and the two moments of the mapped depth (extension)
 };
 static_assert(sizeof(FwdState) == 128, "ray state is one 128-byte record");
 
@@ -156,7 +157,8 @@ __device__ __forceinline__ void fwd_init_state(const FwdParams& p, int ray, FwdS
         s.sox = __ldg(in.ray_o + 3 * (size_t)ray); s.soy = __ldg(in.ray_o + 3 * (size_t)ray + 1); s.soz = __ldg(in.ray_o + 3 * (size_t)ray + 2);
         s.sdx = __ldg(in.ray_d + 3 * (size_t)ray); s.sdy = __ldg(in.ray_d + 3 * (size_t)ray + 1); s.sdz = __ldg(in.ray_d + 3 * (size_t)ray + 2);
     }
-    s.s_prod = 1.f; s.rgb0 = s.rgb1 = s.rgb2 = 0.f; s.bounce = 0; s.hit_count = 0; s.pad0 = 0;
+    s.s_prod = 1.f; s.rgb0 = s.rgb1 = s.rgb2 = 0.f; s.bounce = 0; s.hit_count = 0;
+    s.dist = s.m1 = s.m2 = 0.f; s.m0 = -1.f;
     fwd_begin_segment(s);
 }
 
@@ -230,6 +232,16 @@ __device__ __forceinline__ bool fwd_shade(const FwdParams& p, int ray, FwdState&
             const float2 ax = __ldg(reinterpret_cast<const float2*>(in.others_precomp) + gidx);
             s.O0 = xadd(s.O0, xmul(w, ax.x)); s.O1 = xadd(s.O1, xmul(w, ax.y));
         }
+        if (p.dist_on && s.bounce == 0) {
+            // Depth distortion of 2D Gaussian splatting over the contributions of the primary segment (an extension: the
+            // reference leaves the output at zero, forward.cu:286): sum_i sum_{j<i} w_i w_j (m_i - m_j)^2, accumulated front to
+            // back, with the mapped depth m taken relative to the first contribution's (only differences enter).
+            const float m_abs = DST_DIST_K * (1.0f - DST_DIST_NEAR / s.dpt);
+            if (s.contributor == 1) s.m0 = m_abs;
+            const float m = m_abs - s.m0;
+            s.dist += w * (m * m * (1.0f - s.T_prev) + s.m2 - 2.0f * m * s.m1);
+            s.m1 += m * w; s.m2 += m * m * w;
+        }
         s.D = xadd(s.D, xmul(w, s.dpt));
         s.Nx = xadd(s.Nx, xmul(w, nsign * r2.x)); s.Ny = xadd(s.Ny, xmul(w, nsign * r2.y)); s.Nz = xadd(s.Nz, xmul(w, nsign * r2.z));
         s.T_prev = T_next;
@@ -256,7 +268,8 @@ __device__ __forceinline__ bool fwd_shade(const FwdParams& p, int ray, FwdState&
         p.a.out_dpt[ray] = s.D; p.a.out_acc[ray] = A;
         p.a.out_norm[3 * (size_t)ray] = s.Nx; p.a.out_norm[3 * (size_t)ray + 1] = s.Ny; p.a.out_norm[3 * (size_t)ray + 2] = s.Nz;
         p.a.out_aux[2 * (size_t)ray] = s.O0; p.a.out_aux[2 * (size_t)ray + 1] = s.O1;
-        p.a.out_dist[3 * (size_t)ray] = 0.f; p.a.out_dist[3 * (size_t)ray + 1] = 0.f; p.a.out_dist[3 * (size_t)ray + 2] = 0.f;
+        // zeros as the reference, or (extension) the distortion and the two moments its gradient needs
+        p.a.out_dist[3 * (size_t)ray] = s.dist; p.a.out_dist[3 * (size_t)ray + 1] = s.m1; p.a.out_dist[3 * (size_t)ray + 2] = s.m2;
     }
     const float f_this = (s.bounce == in.max_trace_depth) ? 1.0f : xsub(1.0f, s.O0);
     s.rgb0 = xadd(s.rgb0, xmul(xmul(C0, f_this), s.s_prod));
@@ -632,6 +645,7 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
     FwdParams p;
     p.a = *a; p.bvh = dst_bvh_view(h); p.cache = h->cache; p.status = h->status;
     p.cam_on = cam != nullptr;
+    p.dist_on = h->distortion;
     if (cam) camera_constants(cam, &p.cam); else memset(&p.cam, 0, sizeof(p.cam));
     dst_slot_grid(h, &a->in, &p.grid_h, &p.grid_w);
     p.tiled = p.grid_h >= 16;
@@ -807,6 +821,7 @@ extern "C" int dst_forward_static(dst_handle* h, const dst_fwd_args* a, void* st
     FwdParams p;
     p.a = *a; p.bvh = dst_bvh_view(h); p.status = h->status; p.tiled = tiled; p.grid_h = a->in.H; p.grid_w = a->in.W;
     p.cam_on = 0; memset(&p.cam, 0, sizeof(p.cam));
+    p.dist_on = h->distortion;
     p.cache = reinterpret_cast<const float4*>(base + ST_OFF_CACHE);
     p.state = base + ST_OFF_STATE;
     p.req = reinterpret_cast<EnumReq*>(base + ST_OFF_REQ);

@@ -188,6 +188,11 @@ class OptiXStateWrapper:
         _check(self, lib().dst_kernel_launches(self.handle, C.byref(n)))
         return n.value
 
+    def set_distortion(self, on):
+        """Extension: compute the depth-distortion output (channel 0 of out_dist) and its gradient. Off by default: the
+        reference leaves the output at zero."""
+        _check(self, lib().dst_set_option(self.handle, 8, int(bool(on))))
+
     def set_stable_lists(self, on):
         """Wavefront rounds keep the live-ray list in its original (pixel tile) order (default) or append survivors
         warp by warp as they finish. Scheduling only."""

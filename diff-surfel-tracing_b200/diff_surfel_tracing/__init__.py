@@ -121,6 +121,11 @@ class SurfelTracer(nn.Module):
     def build_acceleration_structure(self, vertices: torch.Tensor, triangles: torch.Tensor, rebuild: bool = 1):
         return _C.build_acceleration_structure(self.optix_context, vertices, triangles, rebuild)
 
+    def enable_distortion(self, enabled: bool = True):
+        """Extension: `dist` becomes the depth-distortion map of 2D Gaussian splatting over the primary segment's
+        contributions (mapped depth with near 0.2, far 100), differentiable. Off by default: the reference returns zeros."""
+        self.optix_context.set_distortion(enabled)
+
     def set_gradient_group(self, enabled: bool = True, group=None):
         """Multi-GPU training with sharded rays and replicated surfels (the reference is single-GPU): when enabled,
         every backward call sums the per-surfel gradients over the ranks of `group` (None: the default process

@@ -86,7 +86,7 @@ typedef struct dst_fwd_args {
     float *out_dpt;               /* (H, W, 1)  */
     float *out_acc;               /* (H, W, 1)  */
     float *out_norm;              /* (H, W, 3)  */
-    float *out_dist;              /* (H, W, 3), zeros: distortion is unimplemented upstream       */
+    float *out_dist;              /* (H, W, 3), zeros as upstream unless DST_OPT_DISTORTION is set  */
     float *out_aux;               /* (H, W, 2)  */
     float *mid_val;               /* (H, W, mid_stride); untraced bounces are zero                */
     float *a_weights;             /* (P, 1), zeroed then accumulated here when training; or NULL  */
@@ -101,7 +101,7 @@ typedef struct dst_bwd_args {
     dst_trace_inputs in;
     /* state saved by the forward call */
     const float *out_rgb, *out_dpt, *out_acc, *out_norm, *out_dist, *out_aux, *mid_val;
-    /* upstream gradients, shapes of the forward outputs; dL_ddist is (H, W, 1) and unused       */
+    /* upstream gradients, shapes of the forward outputs; dL_ddist is (H, W, 1), read only with DST_OPT_DISTORTION */
     const float *dL_drgb, *dL_ddpt, *dL_dacc, *dL_dnorm, *dL_ddist, *dL_daux;
     /* gradient outputs, fully written by the call (no pre-zeroing needed)                        */
     float *dL_dray_o, *dL_dray_d; /* (H, W, 3)                                                    */
@@ -230,6 +230,15 @@ int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t*
  * segment before rays on a reflected one), so that the 32 rays a warp of the gather kernel takes keep
  * starting close to each other; 0 appends the survivors warp by warp in the order the warps happen to finish. */
 #define DST_OPT_STABLE_LISTS 7
+/* Depth distortion, an EXTENSION: the reference declares a distortion output and leaves it at zero with a TODO
+ * (optix_tracer/forward.cu:286, backward.cu:526, 570). 0 (default): zeros, as the reference. 1: out_dist[..., 0] is the
+ * depth-distortion sum of 2D Gaussian splatting over the contributions of the primary segment,
+ * sum_i sum_{j<i} w_i w_j (m_i - m_j)^2 with the mapped depth m = far / (far - near) * (1 - near / depth), near = 0.2 and
+ * far = 100 (the constants optix_tracer/auxiliary.h:20-21 defines and never uses); out_dist[..., 1] and [..., 2] hold the
+ * moments sum w m and sum w m^2 the backward needs; dst_backward then adds the gradient of dL_ddist to every input
+ * gradient. There is nothing upstream to compare this with: it is tested against a CPU restatement of the same formula
+ * and against finite differences. */
+#define DST_OPT_DISTORTION 8
 int dst_set_option(dst_handle* h, int option, int64_t value);
 
 /* Timing of the main kernels with CUDA events on the launching stream. While enabled, every

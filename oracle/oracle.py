@@ -18,7 +18,7 @@ _f = C.POINTER(C.c_float)
 class OrcArgs(C.Structure):
     _fields_ = (
         [(n, C.c_int32) for n in ("P", "H", "W", "D", "M", "max_trace_depth", "training", "start_from_first",
-                                  "clean", "nthreads", "mid_stride", "hit_cap", "portable_exp", "reserved")]
+                                  "clean", "nthreads", "mid_stride", "hit_cap", "portable_exp", "distortion")]
         + [("specular_threshold", C.c_float), ("scale_modifier", C.c_float)]
         + [(n, C.c_void_p) for n in (
             "ray_o", "ray_d", "vertices", "background", "means3D", "shs", "colors_precomp", "others_precomp",
@@ -120,9 +120,10 @@ def key_pidx(keys):
 class Oracle:
     """forward()/backward() with the reference's argument meanings (trace_surfels.h:20-83)."""
 
-    def __init__(self, scene: Scene, impl="restatement", clean=True, nthreads=0, hit_cap=0, portable_exp=True):
+    def __init__(self, scene: Scene, impl="restatement", clean=True, nthreads=0, hit_cap=0, portable_exp=True, distortion=False):
         self.scene, self.impl, self.clean, self.nthreads, self.hit_cap = scene, impl, clean, nthreads, hit_cap
         self.portable_exp = portable_exp
+        self.distortion = distortion       # restatement only: the reference has no distortion code to compare with
         if impl == "reference" and not reference_built():
             raise FileNotFoundError("oracle/_ref is not built (the reference tree was absent at build time)")
 
@@ -156,6 +157,7 @@ class Oracle:
         a.clean = int(self.clean)
         a.nthreads = self.nthreads
         a.portable_exp = int(self.portable_exp)
+        a.distortion = int(self.distortion)
         a.mid_stride = self._mid_stride(a.max_trace_depth)
         a.specular_threshold = float(w.get("specular_threshold", 0.0))
         a.scale_modifier = 1.0

@@ -13,7 +13,7 @@ struct OrcArgs {
     int32_t mid_stride;     // floats of mid_val per ray
     int32_t hit_cap;        // slots of hit_log per ray
     int32_t portable_exp;   // 1: the Gaussian falloff uses orc::pexp (reproducible on the GPU); 0: libm expf
-    int32_t reserved;
+    int32_t distortion;     // 1: the depth-distortion output and its gradient (an extension: the reference leaves them at zero)
     float specular_threshold, scale_modifier;
     const float *ray_o, *ray_d, *vertices, *background, *means3D, *shs, *colors_precomp, *others_precomp,
                 *opacities, *scales, *rotations;

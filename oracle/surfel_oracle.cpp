@@ -183,11 +183,12 @@ static void sh_color_vjp(int deg, const float* shrow, F3 dir, const float* clamp
 
 struct Ctx { const OrcArgs* a; const orc::Scene* sc; };
 
-struct TraceOut { float C[3]; float D, A; F3 N; float O[2]; float T; F3 E; };
+struct TraceOut { float C[3]; float D, A; F3 N; float O[2]; float T; F3 E; float Dist, M1, M2, m0; };
 struct TraceBwd {   // per-trace totals and upstream gradients, backward.cu:342-354, and the register accumulators :366-367
     float out_rgb[3]; float out_dpt, out_acc; F3 out_norm; float out_aux[2];
     float dL_drgb[3]; float dL_ddpt, dL_dacc; F3 dL_dnorm; float dL_daux[2];
     F3* dL_dray_o; F3* dL_dray_d;
+    float dL_ddist, out_m1, out_m2;      // distortion extension: upstream gradient and the two moments the forward saved
 };
 struct Tally { long enums, tests, evals, contribs, anyhits, segs; };
 
@@ -198,8 +199,21 @@ static inline void atomic_add(float* p, float v) {
 
 // forward.cu:136-315 and backward.cu:332-655: chunked nearest-16 gather, front-to-back compositing,
 // and (bw != nullptr) the per-contribution gradients.
+//
+// Distortion (dist_on; NOT in the reference, which leaves the output at zero with a TODO, forward.cu:286 and
+// backward.cu:526, 570): the depth-distortion sum of 2D Gaussian splatting over the contributions of the primary
+// segment, dist = sum_i sum_{j<i} w_i w_j (m_i - m_j)^2 with the mapped depth m = far / (far - near) * (1 - near / dpt),
+// near = 0.2 and far = 100 being the two constants the reference defines for it (auxiliary.h:20-21) and never uses.
+// Only differences of m enter, so m is taken relative to the first contribution's value m0 (mapped depths of one ray
+// sit close together just below 1; their squares would cancel). Accumulated front to back as
+// dist += w (m^2 A + M2 - 2 m M1), M1 += m w, M2 += m^2 w, A = 1 - T_prev. Gradient, with the totals W = sum w (the
+// accumulated opacity), M1, M2 of the whole segment, mu = M1 / W, c_k = m_k - mu, V = M2 - M1^2 / W = sum w c^2:
+// d dist / d m_k = 2 w_k W c_k, d dist / d w_k = W c_k^2 + V, and through w_i = alpha_i T_{i-1}:
+// d dist / d alpha_k = (d dist / d w_k) T_{k-1} - [W (V - V_k) + V (W - W_k)] / (1 - alpha_k), the bracket being
+// sum_{i>k} (d dist / d w_i) w_i written with the running sums V_k = sum_{j<=k} w_j c_j^2 and W_k through k.
+static const float DIST_K = 100.0f / (100.0f - 0.2f);
 static void trace_ray(const Ctx& cx, int ray, F3 ray_o, F3 ray_d, float min_depth, float T_threshold,
-                      TraceOut& out, TraceBwd* bw, Tally& tl)
+                      TraceOut& out, TraceBwd* bw, Tally& tl, bool dist_on = false)
 {
     const OrcArgs& A = *cx.a;
     uint64_t buf[orc::KCHUNK];
@@ -209,6 +223,8 @@ static void trace_ray(const Ctx& cx, int ray, F3 ray_o, F3 ray_d, float min_dept
     F3 ray_ot = ray_o;
     float c[3] = { 0, 0, 0 }, clamped[3] = { 0, 0, 0 };
     float W = 0.0f;                           // never updated by the reference (backward.cu:359, 568)
+    float Wsum = 0.0f, Vsum = 0.0f;           // running sums of w and w c^2, for the distortion gradient
+    bool dist_first = true;
     const float T_final = bw ? 1.0f - bw->out_acc : 0.f;
     tl.segs++;
 
@@ -268,6 +284,14 @@ static void trace_ray(const Ctx& cx, int ray, F3 ray_o, F3 ray_d, float min_dept
                 for (int ch = 0; ch < AUX_CHANNELS; ch++) out.O[ch] += w * A.others_precomp[ch + AUX_CHANNELS * (size_t)gidx];
             out.D += w * dpt;
             out.N += w * normal;
+            float dist_m = 0.0f;
+            if (dist_on) {
+                const float m_abs = DIST_K * (1.0f - 0.2f / dpt);
+                if (dist_first) { out.m0 = m_abs; dist_first = false; }
+                dist_m = m_abs - out.m0;
+                out.Dist += w * (dist_m * dist_m * (1.0f - T_prev) + out.M2 - 2.0f * dist_m * out.M1);
+                out.M1 += dist_m * w; out.M2 += dist_m * dist_m * w;
+            }
 
             if (!bw) {
                 if (A.training && A.a_weights) atomic_add(A.a_weights + gidx, w);   // forward.cu:291-296
@@ -295,6 +319,15 @@ static void trace_ray(const Ctx& cx, int ray, F3 ray_o, F3 ray_d, float min_dept
                 F3 dL_dN = bw->dL_dnorm * w;
                 dL_dalpha += sumf3(bw->dL_dnorm * (T_prev * normal - (bw->out_norm - out.N) / numerator));
                 dL_dalpha += bw->dL_dacc * (T_prev * 1.f - (bw->out_acc - W) / numerator);
+                if (dist_on) {
+                    const float Wt = bw->out_acc, mu = bw->out_m1 / Wt, V = bw->out_m2 - bw->out_m1 * mu;
+                    const float cm = dist_m - mu;
+                    Wsum += w; Vsum += w * cm * cm;
+                    const float d_dw = Wt * cm * cm + V;
+                    const float behind = Wt * (V - Vsum) + V * (Wt - Wsum);
+                    dL_dalpha += bw->dL_ddist * (d_dw * T_prev - behind / numerator);
+                    dL_dD += bw->dL_ddist * 2.0f * w * Wt * cm * DIST_K * 0.2f / (dpt * dpt);
+                }
                 // :573-578
                 const float dL_dG = dL_dalpha * opac;
                 float power_clamped = (opac * G) > 0.99f ? 0.0f : 1.0f;
@@ -384,7 +417,7 @@ static float min_depth_of(const OrcArgs& A, int i) {     // forward.cu:353
 static void forward_ray(const Ctx& cx, int ray, Tally& tl) {
     const OrcArgs& A = *cx.a;
     F3 ray_o = ld3(A.ray_o + 3 * (size_t)ray), ray_d = ld3(A.ray_d + 3 * (size_t)ray);
-    float out_rgb[3] = { 0, 0, 0 }, out_dpt = 0, out_acc = 0, out_aux[2] = { 0, 0 };
+    float out_rgb[3] = { 0, 0, 0 }, out_dpt = 0, out_acc = 0, out_aux[2] = { 0, 0 }, out_dist[3] = { 0, 0, 0 };
     F3 out_norm = mk3(0, 0, 0);
     float* mid = A.mid_val + (size_t)ray * A.mid_stride;
     for (int k = 0; k < A.mid_stride; k++) mid[k] = 0.0f;     // the reference leaves untraced bounces uninitialised (forward.cu:446)
@@ -392,7 +425,8 @@ static void forward_ray(const Ctx& cx, int ray, Tally& tl) {
     float s_prod = 1.0f;
     for (int i = 0; i < A.max_trace_depth + 1; i++) {
         TraceOut t; memset(&t, 0, sizeof(t)); t.T = 1.0f;
-        trace_ray(cx, ray, ray_ot, ray_dt, min_depth_of(A, i), 0.0001f, t, nullptr, tl);
+        trace_ray(cx, ray, ray_ot, ray_dt, min_depth_of(A, i), 0.0001f, t, nullptr, tl, i == 0 && A.distortion);
+        if (i == 0) { out_dist[0] = t.Dist; out_dist[1] = t.M1; out_dist[2] = t.M2; }
         if (i == 0) { out_dpt = t.D; out_acc = t.A; out_norm = t.N; out_aux[0] = t.O[0]; out_aux[1] = t.O[1]; }
         float f_this = (i == A.max_trace_depth) ? 1.0f : 1 - t.O[SPECULAR];
         for (int ch = 0; ch < 3; ch++) out_rgb[ch] += t.C[ch] * f_this * s_prod;
@@ -413,7 +447,8 @@ static void forward_ray(const Ctx& cx, int ray, Tally& tl) {
     for (int ch = 0; ch < 3; ch++) A.out_rgb[3 * (size_t)ray + ch] = out_rgb[ch];
     A.out_dpt[ray] = out_dpt; A.out_acc[ray] = out_acc;
     A.out_norm[3 * (size_t)ray] = out_norm.x; A.out_norm[3 * (size_t)ray + 1] = out_norm.y; A.out_norm[3 * (size_t)ray + 2] = out_norm.z;
-    for (int k = 0; k < 3; k++) A.out_dist[3 * (size_t)ray + k] = 0.0f;              // distortion is a TODO upstream (forward.cu:286)
+    // zeros as upstream (forward.cu:286) unless the distortion extension is on: then the sum and the two moments its gradient needs
+    for (int k = 0; k < 3; k++) A.out_dist[3 * (size_t)ray + k] = out_dist[k];
     A.out_aux[2 * (size_t)ray] = out_aux[0]; A.out_aux[2 * (size_t)ray + 1] = out_aux[1];
 }
 
@@ -472,8 +507,11 @@ static void backward_ray(const Ctx& cx, int ray, Tally& tl) {
             b.dL_daux[0] += g_aux[0]; b.dL_daux[1] += g_aux[1];
         }
         b.dL_dray_o = &dL_dray_o; b.dL_dray_d = &dL_dray_d;
+        const bool dist_on = i == 0 && A.distortion && A.dL_ddist && A.out_dist;
+        b.dL_ddist = dist_on ? A.dL_ddist[ray] : 0.0f;
+        b.out_m1 = dist_on ? A.out_dist[3 * (size_t)ray + 1] : 0.0f; b.out_m2 = dist_on ? A.out_dist[3 * (size_t)ray + 2] : 0.0f;
         TraceOut t; memset(&t, 0, sizeof(t)); t.T = 1.0f;
-        trace_ray(cx, ray, ray_ot, ray_dt, min_depth_of(A, i), 0.0001f, t, &b, tl);
+        trace_ray(cx, ray, ray_ot, ray_dt, min_depth_of(A, i), 0.0001f, t, &b, tl, dist_on);
     }
     A.dL_dray_o[3 * (size_t)ray] = dL_dray_o.x; A.dL_dray_o[3 * (size_t)ray + 1] = dL_dray_o.y; A.dL_dray_o[3 * (size_t)ray + 2] = dL_dray_o.z;
     A.dL_dray_d[3 * (size_t)ray] = dL_dray_d.x; A.dL_dray_d[3 * (size_t)ray + 1] = dL_dray_d.y; A.dL_dray_d[3 * (size_t)ray + 2] = dL_dray_d.z;

@@ -113,6 +113,38 @@ def test_portable_exp_accuracy(oracle_mod, config, record_property):
         assert d[~fragile].max() < (1e-5 if config == 1 else 3e-5)
 
 
+def test_distortion_extension_matches_finite_differences(oracle_mod):
+    """The depth-distortion term is an extension (zeros in the reference), so nothing pins it from outside: the
+    restatement's gradient is checked against central differences of its own forward, along a random direction in
+    opacity space and along a shift of every ray origin along its ray (which changes every hit depth and nothing
+    else). Rays whose contributing hits change under the perturbation are left out."""
+    w = hp.workloads.make_workload(1, P=3000, H=12, W=12)
+    sc = oracle_mod.Scene(w["v"])
+    mk = lambda: oracle_mod.Oracle(sc, distortion=True, portable_exp=False, hit_cap=300, nthreads=4)
+    f = mk().forward(w)
+    assert f["dist"][..., 0].max() > 0 and np.abs(f["dist"][..., 0] - 0).min() >= 0
+    assert float(np.abs(oracle_mod.Oracle(sc, hit_cap=300).forward(w)["dist"]).max()) == 0.0       # off by default
+    b = mk().backward(w, f, dict(dist=np.ones((12, 12, 1), np.float32)))
+    rd = w["ray_d"].numpy()
+
+    def fd(plus, minus, eps):
+        fp, fm = mk().forward(plus), mk().forward(minus)
+        keep = (fp["hit_log"] == fm["hit_log"]).all(-1)
+        d = fp["dist"][..., 0].reshape(-1).astype(np.float64) - fm["dist"][..., 0].reshape(-1)
+        return d[keep].sum() / (2 * eps), keep
+
+    eps = 3e-3
+    num, keep = fd(dict(w, ray_o=(w["ray_o"] - eps * w["ray_d"]).contiguous()), dict(w, ray_o=(w["ray_o"] + eps * w["ray_d"]).contiguous()), eps)
+    ana = float(-((b["ray_o"] * rd).sum(-1).reshape(-1)[keep]).sum())
+    assert keep.sum() > 100 and abs(num - ana) <= 0.05 * abs(ana), (num, ana)
+    g = np.random.default_rng(1).standard_normal(w["opacities"].shape).astype(np.float32)
+    eps = 1e-3
+    num, keep = fd(dict(w, opacities=w["opacities"] + eps * torch.from_numpy(g)), dict(w, opacities=w["opacities"] - eps * torch.from_numpy(g)), eps)
+    assert keep.all()
+    ana = float((b["opacities"] * g).sum())
+    assert abs(num - ana) <= 0.05 * abs(ana), (num, ana)          # float32 forward: the differences carry a few per cent of noise
+
+
 @pytest.mark.parametrize("config", [1, 2, 3, 4, 5])
 def test_restatement_pinned_to_host_compiled_reference(oracle_mod, config):
     """The restatement equals the reference's own shader sources (compiled for the host, same enumerator):

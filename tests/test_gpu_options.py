@@ -144,3 +144,63 @@ def test_inference_mode(C, oracle_mod):
     orc = oracle_mod.Oracle(oracle_mod.Scene(w["v"]), impl="restatement", hit_cap=320, portable_exp=True)
     got, want = _compare(C, orc, w, wave=True, training=False)
     assert float(np.abs(want["wet"]).max()) == 0.0
+
+
+@pytest.mark.parametrize("config,wave", [(1, False), (3, True), (4, False)])
+def test_distortion_extension(C, oracle_mod, config, wave):
+    """The depth-distortion output (an extension: zeros in the reference) against the CPU restatement of the same
+    formula: forward within 1e-5, gradients of an upstream on dist (alone, and mixed with the others) within 1e-3
+    relative L2; every other output keeps its bits; off by default."""
+    w = hp.reduced_workload(config)
+    wc = hp.to_cuda(w)
+    st = _state(C, wc, wave)
+    off = hp.cuda_forward(C, st, wc)
+    assert float(off["dist"].abs().max()) == 0.0
+    st.set_distortion(True)
+    got = hp.cuda_forward(C, st, wc)
+    orc = oracle_mod.Oracle(oracle_mod.Scene(w["v"]), impl="restatement", portable_exp=True, distortion=True)
+    want = orc.forward(w)
+    for k in ("rgb", "dpt", "acc", "norm", "aux", "mid"):
+        assert torch.equal(got[k], off[k]), k
+    gd = got["dist"].cpu().numpy().reshape(want["dist"].shape)
+    assert float(np.abs(want["dist"][..., 0]).max()) > 0
+    assert np.abs(gd - want["dist"]).max() <= 1e-4 * float(np.abs(want["dist"]).max())          # free-form arithmetic on both sides
+    H, W = w["ray_o"].shape[:2]
+    gen = torch.Generator().manual_seed(3)
+    ups = [dict(dist=torch.ones((H, W, 1))),
+           {k: torch.randn((H, W, c), generator=gen) for k, c in (("rgb", 3), ("dpt", 1), ("acc", 1), ("norm", 3), ("aux", 2), ("dist", 1))}]
+    for serial in (st.last_forward_serial, 0):
+        for up in ups:
+            gb = hp.cuda_backward(C, st, wc, got, {k: v.cuda() for k, v in up.items()}, serial=serial)
+            torch.cuda.synchronize()
+            assert st.status() == 0
+            saved = {k: got[k].cpu().numpy().reshape(want[k].shape) for k in ("rgb", "dpt", "acc", "norm", "dist", "aux", "mid")}
+            ob = orc.backward(w, saved, {k: v.numpy() for k, v in up.items()})
+            for k in hp.GRAD_KEYS:
+                g, o = gb[k].cpu().numpy().reshape(ob[k].shape), ob[k]
+                m = np.isfinite(o)
+                assert np.array_equal(np.isfinite(g), m), k
+                if k in ("means3D", "opacities", "scales", "rotations"):
+                    assert float(np.abs(o[m]).max()) > 0, k
+                assert hp.rel_l2(g[m], o[m]) <= GRAD_RTOL, f"config {config} grad {k}: {hp.rel_l2(g[m], o[m])}"
+
+
+def test_distortion_through_the_module(C):
+    from diff_surfel_tracing import SurfelTracer, SurfelTracingSettings
+    w = hp.reduced_workload(1)
+    wc = hp.to_cuda(w)
+    tracer = SurfelTracer()
+    tracer.enable_distortion(True)
+    tracer.build_acceleration_structure(wc["v"], wc["f"], rebuild=True)
+    leaves = {k: wc[k].clone().requires_grad_(True) for k in ("means3D", "shs", "opacities", "scales", "rotations")}
+    g3d = torch.zeros_like(wc["means3D"], requires_grad=True)
+    e = torch.zeros(1, device="cuda")
+    settings = SurfelTracingSettings(128, 128, 1.0, 1.0, wc["bg"], 1.0, e, e, 0, e, False, False)
+    out = tracer(wc["ray_o"], wc["ray_d"], wc["v"], leaves["means3D"], g3d, shs=leaves["shs"], opacities=leaves["opacities"],
+                 scales=leaves["scales"], rotations=leaves["rotations"], tracer_settings=settings)
+    dist = out[4]
+    assert dist.shape == (128, 128, 1) and float(dist.max()) > 0 and float(dist.min()) >= -1e-7
+    dist.sum().backward()
+    for k in ("means3D", "opacities", "scales", "rotations"):
+        assert leaves[k].grad is not None and torch.isfinite(leaves[k].grad).all() and float(leaves[k].grad.abs().sum()) > 0, k
+    assert float(leaves["shs"].grad.abs().sum()) == 0.0          # the distortion does not depend on colour
