@@ -36,7 +36,8 @@ def shard_image_rows(ray_o: torch.Tensor, ray_d: torch.Tensor, world: int, rank:
     if world <= 0 or not (0 <= rank < world):
         raise ValueError("bad rank / world size")
     n_blocks = (image_h + block - 1) // block
-    rows = torch.cat([torch.arange(b * block, min((b + 1) * block, image_h)) for b in range(rank, n_blocks, world)]).to(ray_o.device)
+    mine = [torch.arange(b * block, min((b + 1) * block, image_h)) for b in range(rank, n_blocks, world)]
+    rows = (torch.cat(mine) if mine else torch.zeros((0,), dtype=torch.long)).to(ray_o.device)       # more ranks than row blocks: an empty share
     B = ray_o.shape[0]
     pick = lambda t: t.reshape(B, image_h, image_w, 3).index_select(1, rows).reshape(B, -1, 3).contiguous()
     return pick(ray_o), pick(ray_d)

@@ -308,6 +308,7 @@ def test_split_rows_covers_everything():
             assert torch.equal(pd, -po) and po.is_contiguous() and po.shape[1] % w == 0
         sizes = [p[0].shape[1] // w for p in parts]
         assert max(sizes) - min(sizes) <= 4
+    assert shard.shard_image_rows(o, o, 8, 7, h, w)[0].shape == (B, 0, 3)      # 7 row blocks, 8 ranks: the last rank gets nothing
     first = shard.shard_image_rows(o, o, 2, 1, h, w)[0].reshape(B, -1, w, 3)
     assert torch.equal(first[:, :4], o.reshape(B, h, w, 3)[:, 4:8])          # rank 1 starts with image rows 4..7
 
