@@ -132,23 +132,6 @@ __device__ __forceinline__ int knearest(const BvhView& bvh, float ox, float oy, 
     return n;
 }
 
-// Ray index of a thread. Image-like grids (H >= 16) are walked in 8x4 pixel tiles per warp so the
-// rays of a warp stay close in the hierarchy; batched ray lists (few rows) are walked linearly.
-// The reference's launch puts consecutive threads on consecutive ROWS (optix_tracer/forward.cu:433).
-__device__ __forceinline__ long long ray_of_thread(int H, int W, bool tiled) {
-    if (!tiled) {
-        const long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-        return r < (long long)H * W ? r : -1;
-    }
-    const int tiles_x = (W + 15) >> 4;
-    const int bx = blockIdx.x % tiles_x, by = blockIdx.x / tiles_x;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int x = bx * 16 + (warp & 1) * 8 + (lane & 7);
-    const int y = by * 8 + (warp >> 1) * 4 + (lane >> 3);
-    if (x >= W || y >= H) return -1;
-    return (long long)y * W + x;
-}
-
 // SH constants, optix_tracer/auxiliary.h:26-43
 #define SHC0 0.28209479177387814f
 #define SHC1 0.4886025119029199f
@@ -775,21 +758,44 @@ __device__ __forceinline__ int knearest_warp(const BvhView& bvh, float ox, float
     return n;
 }
 
-// list entry i of round 0 -> ray index (or -1): image-like grids are walked in 8x4 pixel tiles so
-// that the rays of a warp stay close in the hierarchy, batched ray lists linearly
+// List entry i of round 0 -> ray index (or -1). Image-like grids are walked in 8x4 pixel tiles (one tile = the 32
+// rays a warp of the gather kernel takes), and the tiles in Z order inside blocks of 8x8 tiles (64x32 pixels): any
+// aligned run of 2 or 4 consecutive tiles is a compact 16x4 or 16x8 pixel patch. That matters once rays have
+// dropped out: the lists keep this order, so a warp of a later round holds the survivors of a few consecutive
+// tiles, and the tighter the patch they come from, the tighter the hull of their rays. Batched ray lists (few rows)
+// are walked linearly.
+#ifndef DST_TILE_BLOCK
+#define DST_TILE_BLOCK 8              // tiles per side of a Z-ordered block (1: row-major tile order)
+#endif
 __device__ __forceinline__ int ray_of_slot(long long i, int H, int W, bool tiled) {
     if (!tiled) return i < (long long)H * W ? (int)i : -1;
     const int tiles_x = (W + 7) >> 3;
-    const long long tile = i >> 5;
+    long long tile = i >> 5;
     const int lane = (int)(i & 31);
-    const int x = (int)(tile % tiles_x) * 8 + (lane & 7);
-    const int y = (int)(tile / tiles_x) * 4 + (lane >> 3);
+    int tx, ty;
+    if (DST_TILE_BLOCK > 1) {
+        constexpr int BB = DST_TILE_BLOCK * DST_TILE_BLOCK;
+        const int blocks_x = (tiles_x + DST_TILE_BLOCK - 1) / DST_TILE_BLOCK;
+        const long long blk = tile / BB;
+        const unsigned int in = (unsigned int)(tile - blk * BB);
+        // Z order inside the block: even bits -> x, odd bits -> y
+        const unsigned int zx = (in & 1u) | ((in >> 1) & 2u) | ((in >> 2) & 4u), zy = ((in >> 1) & 1u) | ((in >> 2) & 2u) | ((in >> 3) & 4u);
+        tx = (int)(blk % blocks_x) * DST_TILE_BLOCK + (int)zx;
+        ty = (int)(blk / blocks_x) * DST_TILE_BLOCK + (int)zy;
+    } else { tx = (int)(tile % tiles_x); ty = (int)(tile / tiles_x); }
+    const int x = tx * 8 + (lane & 7);
+    const int y = ty * 4 + (lane >> 3);
     if (x >= W || y >= H) return -1;
     return y * W + x;
 }
 __host__ __device__ __forceinline__ long long slots_of_grid(int H, int W, bool tiled) {
     if (!tiled) return (long long)H * W;
-    return (long long)((W + 7) >> 3) * ((H + 3) >> 2) * 32;
+    const long long tiles_x = (W + 7) >> 3, tiles_y = (H + 3) >> 2;
+    if (DST_TILE_BLOCK > 1) {
+        const long long bx = (tiles_x + DST_TILE_BLOCK - 1) / DST_TILE_BLOCK, by = (tiles_y + DST_TILE_BLOCK - 1) / DST_TILE_BLOCK;
+        return bx * by * DST_TILE_BLOCK * DST_TILE_BLOCK * 32;
+    }
+    return tiles_x * tiles_y * 32;
 }
 
 // appends `ray` to the next round's list when `alive`; one atomic per warp, order kept within a warp

@@ -37,7 +37,9 @@ extern "C" {
 #define DST_STATUS_LOG_MISMATCH    8u   /* the chunk log ended before the backward of a ray did */
 
 #define DST_MID_CHANNELS 16             /* per-bounce record, optix_tracer/config.h:7-15       */
+#ifndef DST_CHUNK
 #define DST_CHUNK 16                    /* hits gathered per enumeration, config.h:20          */
+#endif
 
 typedef struct dst_handle dst_handle;
 
