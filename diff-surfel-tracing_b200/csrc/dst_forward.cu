@@ -106,6 +106,29 @@ __global__ void __launch_bounds__(256) k_prepare_cache(int P, const float* __res
     o[3] = make_float4(scales[2 * (size_t)g], scales[2 * (size_t)g + 1], 0.f, 0.f);
 }
 
+// a_weights[gidx] += w (optix_tracer/forward.cu:295), aggregated over the lanes of the warp that are here together.
+// The lanes of a warp are neighbouring pixels walking their chunks in step, and they composite the same surfels at the
+// same time: the lanes that hold the same surfel add their weights up with shuffles and one of them issues the atomic.
+// As one atomic per contribution this was 7 of the 16 ms the composite kernel takes on the 3M-surfel 1080p workload
+// (the L2 serialises additions to one address, and surfels near the camera are hit by thousands of rays).
+__device__ __forceinline__ void add_weight(float* __restrict__ a_weights, int gidx, float w) {
+    const unsigned int act = __activemask();
+    unsigned int peers = __match_any_sync(act, gidx);
+    const int lane = threadIdx.x & 31;
+    const int first = __ffs(peers) - 1;
+    int rel_pos = __popc(peers << (32 - lane)) * (lane != 0);        // my rank among the peers (a shift by 32 is undefined: lane 0 has rank 0)
+    peers &= (0xfffffffeu << lane);                                  // peers above me
+    while (__any_sync(act, peers != 0u)) {
+        const int next = __ffs(peers);
+        const float t = __shfl_sync(act, w, next ? next - 1 : lane);
+        if (next) w += t;
+        const bool done = rel_pos & 1;                               // my value was taken in this step
+        peers &= __ballot_sync(act, !done);
+        rel_pos >>= 1;
+    }
+    if (lane == first) atomicAdd(a_weights + gidx, w);
+}
+
 __device__ __forceinline__ void fwd_begin_segment(FwdState& s) {
     s.offset = 0.f; s.dpt = 0.f; s.T_prev = 1.f;
     s.C0 = s.C1 = s.C2 = 0.f; s.D = 0.f; s.Nx = s.Ny = s.Nz = 0.f; s.O0 = s.O1 = 0.f;
@@ -245,7 +268,7 @@ __device__ __forceinline__ bool fwd_shade(const FwdParams& p, int ray, FwdState&
         s.D = xadd(s.D, xmul(w, s.dpt));
         s.Nx = xadd(s.Nx, xmul(w, nsign * r2.x)); s.Ny = xadd(s.Ny, xmul(w, nsign * r2.y)); s.Nz = xadd(s.Nz, xmul(w, nsign * r2.z));
         s.T_prev = T_next;
-        if (p.a.training && p.a.a_weights) atomicAdd(p.a.a_weights + gidx, w);          // forward.cu:295
+        if (p.a.training && p.a.a_weights) add_weight(p.a.a_weights, gidx, w);          // forward.cu:295
         if (DIAG) {
             tc.contribs++;
             if (p.a.hit_log && s.hit_count < p.a.hit_cap) p.a.hit_log[(size_t)ray * p.a.hit_cap + s.hit_count] = pidx;
