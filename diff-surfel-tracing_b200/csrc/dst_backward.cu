@@ -109,6 +109,67 @@ __device__ __forceinline__ void bulk_stage_commit(BulkStage& b) {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     b.n++;
 }
+// Rows of the same surfel staged by several lanes of a warp are summed in shared memory before they leave, and only
+// the lowest lane of each group hands its (summed) row to the engine. The lanes of a warp are neighbouring pixels that
+// walk their chunk logs in step, so at one point of the loop most of them hold one of a handful of surfels; without the
+// summing every lane's row is an addition of its own at the L2, which serialises additions to one address (the
+// reductions were 11 of the backward's 26 ms on the 3M-surfel 1080p workload). The lanes that are here together split the
+// 17 float4 columns of a row between them and each sums its columns over the rows of a group, in lane order.
+// gidx < 0: this lane has no row. Returns true for the lanes that send their row.
+#ifndef DST_BWD_AGGREGATE
+#define DST_BWD_AGGREGATE 1
+#endif
+__device__ __forceinline__ bool bulk_stage_aggregate(const BulkStage& b, int gidx) {
+#if DST_BWD_AGGREGATE
+    const unsigned int act = __activemask();
+    const int lane = threadIdx.x & 31;
+    const unsigned int staged = __ballot_sync(act, gidx >= 0);           // lanes without a row pass -1 and form a group that is skipped
+    // Worth it only where neighbouring pixels do hold the same surfels: when fewer than three quarters of the rows have the
+    // surfel of the lane next door, every lane sends its own row (grouping costs more than it saves on scenes whose
+    // surfels are small against the pixel spacing).
+    const int next_door = __shfl_xor_sync(act, gidx, 1);
+    const unsigned int paired = __ballot_sync(act, gidx >= 0 && ((act >> (lane ^ 1)) & 1u) != 0u && next_door == gidx);
+    if (4 * __popc(paired) < 3 * __popc(staged)) return gidx >= 0;
+    const unsigned int peers = __match_any_sync(act, gidx);
+    const int first = __ffs(peers) - 1;
+    const unsigned int leaders = __ballot_sync(act, lane == first) & staged;
+    const unsigned int parity = __ballot_sync(act, (b.n & 1u) != 0u);
+    __syncwarp(act);                                                     // every lane's row is staged
+    if (leaders != staged) {                                              // some surfel is held by more than one lane
+        float* warp_rows = b.base - (size_t)lane * STAGE_FLOATS;         // buffer 0 of lane 0
+        const int rank = __popc(act & ((1u << lane) - 1u)), nact = __popc(act);
+        for (unsigned int todo = leaders; todo; todo &= todo - 1u) {
+            const int lead = __ffs(todo) - 1;
+            const unsigned int grp = __shfl_sync(act, peers, lead);
+            if ((grp & (grp - 1u)) == 0u) continue;                      // a lane alone with its surfel
+            for (int col = rank; col < STAGE_FLOATS / 4; col += nact) {
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (unsigned int q = grp; q;) {                         // four rows per pass, so that their loads are in flight together
+                    const int r0 = __ffs(q) - 1; q &= q - 1u;
+                    const int r1 = __ffs(q) - 1; q &= q - 1u;
+                    const int r2 = __ffs(q) - 1; q &= q - 1u;
+                    const int r3 = __ffs(q) - 1; q &= q - 1u;
+#define DST_STAGED(r) reinterpret_cast<const float4*>(warp_rows + ((r) + (int)((parity >> (r)) & 1u) * BWD_THREADS) * STAGE_FLOATS)[col]
+                    const float4 x0 = DST_STAGED(r0);
+                    const float4 x1 = r1 >= 0 ? DST_STAGED(r1) : zero;
+                    const float4 x2 = r2 >= 0 ? DST_STAGED(r2) : zero;
+                    const float4 x3 = r3 >= 0 ? DST_STAGED(r3) : zero;
+#undef DST_STAGED
+                    acc.x += (x0.x + x1.x) + (x2.x + x3.x); acc.y += (x0.y + x1.y) + (x2.y + x3.y);
+                    acc.z += (x0.z + x1.z) + (x2.z + x3.z); acc.w += (x0.w + x1.w) + (x2.w + x3.w);
+                }
+                reinterpret_cast<float4*>(warp_rows + (lead + (int)((parity >> lead) & 1u) * BWD_THREADS) * STAGE_FLOATS)[col] = acc;
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp(act);                                                 // the sums are in place
+    }
+    return lane == first && gidx >= 0;
+#else
+    return true;
+#endif
+}
 // before the kernel ends: every row has been read from shared memory and added
 __device__ __forceinline__ void bulk_stage_drain() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
@@ -317,10 +378,16 @@ __device__ __forceinline__ bool bwd_shade(const BwdParams& p, int ray, BwdState&
 
     bool stop = false;
     for (int sl = 0; sl < cnt; sl++) {
+        // One pass of the body per hit; a hit that does not contribute leaves it early. The lanes of the warp meet again
+        // behind it, where the rows of the lanes that did contribute are summed per surfel and sent.
+        bool staged = false;
+        int gsent = -1;
+        float4* st = nullptr;
+        do {
         const unsigned long long key = kb[sl * KS];
         const int pidx = (int)(unsigned int)key;
         const int gidx = pidx >> 1;
-        if (gidx == last_gidx) continue;
+        if (gidx == last_gidx) break;
         if (DIAG) tc.evals++;
 #if DST_BWD_PREFETCH
         // Everything this surfel may need is requested now, before the first dependent use: the shading record (inside
@@ -340,7 +407,7 @@ __device__ __forceinline__ bool bwd_shade(const BwdParams& p, int ray, BwdState&
         SlotEval e;
         const bool ok = eval_slot(key, offset, sox, soy, soz, sdx, sdy, sdz, min_depth, p.cache, gidx, e);
         dpt = e.dpt;
-        if (!ok) continue;
+        if (!ok) break;
         const float alpha = e.alpha;
         T_next = xmul(T_prev, xsub(1.0f, alpha));
         if (T_next < T_threshold) { stop = true; break; }
@@ -450,7 +517,9 @@ __device__ __forceinline__ bool bwd_shade(const BwdParams& p, int ray, BwdState&
         const float dq3 = 2.f * (qx * (dR0.z + dR2.x) + qy * (dR1.z + dR2.y) - 2.f * qz * (dR0.x + dR1.y) + qw * (dR0.y - dR1.x));
 
         // per-surfel accumulation (backward.cu:543, 557, 578, 610-626)
+#if !DST_BWD_BULK
         float* row = p.arena + (size_t)gidx * DST_ARENA_FLOATS;
+#endif
         const float hd = 0.5f * dpt;
         const float dc0 = t_rgb0 * w, dc1 = t_rgb1 * w, dc2 = t_rgb2 * w;
         const float m0c = dc0 * k0, m1c = dc1 * k1, m2c = dc2 * k2;
@@ -458,7 +527,7 @@ __device__ __forceinline__ bool bwd_shade(const BwdParams& p, int ray, BwdState&
         float* dsh = use_sh ? p.a.dL_dshs + 3 * (size_t)gidx * in.sh_coeffs : nullptr;
 #if DST_BWD_BULK
         {
-            float4* st = reinterpret_cast<float4*>(bulk_stage_row(stage));
+            st = reinterpret_cast<float4*>(bulk_stage_row(stage));
             st[0] = make_float4(dq0, dq1, dq2, dq3);
             st[1] = make_float4(dmean.x, dmean.y, dmean.z, dL_dopac);
             st[2] = make_float4(dmean.x * hd, dmean.y * hd, dmean.z * hd, 0.f);
@@ -476,10 +545,7 @@ __device__ __forceinline__ bool bwd_shade(const BwdParams& p, int ray, BwdState&
                     }
                 }
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the staged values become visible to the bulk copy engine
-            bulk_add(row, reinterpret_cast<const float*>(st), DST_ARENA_FLOATS * 4);
-            if (sh_bulk) bulk_add(dsh, reinterpret_cast<const float*>(st + DST_ARENA_FLOATS / 4), nf * 4);
-            bulk_stage_commit(stage);
+            staged = true; gsent = gidx;
             if (use_sh && !sh_bulk) {
                 if (dsh_aligned) {
 #pragma unroll
@@ -531,6 +597,17 @@ __device__ __forceinline__ bool bwd_shade(const BwdParams& p, int ray, BwdState&
             dir_gidx = gidx; dir_g0 = m0c; dir_g1 = m1c; dir_g2 = m2c;
         }
         T_prev = T_next;
+        } while (false);
+#if DST_BWD_BULK
+        if (bulk_stage_aggregate(stage, gsent) && staged) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the staged values become visible to the bulk copy engine
+            bulk_add(p.arena + (size_t)gsent * DST_ARENA_FLOATS, reinterpret_cast<const float*>(st), DST_ARENA_FLOATS * 4);
+            if (use_sh && dsh_aligned && ((3 * ncoef) & 3) == 0)
+                bulk_add(p.a.dL_dshs + 3 * (size_t)gsent * in.sh_coeffs, reinterpret_cast<const float*>(st + DST_ARENA_FLOATS / 4), 3 * ncoef * 4);
+            bulk_stage_commit(stage);
+        }
+#endif
+        if (stop) break;
     }
     s.C0 = C0; s.C1 = C1; s.C2 = C2; s.D = D; s.O0 = O0; s.O1 = O1; s.Nx = N.x; s.Ny = N.y; s.Nz = N.z;
     s.T_prev = T_prev; s.dpt = dpt; s.last_gidx = last_gidx; s.contributor = contributor;
@@ -663,26 +740,38 @@ __global__ void __launch_bounds__(BWD_THREADS, DST_BWD_LOGGED_BLOCKS) k_bwd_logg
     TraceCounters tc = { 0, 0, 0, 0, 0, 0 };
     extern __shared__ __align__(128) unsigned char dyn_smem[];
     BulkStage stage = bulk_stage_init(dyn_smem);
-    bool requeue = false;
-    if (ray >= 0) {
-        BwdState s;
-        if (bwd_init_state(p, ray, s)) {
-            if (!p.log_ray_ok[ray]) {
-                bwd_store_state(p.state, ray, s);
-                EnumReq q;
-                bwd_request(s, q);
-                p.req[ray] = q;
-                requeue = true;
-            } else {
-                const int* heads = p.log_seg_head + (size_t)ray * p.log_seg_stride;
-                int idx = heads[s.seg];
-                for (;;) {
-                    if (idx < 0) { atomicOr(p.status, DST_STATUS_LOG_MISMATCH); break; }
-                    const int2 hdr = __ldg(p.log_hdr + idx);
-                    if (DIAG) tc.enums++;
-                    if (!bwd_shade<DIAG, 1, DIST>(p, ray, s, p.log_keys + (size_t)idx * DST_CHUNK, hdr.y, tc, stage)) break;
-                    idx = (s.chunk == 0) ? heads[s.seg] : hdr.x;      // chunk == 0: an earlier segment has begun
-                }
+    bool requeue = false, active = false;
+    BwdState s;
+    s.seg = -1;
+    const int* heads = nullptr;
+    int idx = -1;
+    if (ray >= 0 && bwd_init_state(p, ray, s)) {
+        if (!p.log_ray_ok[ray]) {
+            bwd_store_state(p.state, ray, s);
+            EnumReq q;
+            bwd_request(s, q);
+            p.req[ray] = q;
+            requeue = true;
+        } else {
+            heads = p.log_seg_head + (size_t)ray * p.log_seg_stride;
+            idx = heads[s.seg];
+            active = true;
+        }
+    }
+    // The warp walks its rays' chunk chains in step: one chunk per pass, and only the lanes whose ray is in the
+    // latest segment still open in the warp (the backward visits a ray's segments last to first). Neighbouring pixels then
+    // composite the same surfels in the same pass of the hit loop, which is what bulk_stage_aggregate() feeds on, and
+    // the lanes run one instruction stream instead of drifting apart chunk by chunk.
+    for (;;) {
+        const int cur = __reduce_max_sync(0xffffffffu, active ? s.seg : -1);
+        if (cur < 0) break;
+        if (active && s.seg == cur) {
+            if (idx < 0) { atomicOr(p.status, DST_STATUS_LOG_MISMATCH); active = false; }
+            else {
+                const int2 hdr = __ldg(p.log_hdr + idx);
+                if (DIAG) tc.enums++;
+                if (!bwd_shade<DIAG, 1, DIST>(p, ray, s, p.log_keys + (size_t)idx * DST_CHUNK, hdr.y, tc, stage)) active = false;
+                else idx = (s.chunk == 0) ? heads[s.seg] : hdr.x;      // chunk == 0: an earlier segment has begun
             }
         }
     }
