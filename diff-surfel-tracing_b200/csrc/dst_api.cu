@@ -111,6 +111,10 @@ int dst_destroy(dst_handle* h) {
     cudaFree(h->log_keys); cudaFree(h->log_hdr); cudaFree(h->log_count); cudaFree(h->log_seg_head); cudaFree(h->log_ray_ok);
     cudaFree(h->wf_state); cudaFree(h->wf_req); cudaFree(h->wf_kbuf); cudaFree(h->wf_kcnt); cudaFree(h->wf_list[0]); cudaFree(h->wf_list[1]); cudaFree(h->wf_counts);
     cudaFree(h->wf_tmp); cudaFree(h->wf_wcnt); cudaFree(h->wf_bcnt);
+    if (h->slice_streams_ready) {
+        cudaEventDestroy(h->slice_fork);
+        for (int g = 0; g < DST_MAX_SLICES - 1; g++) { cudaStreamDestroy(h->slice_stream[g]); cudaEventDestroy(h->slice_join[g]); }
+    }
     for (int k = 0; k < 4; k++) {
         if (h->ev[k]) { for (int i = 0; i < 2 * DST_PROF_SLOTS; i++) cudaEventDestroy(h->ev[k][i]); delete[] h->ev[k]; }
     }
@@ -225,6 +229,7 @@ int dst_set_option(dst_handle* h, int option, int64_t value) {
         case DST_OPT_SINGLE_KERNEL_REFIT: h->single_kernel_refit = value != 0; return DST_OK;
         case DST_OPT_DISTORTION: h->distortion = value != 0; return DST_OK;
         case DST_OPT_STABLE_LISTS: h->stable_lists = value != 0; return DST_OK;
+        case DST_OPT_FORWARD_SLICES: h->fwd_slices = value < 0 ? 0 : (value > DST_MAX_SLICES ? DST_MAX_SLICES : (int)value); return DST_OK;
         case DST_OPT_CHUNK_LOG: h->log_enabled = value != 0; if (!h->log_enabled) h->log_serial = 0; return DST_OK;
         default: return dst_set_error(h, DST_E_ARG, "unknown option %d", option);
     }
@@ -284,9 +289,13 @@ int dst_debug_round_counts(dst_handle* h, int32_t* counts, int32_t cap, void* st
     if (!h->wf_counts) return dst_set_error(h, DST_E_STATE, "no trace call has run on this handle");
     DeviceGuard g(h->device);
     const int n = cap < 50 ? cap : 50;      // DST_WF_ROUNDS + 2 list lengths
-    DST_CUDA_TRY(h, cudaMemcpyAsync(counts, h->wf_counts, 4 * (size_t)n, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    // one set of counters per slice of the last forward call (one set for every other call): the lengths add up
+    int32_t all[DST_MAX_SLICES * 100];
+    const int sets = h->slices_used > 1 ? h->slices_used : 1;
+    DST_CUDA_TRY(h, cudaMemcpyAsync(all, h->wf_counts, sizeof(int32_t) * 100 * (size_t)sets, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     DST_CUDA_TRY(h, cudaStreamSynchronize((cudaStream_t)stream));
-    for (int i = n; i < cap; i++) counts[i] = 0;
+    for (int i = 0; i < cap; i++) counts[i] = 0;
+    for (int g = 0; g < sets; g++) for (int i = 0; i < n; i++) counts[i] += all[g * 100 + i];
     return DST_OK;
 }
 

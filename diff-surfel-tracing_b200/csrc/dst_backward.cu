@@ -862,6 +862,7 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
     p.log_keys = h->log_keys; p.log_hdr = h->log_hdr; p.log_seg_head = h->log_seg_head; p.log_ray_ok = h->log_ray_ok;
     p.log_seg_stride = a->in.max_trace_depth + 1;
     DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 2 * (DST_WF_ROUNDS + 2), st));
+    h->slices_used = 1;
     const bool wave = slots >= h->wf_min_rays;
     rc = dst_live_lists(h, slots, &p.lv, st);
     if (rc != DST_OK) return rc;

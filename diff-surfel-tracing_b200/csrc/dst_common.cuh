@@ -52,6 +52,7 @@ struct SurfelCacheView { const float4* rec; };
 #define DST_ARENA_FLOATS 20
 #define DST_LOG_MAX_RECORDS (320ll << 20)     // 136 B each: at most 43.5 GB of chunk log
 
+#define DST_MAX_SLICES 8
 struct dst_handle {
     int device;
     char err[512];
@@ -86,6 +87,13 @@ struct dst_handle {
     int distortion;               // 1: the depth-distortion output and its gradient are computed (default 0: zeros, as the reference)
     int stable_lists;             // 1 (default): live lists keep their order from round to round; 0: survivors are appended per warp
     long long wf_min_rays;        // launches with fewer rays skip the wavefront rounds
+    // Slices of the forward wavefront: the ray slots of a large call are cut into up to DST_MAX_SLICES contiguous ranges
+    // whose rounds run on streams of their own (slice 0 on the caller's), so that the stragglers of one slice's round
+    // overlap with the other slices' work. fwd_slices: 0 = chosen from the ray count, n = at most n.
+    int fwd_slices, slices_used;
+    cudaStream_t slice_stream[DST_MAX_SLICES - 1];
+    cudaEvent_t slice_fork, slice_join[DST_MAX_SLICES - 1];
+    bool slice_streams_ready;
     // chunk log: the 16-hit chunks every ray composited in the last training forward, chained per ray and segment,
     // so that the backward re-composites them without walking the hierarchy again
     unsigned long long* log_keys; int2* log_hdr; int* log_count; int* log_seg_head; unsigned char* log_ray_ok;

@@ -20,6 +20,12 @@
 #ifndef DST_WARP_TAIL_MAX_RAYS
 #define DST_WARP_TAIL_MAX_RAYS 32768   // up to this many rays the tail kernel runs one warp per ray
 #endif
+#ifndef DST_FWD_SLICES
+#define DST_FWD_SLICES 4               // slices of a large forward call (see forward_common)
+#endif
+#ifndef DST_SLICE_MIN_SLOTS
+#define DST_SLICE_MIN_SLOTS 262144     // a slice is at least this many ray slots
+#endif
 #ifndef DST_SHADE_GRID_PER_SM
 #define DST_SHADE_GRID_PER_SM 4        // what fits an SM at once at 128 registers (measured: 8 is 2.5 % slower on the headline workload)
 #endif
@@ -49,6 +55,7 @@ struct FwdParams {
     const float4* cache;
     unsigned int* status;
     int tiled, grid_h, grid_w;      // ray order: 8x4 tiles over a grid_h x grid_w pixel grid, or linear
+    long long slot0;                // first ray slot of the slice these lists belong to (see forward_common)
     // wavefront scratch
     void* state;
     EnumReq* req;
@@ -354,7 +361,7 @@ __global__ void __launch_bounds__(256) k_fwd_init(const __grid_constant__ FwdPar
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= slots) return;
     if (i == 0) p.counts[0] = (int)slots;
-    const int ray = ray_of_slot(i, p.grid_h, p.grid_w, p.tiled != 0);
+    const int ray = ray_of_slot(p.slot0 + i, p.grid_h, p.grid_w, p.tiled != 0);
     p.list[0][i] = ray;
     if (ray < 0) return;
     FwdState s;
@@ -540,7 +547,7 @@ int dst_ensure_wavefront(dst_handle* h, long long slots, size_t state_bytes) {
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_kcnt, 4 * (size_t)cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_list[0], 4 * (size_t)cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_list[1], 4 * (size_t)cap);
-    if (e == cudaSuccess) e = cudaMalloc(&h->wf_counts, 4 * 2 * (DST_WF_ROUNDS + 2));
+    if (e == cudaSuccess) e = cudaMalloc(&h->wf_counts, 4 * (size_t)DST_COUNTS_STRIDE * DST_MAX_SLICES);
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_tmp, 4 * (size_t)(cap + 32));
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_wcnt, 4 * (size_t)(cap / 32 + 2));
     if (e == cudaSuccess) e = cudaMalloc(&h->wf_bcnt, 4 * 2 * (size_t)dst_live_blocks(cap));
@@ -668,6 +675,7 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
     FwdParams p;
     p.a = *a; p.bvh = dst_bvh_view(h); p.cache = h->cache; p.status = h->status;
     p.cam_on = cam != nullptr;
+    p.slot0 = 0;
     p.dist_on = h->distortion;
     if (cam) camera_constants(cam, &p.cam); else memset(&p.cam, 0, sizeof(p.cam));
     dst_slot_grid(h, &a->in, &p.grid_h, &p.grid_w);
@@ -697,20 +705,44 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
     // small launches go straight to the per-ray kernel; large ones run wavefront rounds until few rays are left
     const bool wave = slots >= h->wf_min_rays;
     p.rounds = wave ? DST_WF_ROUNDS : 0;
-    {
-        long long hand_over = slots / DST_TAIL_DIV > DST_TAIL_MIN ? slots / DST_TAIL_DIV : DST_TAIL_MIN;
-        if (hand_over > DST_WARP_TAIL_MAX_RAYS) hand_over = DST_WARP_TAIL_MAX_RAYS;       // what the warp-per-ray tail takes
-        p.min_count = wave ? (int)hand_over : 1;
+    // Slices. A round ends when its slowest batch of 32 rays does, and on scenes with reflections a few batches take ten
+    // times the mean: measured on the 3M-surfel 1080p workload the gather kernels kept the SMs 30-80 % busy, the later
+    // rounds least. So a large call is cut into contiguous ranges of ray slots whose rounds are independent (own lists,
+    // counters and cursors; ray-indexed scratch is shared) and run on streams of their own: while one slice waits for its
+    // stragglers the blocks of the next slice's kernel take the free SMs. Per-launch timing (profile level 2) keeps one slice.
+    int nsl = 1;
+    if (wave && h->profiling < 2) {
+        nsl = h->fwd_slices > 0 ? h->fwd_slices : DST_FWD_SLICES;
+        if (nsl > DST_MAX_SLICES) nsl = DST_MAX_SLICES;
+        while (nsl > 1 && slots / nsl < DST_SLICE_MIN_SLOTS) nsl--;
     }
+    if (nsl > 1 && !h->slice_streams_ready) {
+        bool ok = cudaEventCreateWithFlags(&h->slice_fork, cudaEventDisableTiming) == cudaSuccess;
+        for (int g = 0; g < DST_MAX_SLICES - 1 && ok; g++) {
+            ok = cudaStreamCreateWithFlags(&h->slice_stream[g], cudaStreamNonBlocking) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&h->slice_join[g], cudaEventDisableTiming) == cudaSuccess;
+        }
+        if (!ok) { cudaGetLastError(); return dst_set_error(h, DST_E_CUDA, "creating the streams of the forward slices failed"); }
+        h->slice_streams_ready = true;
+    }
+    h->slices_used = nsl;
+    long long hand_over = slots / DST_TAIL_DIV > DST_TAIL_MIN ? slots / DST_TAIL_DIV : DST_TAIL_MIN;
+    if (hand_over > DST_WARP_TAIL_MAX_RAYS) hand_over = DST_WARP_TAIL_MAX_RAYS;       // what the warp-per-ray tail takes
+    if (nsl > 1) { hand_over /= nsl; if (hand_over < 1024) hand_over = 1024; }
+    p.min_count = wave ? (int)hand_over : 1;
     // Rounds are enqueued without knowing how many the rays will need; a round on an exhausted list costs a few
     // microseconds per kernel. The list lengths of the previous forward of the same shape (read back without
     // synchronising) say how many were used: enqueue that many plus a margin. Scheduling only: rays that need more
     // are finished by the tail kernel, and the next call sees the longer history.
-    const long long sig = dst_call_signature(&a->in);
+    const long long sig = dst_call_signature(&a->in) * 16 + nsl;
     if (wave) {
         if (h->rounds_host && h->rounds_event && cudaEventQuery(h->rounds_event) == cudaSuccess) {
             int used = 0;
-            while (used < DST_WF_ROUNDS && h->rounds_host[used] >= h->rounds_pending_min) used++;
+            for (int g = 0; g < DST_MAX_SLICES; g++) {
+                int u = 0;
+                while (u < DST_WF_ROUNDS && h->rounds_host[g * DST_COUNTS_STRIDE + u] >= h->rounds_pending_min) u++;
+                if (u > used) used = u;
+            }
             h->rounds_known = used; h->rounds_known_sig = h->rounds_pending_sig;
         } else cudaGetLastError();
         if (h->rounds_known > 0 && h->rounds_known_sig == sig) {
@@ -719,45 +751,79 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
         }
     }
     const bool diag = a->hit_log || a->hit_cnt || a->counters;
-    DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * 2 * (DST_WF_ROUNDS + 2), st));
+    DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * (size_t)DST_COUNTS_STRIDE * DST_MAX_SLICES, st));
     rc = dst_live_lists(h, slots, &p.lv, st);
     if (rc != DST_OK) return rc;
-    const int g_compact = (int)((slots + DST_LIVE_BLOCK - 1) / DST_LIVE_BLOCK);
     dst_prof_mark(h, 1, 0, st);
-    k_fwd_init<<<(unsigned int)((slots + 255) / 256), 256, 0, st>>>(p, slots);
-    const int g_enum = dst_wavefront_grid(h, slots, ENUM_THREADS, DST_ENUM_GRID_PER_SM), g_shade = dst_wavefront_grid(h, slots, SHADE_THREADS, DST_SHADE_GRID_PER_SM);
+    // the slices: ranges of whole list blocks, each with its own view of the lists and counters
+    FwdParams ps[DST_MAX_SLICES];
+    cudaStream_t sst[DST_MAX_SLICES];
+    long long sslots[DST_MAX_SLICES];
+    {
+        const long long blocks_total = (slots + DST_LIVE_BLOCK - 1) / DST_LIVE_BLOCK;
+        for (int g = 0; g < nsl; g++) {
+            const long long b0 = blocks_total * g / nsl, b1 = blocks_total * (g + 1) / nsl;
+            const long long s0 = b0 * DST_LIVE_BLOCK, s1 = g == nsl - 1 ? slots : b1 * DST_LIVE_BLOCK;
+            FwdParams& q = ps[g];
+            q = p;
+            q.slot0 = s0;
+            q.list[0] = p.list[0] + s0; q.list[1] = p.list[1] + s0;
+            q.counts = p.counts + (size_t)g * DST_COUNTS_STRIDE;
+            q.lv.tmp = p.lv.tmp + s0; q.lv.wcnt = p.lv.wcnt + s0 / 32;
+            q.lv.bcnt[0] = p.lv.bcnt[0] + b0; q.lv.bcnt[1] = p.lv.bcnt[1] + b0;
+            sslots[g] = s1 - s0;
+            sst[g] = g == 0 ? st : h->slice_stream[g - 1];
+        }
+    }
+    if (nsl > 1) {
+        DST_CUDA_TRY(h, cudaEventRecord(h->slice_fork, st));
+        for (int g = 1; g < nsl; g++) DST_CUDA_TRY(h, cudaStreamWaitEvent(sst[g], h->slice_fork, 0));
+    }
+    for (int g = 0; g < nsl; g++) k_fwd_init<<<(unsigned int)((sslots[g] + 255) / 256), 256, 0, sst[g]>>>(ps[g], sslots[g]);
     for (int r = 0; r < p.rounds; r++) {
-        dst_prof_mark(h, 3, 0, st);
-        launch_gather(diag, g_enum, st, p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt,
-                      p.status, a->counters, r + 1);
-        dst_prof_mark(h, 3, 1, st);
-        if (diag) k_fwd_shade<true><<<g_shade, SHADE_THREADS, 0, st>>>(p, r);
-        else k_fwd_shade<false><<<g_shade, SHADE_THREADS, 0, st>>>(p, r);
-        if (p.lv.stable) k_compact<<<g_compact, 256, 0, st>>>(p.lv, p.counts + r, p.counts + r + 1, p.min_count, p.list[(r + 1) & 1], r);
+        for (int g = 0; g < nsl; g++) {
+            const FwdParams& q = ps[g];
+            const int g_enum = dst_wavefront_grid(h, sslots[g], ENUM_THREADS, DST_ENUM_GRID_PER_SM), g_shade = dst_wavefront_grid(h, sslots[g], SHADE_THREADS, DST_SHADE_GRID_PER_SM);
+            const int g_compact = (int)((sslots[g] + DST_LIVE_BLOCK - 1) / DST_LIVE_BLOCK);
+            dst_prof_mark(h, 3, 0, sst[g]);
+            launch_gather(diag, g_enum, sst[g], q.bvh, q.req, q.list[r & 1], q.counts + r, q.counts + DST_WF_ROUNDS + 2 + r, q.min_count, q.kbuf, q.kcnt,
+                          q.status, a->counters, r + 1);
+            dst_prof_mark(h, 3, 1, sst[g]);
+            if (diag) k_fwd_shade<true><<<g_shade, SHADE_THREADS, 0, sst[g]>>>(q, r);
+            else k_fwd_shade<false><<<g_shade, SHADE_THREADS, 0, sst[g]>>>(q, r);
+            if (q.lv.stable) k_compact<<<g_compact, 256, 0, sst[g]>>>(q.lv, q.counts + r, q.counts + r + 1, q.min_count, q.list[(r + 1) & 1], r);
+        }
     }
     // few rays left (or a small call): one warp per ray; many: one thread per ray
-    const long long tail_rays = wave ? p.min_count : slots;
-    if (tail_rays <= DST_WARP_TAIL_MAX_RAYS) {
-        const int g_wtail = dst_wavefront_grid(h, tail_rays * 32, WTAIL_THREADS, 16);
-        if (diag) k_fwd_tail_warp<true><<<g_wtail, WTAIL_THREADS, 0, st>>>(p);
-        else k_fwd_tail_warp<false><<<g_wtail, WTAIL_THREADS, 0, st>>>(p);
-    } else {
-        const int g_tail = dst_wavefront_grid(h, tail_rays, TAIL_THREADS, 8);
-        if (diag) k_fwd_tail<false, true><<<g_tail, TAIL_THREADS, 0, st>>>(p);
-        else k_fwd_tail<false, false><<<g_tail, TAIL_THREADS, 0, st>>>(p);
+    for (int g = 0; g < nsl; g++) {
+        const FwdParams& q = ps[g];
+        const long long tail_rays = wave ? q.min_count : sslots[g];
+        if (tail_rays <= DST_WARP_TAIL_MAX_RAYS) {
+            const int g_wtail = dst_wavefront_grid(h, tail_rays * 32, WTAIL_THREADS, 16);
+            if (diag) k_fwd_tail_warp<true><<<g_wtail, WTAIL_THREADS, 0, sst[g]>>>(q);
+            else k_fwd_tail_warp<false><<<g_wtail, WTAIL_THREADS, 0, sst[g]>>>(q);
+        } else {
+            const int g_tail = dst_wavefront_grid(h, tail_rays, TAIL_THREADS, 8);
+            if (diag) k_fwd_tail<false, true><<<g_tail, TAIL_THREADS, 0, sst[g]>>>(q);
+            else k_fwd_tail<false, false><<<g_tail, TAIL_THREADS, 0, sst[g]>>>(q);
+        }
+    }
+    for (int g = 1; g < nsl; g++) {
+        DST_CUDA_TRY(h, cudaEventRecord(h->slice_join[g - 1], sst[g]));
+        DST_CUDA_TRY(h, cudaStreamWaitEvent(st, h->slice_join[g - 1], 0));
     }
     dst_prof_mark(h, 1, 1, st);
     DST_CUDA_TRY(h, cudaGetLastError());
-    h->launches += 2 + (p.lv.stable ? 3 : 2) * p.rounds;       // ray init, the rounds, tail
+    h->launches += (long long)nsl * (2 + (p.lv.stable ? 3 : 2) * p.rounds);       // per slice: ray init, the rounds, tail
     if (wave) {
         if (!h->rounds_host) {
-            if (cudaMallocHost(&h->rounds_host, 4 * (DST_WF_ROUNDS + 2)) != cudaSuccess) { cudaGetLastError(); h->rounds_host = nullptr; }
+            if (cudaMallocHost(&h->rounds_host, 4 * (size_t)DST_COUNTS_STRIDE * DST_MAX_SLICES) != cudaSuccess) { cudaGetLastError(); h->rounds_host = nullptr; }
             if (h->rounds_host && cudaEventCreateWithFlags(&h->rounds_event, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); h->rounds_event = nullptr; }
         }
         if (h->rounds_host && h->rounds_event && cudaEventQuery(h->rounds_event) != cudaErrorNotReady) {
             // (a copy still in flight keeps the buffer: its event decides when the buffer may be read)
             cudaGetLastError();
-            cudaMemcpyAsync(h->rounds_host, h->wf_counts, 4 * (DST_WF_ROUNDS + 2), cudaMemcpyDeviceToHost, st);
+            cudaMemcpyAsync(h->rounds_host, h->wf_counts, 4 * (size_t)DST_COUNTS_STRIDE * DST_MAX_SLICES, cudaMemcpyDeviceToHost, st);
             cudaEventRecord(h->rounds_event, st);
             h->rounds_pending_sig = sig; h->rounds_pending_min = p.min_count;
         }
@@ -844,6 +910,7 @@ extern "C" int dst_forward_static(dst_handle* h, const dst_fwd_args* a, void* st
     FwdParams p;
     p.a = *a; p.bvh = dst_bvh_view(h); p.status = h->status; p.tiled = tiled; p.grid_h = a->in.H; p.grid_w = a->in.W;
     p.cam_on = 0; memset(&p.cam, 0, sizeof(p.cam));
+    p.slot0 = 0;
     p.dist_on = h->distortion;
     p.cache = reinterpret_cast<const float4*>(base + ST_OFF_CACHE);
     p.state = base + ST_OFF_STATE;

@@ -267,7 +267,11 @@ __device__ __forceinline__ bool eval_slot(unsigned long long key, float offset, 
 struct __align__(16) EnumReq { float ox, oy, oz, dx, dy, dz, kmax0, pad; };
 
 constexpr int ENUM_THREADS = 128;
+#ifndef DST_ENUM_MIN_BLOCKS
+#define DST_ENUM_MIN_BLOCKS 6         // resident blocks per SM the gather kernel is compiled for
+#endif
 #define DST_WF_ROUNDS 48
+#define DST_COUNTS_STRIDE (2 * (DST_WF_ROUNDS + 2))      // ints per set of round counters: list lengths, then batch cursors
 
 // Slab constants of one ray for the padded child-box test (see knearest()).
 struct RaySlab {
@@ -380,7 +384,7 @@ static __device__ unsigned long long g_round_stats[64][8];
 #define RSTAT(i, v) do { } while (0)
 #endif
 template <bool COUNT>
-__global__ void __launch_bounds__(ENUM_THREADS) k_enum(BvhView bvh, const EnumReq* __restrict__ req, const int* __restrict__ list,
+__global__ void __launch_bounds__(ENUM_THREADS, DST_ENUM_MIN_BLOCKS) k_enum(BvhView bvh, const EnumReq* __restrict__ req, const int* __restrict__ list,
                                                        const int* __restrict__ count_ptr, int* cursor, int min_count,
                                                        unsigned long long* __restrict__ kbuf, int* __restrict__ kcnt,
                                                        unsigned int* status, unsigned long long* counters, int tag) {

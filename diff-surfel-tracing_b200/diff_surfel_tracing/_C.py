@@ -198,6 +198,11 @@ class OptiXStateWrapper:
         warp by warp as they finish. Scheduling only."""
         _check(self, lib().dst_set_option(self.handle, 7, int(bool(on))))
 
+    def set_forward_slices(self, n):
+        """Large forward calls run as `n` independent slices of the ray grid on streams of their own (0: chosen from the
+        ray count, 1: no slicing). Scheduling only."""
+        _check(self, lib().dst_set_option(self.handle, 9, int(n)))
+
     def profile(self, on=True):
         """Records CUDA events around the build, forward and backward kernels of later calls; on=2 also around
         every launch of the gather kernel."""

@@ -241,6 +241,11 @@ int dst_bvh_info(const dst_handle* h, int64_t* surfels, int64_t* nodes, int64_t*
  * gradient. There is nothing upstream to compare this with: it is tested against a CPU restatement of the same formula
  * and against finite differences. */
 #define DST_OPT_DISTORTION 8
+/* Slices of a large forward call (results are not affected): the ray slots are cut into this many contiguous ranges
+ * whose wavefront rounds run on streams of their own, ordered after what the caller's stream held at the call and
+ * joined into it before the call returns, so that the slow last batches of one slice's round overlap with the other
+ * slices' work. 0 (default): 4 for calls of a million rays and more, fewer for smaller ones; 1: no slicing; at most 8. */
+#define DST_OPT_FORWARD_SLICES 9
 int dst_set_option(dst_handle* h, int option, int64_t value);
 
 /* Timing of the main kernels with CUDA events on the launching stream. While enabled, every
