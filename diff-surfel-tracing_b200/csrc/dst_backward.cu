@@ -888,7 +888,7 @@ int dst_backward_impl(dst_handle* h, const dst_bwd_args* a, cudaStream_t st) {
     for (int r = 0; r < p.rounds; r++) {
         dst_prof_mark(h, 3, 0, st);
         launch_gather(diag, g_enum, st, p.bvh, p.req, p.list[r & 1], p.counts + r, p.counts + DST_WF_ROUNDS + 2 + r, p.min_count, p.kbuf, p.kcnt,
-                      p.status, a->counters, r + 1);
+                      p.status, a->counters, r + 1, p.tiled != 0);
         dst_prof_mark(h, 3, 1, st);
         if (dist) { if (diag) k_bwd_shade<true, true><<<g_shade, BWD_THREADS, BWD_STAGE_BYTES, st>>>(p, r); else k_bwd_shade<false, true><<<g_shade, BWD_THREADS, BWD_STAGE_BYTES, st>>>(p, r); }
         else { if (diag) k_bwd_shade<true, false><<<g_shade, BWD_THREADS, BWD_STAGE_BYTES, st>>>(p, r); else k_bwd_shade<false, false><<<g_shade, BWD_THREADS, BWD_STAGE_BYTES, st>>>(p, r); }

@@ -787,7 +787,7 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
             const int g_compact = (int)((sslots[g] + DST_LIVE_BLOCK - 1) / DST_LIVE_BLOCK);
             dst_prof_mark(h, 3, 0, sst[g]);
             launch_gather(diag, g_enum, sst[g], q.bvh, q.req, q.list[r & 1], q.counts + r, q.counts + DST_WF_ROUNDS + 2 + r, q.min_count, q.kbuf, q.kcnt,
-                          q.status, a->counters, r + 1);
+                          q.status, a->counters, r + 1, q.tiled != 0);
             dst_prof_mark(h, 3, 1, sst[g]);
             if (diag) k_fwd_shade<true><<<g_shade, SHADE_THREADS, 0, sst[g]>>>(q, r);
             else k_fwd_shade<false><<<g_shade, SHADE_THREADS, 0, sst[g]>>>(q, r);

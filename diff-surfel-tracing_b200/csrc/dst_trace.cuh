@@ -8,8 +8,16 @@
 #define DST_MAX_CHUNKS 4096          // bound on enumerations per ray segment (the reference loops without one)
 #define DST_MAX_INTERSECTION 256     // optix_tracer/config.h:23
 #define DST_NODE_VOTE 10                // lanes with node work needed to stay in the node phase of k_enum
-#ifndef DST_SHARE_MIN_PCT
-#define DST_SHARE_MIN_PCT 25              // the warp gives up walking together when fewer than this % of the lane tests are wanted
+// The warp gives up walking together when fewer than this % of the lane tests are wanted. Pixel tiles: never. Measured on
+// tiled image grids (forward, 0 / 10 / 25 %): 3M-surfel reflective scene 61.6 / 62.7 / 67.1 ms, object-scale scene 9.0 / 10.7 /
+// 13.8 ms: even batches of reflected rays, whose directions have little in common, start from one small patch and find their
+// 16 nearest hits close to it. Linear ray lists (LiDAR sweeps: one origin, directions fanning out over metres of a sparse
+// scene) are the opposite case: 4.4 / 3.95 / 3.3 ms.
+#ifndef DST_SHARE_MIN_PCT_TILED
+#define DST_SHARE_MIN_PCT_TILED 0
+#endif
+#ifndef DST_SHARE_MIN_PCT_LINEAR
+#define DST_SHARE_MIN_PCT_LINEAR 25
 #endif
 #ifndef DST_SHARE_VOTE
 #define DST_SHARE_VOTE 1                // lanes that must want a subtree for the warp to walk it together (k_enum)
@@ -306,9 +314,9 @@ __device__ __forceinline__ RaySlab make_slab(float ox, float oy, float oz, float
 //                  A leaf run reached here is NOT tested quad by quad by every lane: lane q fetches quad q and
 //                  decides, against the hull of the batch's rays (hull_quad), whether any ray of the batch can hit
 //                  it; only the survivors (a few of 32 for neighbouring rays) are handed round and tested exactly
-//                  by every lane. When most lanes sit out most tests (after 64 nodes, under DST_SHARE_MIN_PCT % of
-//                  the lane x test slots wanted) the warp gives the shared walk up: every lane takes the pending
-//                  subtrees onto its own stack.
+//                  by every lane. For linear ray lists only: when most lanes sit out most tests (after 64 nodes, under
+//                  share_min_pct % of the lane x test slots wanted) the warp gives the shared walk up and every lane
+//                  takes the pending subtrees onto its own stack (see DST_SHARE_MIN_PCT_TILED above).
 //   private phase  every lane drains its own stack as in knearest(), lanes alternating between a node phase (kept
 //                  while at least DST_NODE_VOTE lanes have node work) and a leaf phase.
 // Pruning uses each lane's own 16th-nearest distance throughout and the hull test is conservative, so the hit set is
@@ -387,7 +395,7 @@ template <bool COUNT>
 __global__ void __launch_bounds__(ENUM_THREADS, DST_ENUM_MIN_BLOCKS) k_enum(BvhView bvh, const EnumReq* __restrict__ req, const int* __restrict__ list,
                                                        const int* __restrict__ count_ptr, int* cursor, int min_count,
                                                        unsigned long long* __restrict__ kbuf, int* __restrict__ kcnt,
-                                                       unsigned int* status, unsigned long long* counters, int tag) {
+                                                       unsigned int* status, unsigned long long* counters, int tag, int share_min_pct) {
     __shared__ unsigned long long kshared[DST_CHUNK * ENUM_THREADS];
     __shared__ int sstack[ENUM_THREADS / 32][DST_SHARED_STACK];
     __shared__ BeamQ sbeam[ENUM_THREADS / 32];
@@ -511,7 +519,7 @@ __global__ void __launch_bounds__(ENUM_THREADS, DST_ENUM_MIN_BLOCKS) k_enum(BvhV
         if (scur != DONE) {
             for (;;) {
                 if (__any_sync(FULL, sp >= DST_ENUM_DEFER)) break;     // drain the private stacks first, then come back to scur
-                if (s_tests >= 64 * 32 && s_wanted * 100 < s_tests * DST_SHARE_MIN_PCT && ssp + 1 <= DST_ENUM_STACK - DST_ENUM_DEFER - 40) {
+                if (s_tests >= 64 * 32 && s_wanted * 100 < s_tests * share_min_pct && ssp + 1 <= DST_ENUM_STACK - DST_ENUM_DEFER - 40) {
                     // these rays do not travel together (most lanes sit out most tests): every lane takes the
                     // pending subtrees onto its own stack and the batch continues lane by lane
                     if (active) {
@@ -636,9 +644,10 @@ __global__ void __launch_bounds__(ENUM_THREADS, DST_ENUM_MIN_BLOCKS) k_enum(BvhV
 // one gather launch of a wavefront round (diag: with traversal counters)
 static inline void launch_gather(bool diag, int grid, cudaStream_t st, const BvhView& bvh, const EnumReq* req, const int* list,
                                  const int* count_ptr, int* cursor, int min_count, unsigned long long* kbuf, int* kcnt, unsigned int* status,
-                                 unsigned long long* counters, int tag) {
-    if (diag) k_enum<true><<<grid, ENUM_THREADS, 0, st>>>(bvh, req, list, count_ptr, cursor, min_count, kbuf, kcnt, status, counters, tag);
-    else k_enum<false><<<grid, ENUM_THREADS, 0, st>>>(bvh, req, list, count_ptr, cursor, min_count, kbuf, kcnt, status, nullptr, tag);
+                                 unsigned long long* counters, int tag, bool tiled) {
+    const int share_min_pct = tiled ? DST_SHARE_MIN_PCT_TILED : DST_SHARE_MIN_PCT_LINEAR;
+    if (diag) k_enum<true><<<grid, ENUM_THREADS, 0, st>>>(bvh, req, list, count_ptr, cursor, min_count, kbuf, kcnt, status, counters, tag, share_min_pct);
+    else k_enum<false><<<grid, ENUM_THREADS, 0, st>>>(bvh, req, list, count_ptr, cursor, min_count, kbuf, kcnt, status, nullptr, tag, share_min_pct);
 }
 
 // The 16 nearest hits of ONE ray, found by a whole warp (same result as knearest()). For the few rays the

@@ -217,6 +217,33 @@ def test_list_order_does_not_change_results(C, config):
         assert hp.rel_l2(outs[0][1][k].cpu().numpy(), outs[1][1][k].cpu().numpy()) < 1e-4, k
 
 
+def test_forward_slices_do_not_change_results(C):
+    """A large forward call runs as up to four slices of the ray grid on streams of their own (scheduling only): the
+    outputs equal those of the unsliced call bit for bit, call after call, and the backward over the chunk log the
+    slices wrote together gives the same gradients."""
+    import workloads
+    wc = hp.to_cuda(workloads.make_workload(3, P=150000, H=1080, W=1024))
+    up = dict(rgb=torch.ones((1080, 1024, 3), device="cuda"))
+    ref_f = ref_g = None
+    for slices in (1, 4, 2, 4):
+        st = _build(C, wc)
+        st.set_forward_slices(slices)
+        for rep in range(3):
+            f = hp.cuda_forward(C, st, wc)
+            g = hp.cuda_backward(C, st, wc, f, up, serial=st.last_forward_serial)
+            torch.cuda.synchronize()
+            assert st.status() == 0
+            if ref_f is None:
+                ref_f, ref_g = f, g
+                continue
+            for k in ("rgb", "dpt", "acc", "norm", "aux", "mid"):
+                assert torch.equal(f[k], ref_f[k]), (slices, rep, k)
+            for k in ("ray_o", "ray_d"):
+                assert torch.equal(g[k], ref_g[k]), (slices, rep, k)
+            for k in ("means3D", "shs", "opacities", "scales", "rotations"):
+                assert hp.rel_l2(g[k].cpu().numpy(), ref_g[k].cpu().numpy()) < 1e-4, (slices, rep, k)
+
+
 def test_image_width_hint_does_not_change_results(C):
     """(B, h*w, 3) ray batches walked in pixel tiles (image width known) or in the order given: same bits."""
     wc = hp.to_cuda(hp.reduced_workload(5))               # 2 cameras of 54 x 96 pixels as a (2, 5184, 3) batch
