@@ -838,7 +838,7 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
         if (h->log_needed_host && h->log_needed_event) {
             cudaMemcpyAsync(h->log_needed_host, h->log_count, sizeof(int), cudaMemcpyDeviceToHost, st);
             cudaEventRecord(h->log_needed_event, st);
-            h->log_pending_sig = sig;
+            h->log_pending_sig = dst_call_signature(&a->in);      // (the backward compares with the plain shape: slices are the forward's business)
         }
     }
     return DST_OK;
