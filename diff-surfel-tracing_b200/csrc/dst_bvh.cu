@@ -123,33 +123,34 @@ __global__ void __launch_bounds__(SORT_THREADS) k_sort_hist(const unsigned long 
     block_hist[threadIdx.x * nblocks + blockIdx.x] = sh[threadIdx.x];
 }
 
-// exclusive scan of `total` counters by one 1024-thread block
-__global__ void __launch_bounds__(1024) k_sort_scan(unsigned int* __restrict__ data, int total) {
-    __shared__ unsigned int warp_sum[32];
+// Exclusive scan of the per-block counts of ONE digit (block d of the grid takes digit d): block_hist[d][0..nblocks)
+// becomes the number of keys with digit d in the blocks before, and digit_total[d] their number in all blocks. The
+// scatter kernel adds the keys with smaller digits itself (a 256-entry scan every block repeats), so no block of any
+// kernel waits for another and no single block walks all 256 x nblocks counters.
+__global__ void __launch_bounds__(256) k_sort_scan(unsigned int* __restrict__ block_hist, int nblocks, unsigned int* __restrict__ digit_total) {
+    __shared__ unsigned int warp_sum[8];
     __shared__ unsigned int carry_s;
+    unsigned int* data = block_hist + (size_t)blockIdx.x * nblocks;
     if (threadIdx.x == 0) carry_s = 0;
     __syncthreads();
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    for (int base = 0; base < total; base += 1024) {
+    for (int base = 0; base < nblocks; base += 256) {
         const int idx = base + threadIdx.x;
-        unsigned int x = idx < total ? data[idx] : 0u, incl = x;
+        unsigned int x = idx < nblocks ? data[idx] : 0u, incl = x;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) { unsigned int y = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += y; }
         if (lane == 31) warp_sum[wid] = incl;
         __syncthreads();
-        if (wid == 0) {
-            unsigned int s = warp_sum[lane], si = s;
+        unsigned int before = 0;
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) { unsigned int y = __shfl_up_sync(0xffffffffu, si, o); if (lane >= o) si += y; }
-            warp_sum[lane] = si - s;
-        }
-        __syncthreads();
+        for (int k = 0; k < 8; k++) if (k < wid) before += warp_sum[k];
         const unsigned int carry = carry_s;
-        if (idx < total) data[idx] = carry + warp_sum[wid] + incl - x;
+        if (idx < nblocks) data[idx] = carry + before + incl - x;
         __syncthreads();
-        if (threadIdx.x == 1023) carry_s = carry + warp_sum[wid] + incl;
+        if (threadIdx.x == 255) carry_s = carry + before + incl;
         __syncthreads();
     }
+    if (threadIdx.x == 0) digit_total[blockIdx.x] = carry_s;
 }
 
 // stable scatter: warp w of a block owns 512 consecutive keys and ranks them 32 at a time
@@ -157,8 +158,24 @@ __global__ void __launch_bounds__(SORT_THREADS) k_sort_scatter(const unsigned lo
                                                                const unsigned int* __restrict__ vals_in,
                                                                unsigned long long* __restrict__ keys_out,
                                                                unsigned int* __restrict__ vals_out, int n, int shift,
-                                                               const unsigned int* __restrict__ block_offs, int nblocks) {
+                                                               const unsigned int* __restrict__ block_offs, int nblocks,
+                                                               const unsigned int* __restrict__ digit_total) {
     __shared__ unsigned int wc[SORT_WARPS][257];
+    __shared__ unsigned int digit_base[256];
+    __shared__ unsigned int dsum[SORT_WARPS];
+    {   // keys with a smaller digit, in all blocks: exclusive scan of the 256 digit totals
+        const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+        const unsigned int x = digit_total[threadIdx.x];
+        unsigned int incl = x;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { unsigned int y = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += y; }
+        if (lane == 31) dsum[w] = incl;
+        __syncthreads();
+        unsigned int before = 0;
+#pragma unroll
+        for (int k = 0; k < SORT_WARPS; k++) if (k < w) before += dsum[k];
+        digit_base[threadIdx.x] = before + incl - x;
+    }
     for (int i = threadIdx.x; i < SORT_WARPS * 257; i += SORT_THREADS) (&wc[0][0])[i] = 0;
     __syncthreads();
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
@@ -183,7 +200,7 @@ __global__ void __launch_bounds__(SORT_THREADS) k_sort_scatter(const unsigned lo
     __syncthreads();
     {
         const int d = threadIdx.x;     // SORT_THREADS == 256 digits
-        unsigned int sum = block_offs[d * nblocks + blockIdx.x];
+        unsigned int sum = digit_base[d] + block_offs[d * nblocks + blockIdx.x];
 #pragma unroll
         for (int ww = 0; ww < SORT_WARPS; ww++) { unsigned int c = wc[ww][d]; wc[ww][d] = sum; sum += c; }
     }
@@ -432,7 +449,7 @@ int ensure_capacity(dst_handle* h, int64_t P) {
     if (e == cudaSuccess) e = cudaMalloc(&h->keys_alt, 8 * cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->vals, 4 * cap);
     if (e == cudaSuccess) e = cudaMalloc(&h->vals_alt, 4 * cap);
-    if (e == cudaSuccess) e = cudaMalloc(&h->block_hist, 4 * 256 * nblocks);
+    if (e == cudaSuccess) e = cudaMalloc(&h->block_hist, 4 * 256 * (nblocks + 1));       // + the 256 digit totals
     if (e != cudaSuccess) {
         cudaGetLastError();
         return dst_set_error(h, DST_E_NOMEM, "device allocation for %lld surfels failed: %s", (long long)P, cudaGetErrorString(e));
@@ -493,8 +510,8 @@ int dst_bvh_build_impl(dst_handle* h, const float* v, int64_t P, int rebuild, cu
         for (int pass = 0; pass < 8; pass++) {
             const int shift = 8 * pass;
             k_sort_hist<<<nblocks, SORT_THREADS, 0, st>>>(kin, n, shift, h->block_hist, nblocks);
-            k_sort_scan<<<1, 1024, 0, st>>>(h->block_hist, 256 * nblocks);
-            k_sort_scatter<<<nblocks, SORT_THREADS, 0, st>>>(kin, vin, kout, vout, n, shift, h->block_hist, nblocks);
+            k_sort_scan<<<256, 256, 0, st>>>(h->block_hist, nblocks, h->block_hist + 256 * (size_t)nblocks);
+            k_sort_scatter<<<nblocks, SORT_THREADS, 0, st>>>(kin, vin, kout, vout, n, shift, h->block_hist, nblocks, h->block_hist + 256 * (size_t)nblocks);
             unsigned long long* tk = kin; kin = kout; kout = tk;
             unsigned int* tv = vin; vin = vout; vout = tv;
         }
