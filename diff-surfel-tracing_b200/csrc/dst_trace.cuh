@@ -472,7 +472,9 @@ __global__ void __launch_bounds__(ENUM_THREADS, DST_ENUM_MIN_BLOCKS) k_enum(BvhV
         if (lane == 0) base = atomicAdd(cursor, 32);
         base = __shfl_sync(FULL, base, 0);
         if (base >= total) break;
-        const int idx = base + lane;
+        // The list is taken from its end: rays on a reflected segment come last in it (k_compact) and their batches are
+        // the slow ones, so they start first and the cheap batches of primary rays fill the end of the round.
+        const int idx = (((total + 31) >> 5) - 1 - (base >> 5)) * 32 + lane;
         int ray = idx < total ? list[idx] : -1;
         bool active = false;
         // takes up `ray`: request, slab constants, empty k-buffer and stack
