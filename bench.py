@@ -142,7 +142,7 @@ def config_block(w, P, rays_per_gpu, world, scale_out=False):
     return {"workload": w["name"], "surfels": P, "rays_per_gpu": rays_per_gpu, "sh_degree": w["sh_degree"],
             "max_trace_depth": w["max_trace_depth"], "specular_threshold": w["specular_threshold"],
             "parallelism": (f"rows of 8 cameras dealt over {world} GPUs, hierarchy replicated and rebuilt every step, 1 all-reduce/step" if scale_out
-                            else f"one camera of a ring of 8 per GPU x{world}, hierarchy replicated, 1 all-reduce/step" if world > 1 else "1 GPU"),
+                            else f"one camera of a ring of 8 per GPU x{world}, 4-row blocks of every camera dealt over the GPUs, hierarchy replicated, 1 all-reduce/step" if world > 1 else "1 GPU"),
             "l2": "inputs larger than L2 (hierarchy + surfel records + SH rows > 126 MB), no flush"}
 
 
@@ -414,13 +414,23 @@ def main():
     # with N > 1 rank r traces camera r of the ring (weak scaling; the exchange step is what is added).
     scale_out = args.config == 5
     total_rays = w["ray_o"].shape[0] * w["ray_o"].shape[1]
+    dealt_width = None
     if scale_out and world > 1:
         import shard
         ro, rd = shard.shard_image_rows(w["ray_o"], w["ray_d"], world, rank, 1080, 1920)
         w = dict(w, ray_o=ro, ray_d=rd)
-    elif args.config == 3 and world > 1 and rank > 0:
-        ro, rd = workloads.pinhole_rays(w["ray_o"].shape[0], w["ray_o"].shape[1], 50.0, ring_camera(rank))
+    elif args.config == 3 and world > 1:
+        # weak scaling: the job is one camera of the ring per GPU (camera 0 is the N = 1 workload). The cameras' costs
+        # differ by up to a third, so a rank does not trace "its" camera: 4-row blocks of every camera are dealt round-robin
+        # over the ranks and every rank traces 1/N of each of the N images, one image's worth of rays in all.
+        import shard
+        ih, iw = w["ray_o"].shape[:2]
+        cams = [workloads.pinhole_rays(ih, iw, 50.0, ring_camera(c)) for c in range(world)]
+        ro = torch.stack([c[0].reshape(-1, 3) for c in cams]); rd = torch.stack([c[1].reshape(-1, 3) for c in cams])
+        total_rays = world * ih * iw
+        ro, rd = shard.shard_image_rows(ro, rd, world, rank, ih, iw)
         w = dict(w, ray_o=ro, ray_d=rd)
+        dealt_width = iw
     H, W = w["ray_o"].shape[:2]
     log(f"[rank {rank}] workload '{w['name']}' generated in {time.perf_counter() - t0:.1f} s")
     wc = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in w.items()}
@@ -431,6 +441,8 @@ def main():
     st.profile(1)
     if scale_out:
         st.set_image_width(1920)          # what SurfelTracingSettings.image_width tells the module API: 1080x1920 images
+    elif dealt_width:
+        st.set_image_width(dealt_width)
     # hierarchy: build (timed 3x) and refit (timed 3x)
     for _ in range(3):
         tracer.build_acceleration_structure(wc["v"], wc["f"], rebuild=True)
@@ -518,7 +530,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total = float(t.item())
     ms_step = ms_total / args.steps
-    job_rays = total_rays if scale_out else world * R
+    job_rays = total_rays if (scale_out or dealt_width) else world * R
     value = job_rays / (ms_step * 1e-3) / 1e6
     fwd_ms = prof["forward"][0] / max(prof["forward"][1], 1)
     bwd_ms = prof["backward"][0] / max(prof["backward"][1], 1)
@@ -547,7 +559,8 @@ def main():
         oth_l = wc["others_precomp"].clone().requires_grad_(True) if wc["others_precomp"] is not None else None
         g3d = torch.zeros_like(wc["means3D"], requires_grad=True)
         z = torch.zeros(1, device=dev)
-        ih, iw = (1080, 1920) if scale_out else (H, W)
+        # image size as the module API hears it: this rank's rows of every image when the rays were dealt out
+        ih, iw = (W // 1920, 1920) if scale_out else (W // dealt_width, dealt_width) if dealt_width else (H, W)
         settings = SurfelTracingSettings(ih, iw, 1.0, 1.0, wc["bg"], 1.0, z, z, w["sh_degree"], z, False, False,
                                          w["max_trace_depth"], w["specular_threshold"])
         tracer.train()
