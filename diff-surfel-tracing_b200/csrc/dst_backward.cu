@@ -16,9 +16,6 @@ namespace {
 #define DST_BWD_THREADS 128
 #endif
 constexpr int BWD_THREADS = DST_BWD_THREADS;
-#ifndef DST_BWD_PREFETCH
-#define DST_BWD_PREFETCH 1           // request all per-surfel data of a slot at once, before the first dependent use
-#endif
 #ifndef DST_BWD_LOGGED_BLOCKS
 #define DST_BWD_LOGGED_BLOCKS 1      // resident blocks per SM the logged backward is compiled for
 #endif
@@ -389,21 +386,6 @@ __device__ __forceinline__ bool bwd_shade(const BwdParams& p, int ray, BwdState&
         const int gidx = pidx >> 1;
         if (gidx == last_gidx) break;
         if (DIAG) tc.evals++;
-#if DST_BWD_PREFETCH
-        // Everything this surfel may need is requested now, before the first dependent use: the shading record (inside
-        // eval_slot), its colour row, auxiliaries, quad corners, mean and rotation. A slot that turns out not to contribute
-        // wastes the requests (mostly L2 hits); a contributing one waits for memory once instead of four times in a row.
-        float csh[48];
-        float pc0 = 0.f, pc1 = 0.f, pc2 = 0.f;
-        if (use_sh) load_sh_row(in.shs + 3 * (size_t)gidx * in.sh_coeffs, 3 * ncoef, sh_aligned, csh);
-        else { const float* cp = in.colors_precomp + 3 * (size_t)gidx; pc0 = __ldg(cp); pc1 = __ldg(cp + 1); pc2 = __ldg(cp + 2); }
-        float2 ax = make_float2(0.f, 0.f);
-        if (has_aux) ax = __ldg(reinterpret_cast<const float2*>(in.others_precomp) + gidx);
-        const float4* vq = reinterpret_cast<const float4*>(in.vertices + 12 * (size_t)gidx);
-        const float4 va = __ldg(vq), vb = __ldg(vq + 1), vc = __ldg(vq + 2);
-        const V3 pm = v3(__ldg(in.means3D + 3 * (size_t)gidx), __ldg(in.means3D + 3 * (size_t)gidx + 1), __ldg(in.means3D + 3 * (size_t)gidx + 2));
-        const float4 q = __ldg(reinterpret_cast<const float4*>(in.rotations) + gidx);
-#endif
         SlotEval e;
         const bool ok = eval_slot(key, offset, sox, soy, soz, sdx, sdy, sdz, min_depth, p.cache, gidx, e);
         dpt = e.dpt;
@@ -418,7 +400,6 @@ __device__ __forceinline__ bool bwd_shade(const BwdParams& p, int ray, BwdState&
         const float w = xmul(alpha, T_prev);
         const V3 normal = v3(e.nsign * e.r2.x, e.nsign * e.r2.y, e.nsign * e.r2.z);
         float c0, c1, c2, k0 = 1.f, k1 = 1.f, k2 = 1.f;       // colour and its clamp mask
-#if !DST_BWD_PREFETCH
         float csh[48];
         float pc0 = 0.f, pc1 = 0.f, pc2 = 0.f;
         if (use_sh) load_sh_row(in.shs + 3 * (size_t)gidx * in.sh_coeffs, 3 * ncoef, sh_aligned, csh);
@@ -429,7 +410,6 @@ __device__ __forceinline__ bool bwd_shade(const BwdParams& p, int ray, BwdState&
         const float4 va = __ldg(vq), vb = __ldg(vq + 1), vc = __ldg(vq + 2);
         const V3 pm = v3(__ldg(in.means3D + 3 * (size_t)gidx), __ldg(in.means3D + 3 * (size_t)gidx + 1), __ldg(in.means3D + 3 * (size_t)gidx + 2));
         const float4 q = __ldg(reinterpret_cast<const float4*>(in.rotations) + gidx);
-#endif
         if (use_sh) {
             c0 = sh_channel(ncoef, sb, csh, 0); c1 = sh_channel(ncoef, sb, csh, 1); c2 = sh_channel(ncoef, sb, csh, 2);
             k0 = c0 < 0.f ? 0.f : 1.f; k1 = c1 < 0.f ? 0.f : 1.f; k2 = c2 < 0.f ? 0.f : 1.f;
@@ -599,7 +579,7 @@ __device__ __forceinline__ bool bwd_shade(const BwdParams& p, int ray, BwdState&
         T_prev = T_next;
         } while (false);
 #if DST_BWD_BULK
-        if (bulk_stage_aggregate(stage, gsent) && staged) {
+        if ((p.tiled ? bulk_stage_aggregate(stage, gsent) : true) && staged) {       // linear ray lists: neighbours in the list are not neighbours on a surface
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the staged values become visible to the bulk copy engine
             bulk_add(p.arena + (size_t)gsent * DST_ARENA_FLOATS, reinterpret_cast<const float*>(st), DST_ARENA_FLOATS * 4);
             if (use_sh && dsh_aligned && ((3 * ncoef) & 3) == 0)

@@ -712,7 +712,7 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
     // stragglers the blocks of the next slice's kernel take the free SMs. Per-launch timing (profile level 2) keeps one slice.
     int nsl = 1;
     if (wave && h->profiling < 2) {
-        nsl = h->fwd_slices > 0 ? h->fwd_slices : DST_FWD_SLICES;
+        nsl = h->fwd_slices > 0 ? h->fwd_slices : (p.tiled ? DST_FWD_SLICES : 1);       // linear ray lists (a few short rounds) gain nothing
         if (nsl > DST_MAX_SLICES) nsl = DST_MAX_SLICES;
         while (nsl > 1 && slots / nsl < DST_SLICE_MIN_SLOTS) nsl--;
     }
