@@ -325,7 +325,7 @@ __device__ __forceinline__ RaySlab make_slab(float ox, float oy, float oz, float
 #define DST_ENUM_STACK 160       // private stack of k_enum: subtrees deferred by the shared walk + one depth-first descent
 #define DST_ENUM_DEFER 64        // the shared walk pauses to drain the private stacks when a lane holds this many entries
 // Hull of the rays of one batch (origins and directions, component by component), kept in shared memory per warp.
-struct BeamQ { float omin[3], omax[3], dmin[3], dmax[3]; };
+struct BeamQ { float omin[3], omax[3], dmin[3], dmax[3], dabs[3], dsum; };      // dabs: largest |d| per axis, dsum: their sum
 
 __device__ __forceinline__ unsigned int f2ord_q(float f) {
     const unsigned int u = __float_as_uint(f);
@@ -335,9 +335,10 @@ __device__ __forceinline__ float ord2f_q(unsigned int u) { return __uint_as_floa
 __device__ __forceinline__ float wmin_f(float v) { return ord2f_q(__reduce_min_sync(0xffffffffu, f2ord_q(v))); }
 __device__ __forceinline__ float wmax_f(float v) { return ord2f_q(__reduce_max_sync(0xffffffffu, f2ord_q(v))); }
 
+// [rl, rh] += c * [lo, hi]
 __device__ __forceinline__ void ivmul(float c, float lo, float hi, float& rl, float& rh) {
-    const float a = c * lo, b = c * hi;
-    rl += fminf(a, b); rh += fmaxf(a, b);
+    const bool pos = c >= 0.f;
+    rl = fmaf(c, pos ? lo : hi, rl); rh = fmaf(c, pos ? hi : lo, rh);
 }
 // Conservative test of one quad against the hull of a batch of rays, in interval arithmetic over the hull's origins
 // and directions: can ANY ray of the batch pass ray_quad() with a hit no farther than kmaxb? The steps are those of
@@ -349,20 +350,21 @@ __device__ __forceinline__ void ivmul(float c, float lo, float hi, float& rl, fl
 __device__ __forceinline__ bool hull_quad(const BeamQ& bm, const float4 qa, const float4 qb, const float4 qc, float kmaxb) {
     const float p0[3] = { qa.x, qa.y, qa.z }, nn[3] = { qa.w, qb.x, qb.y }, wu[3] = { qb.z, qb.w, qc.x }, wv[3] = { qc.y, qc.z, qc.w };
     float rl[3], rh[3];
-    float bl = 0.f, bh = 0.f, al = 0.f, ah = 0.f, scale = 0.f, dsum = 0.f;
+    float bl = 0.f, bh = 0.f, al = 0.f, ah = 0.f, scale = 0.f;
 #pragma unroll
     for (int a = 0; a < 3; a++) {
         rl[a] = p0[a] - bm.omax[a]; rh[a] = p0[a] - bm.omin[a];
         ivmul(nn[a], bm.dmin[a], bm.dmax[a], bl, bh);
         ivmul(nn[a], rl[a], rh[a], al, ah);
         scale = fmaxf(scale, fmaxf(fabsf(rl[a]), fabsf(rh[a])));
-        dsum += fmaxf(fabsf(bm.dmin[a]), fabsf(bm.dmax[a]));
     }
     const float nmag = fabsf(nn[0]) + fabsf(nn[1]) + fabsf(nn[2]);
-    const float eb = 4e-6f * nmag * dsum, ea = 12e-6f * nmag * scale;
+    const float eb = 4e-6f * nmag * bm.dsum, ea = 12e-6f * nmag * scale;
     bl -= eb; bh += eb; al -= ea; ah += ea;
-    if (!(bl > 0.f || bh < 0.f)) return true;               // some direction of the hull is parallel to the plane: no bound
-    const float t1 = al / bl, t2 = al / bh, t3 = ah / bl, t4 = ah / bh;
+    if (!(bl > 1e-30f || bh < -1e-30f)) return true;        // some direction of the hull is (all but) parallel to the plane: no bound
+    // quotients by approximate reciprocals (two units in the last place; the interval is widened by 1e-5 relative below)
+    const float ibl = __fdividef(1.0f, bl), ibh = __fdividef(1.0f, bh);
+    const float t1 = al * ibl, t2 = al * ibh, t3 = ah * ibl, t4 = ah * ibh;
     float tl = fminf(fminf(t1, t2), fminf(t3, t4)), th = fmaxf(fmaxf(t1, t2), fmaxf(t3, t4));
     tl -= 1e-5f * fabsf(tl) + 1e-30f; th += 1e-5f * fabsf(th) + 1e-30f;
     if (th < 0.f || tl > kmaxb) return false;
@@ -370,11 +372,11 @@ __device__ __forceinline__ bool hull_quad(const BeamQ& bm, const float4 qa, cons
     float ul = 0.f, uh = 0.f, vl = 0.f, vh = 0.f, hmag = 0.f;
 #pragma unroll
     for (int a = 0; a < 3; a++) {
-        const float c1 = tl * bm.dmin[a], c2 = tl * bm.dmax[a], c3 = th * bm.dmin[a], c4 = th * bm.dmax[a];
-        const float hl = fminf(fminf(c1, c2), fminf(c3, c4)) - rh[a], hh = fmaxf(fmaxf(c1, c2), fmaxf(c3, c4)) - rl[a];
+        // t in [tl, th] with 0 <= tl <= th, d in [dmin, dmax]: the smallest t d is at (tl, dmin) or (th, dmin), the largest at (th, dmax) or (tl, dmax)
+        const float hl = bm.dmin[a] * (bm.dmin[a] >= 0.f ? tl : th) - rh[a], hh = bm.dmax[a] * (bm.dmax[a] >= 0.f ? th : tl) - rl[a];
         ivmul(wu[a], hl, hh, ul, uh);
         ivmul(wv[a], hl, hh, vl, vh);
-        hmag = fmaxf(hmag, fmaxf(fabsf(hl), fabsf(hh)) + scale + th * fmaxf(fabsf(bm.dmin[a]), fabsf(bm.dmax[a])));
+        hmag = fmaxf(hmag, fmaxf(fabsf(hl), fabsf(hh)) + scale + th * bm.dabs[a]);
     }
     // u and v are of order 1; their rounding error is that of h (cancellation of t d against p0 - o) times |w|
     const float eu = 1e-5f + 8e-6f * hmag * (fabsf(wu[0]) + fabsf(wu[1]) + fabsf(wu[2]));
@@ -510,18 +512,21 @@ __global__ void __launch_bounds__(ENUM_THREADS, DST_ENUM_MIN_BLOCKS) k_enum(BvhV
             for (int a = 0; a < 3; a++) {
                 const float lo = wmin_f(active ? o3[a] : INFINITY), hi = wmax_f(active ? o3[a] : -INFINITY);
                 const float dl = wmin_f(active ? d3[a] : INFINITY), dh = wmax_f(active ? d3[a] : -INFINITY);
-                if (lane == 0) { sbeam[wid].omin[a] = lo; sbeam[wid].omax[a] = hi; sbeam[wid].dmin[a] = dl; sbeam[wid].dmax[a] = dh; }
+                if (lane == 0) { sbeam[wid].omin[a] = lo; sbeam[wid].omax[a] = hi; sbeam[wid].dmin[a] = dl; sbeam[wid].dmax[a] = dh; sbeam[wid].dabs[a] = fmaxf(fabsf(dl), fabsf(dh)); }
             }
+            __syncwarp();
+            if (lane == 0) sbeam[wid].dsum = sbeam[wid].dabs[0] + sbeam[wid].dabs[1] + sbeam[wid].dabs[2];
             __syncwarp();
         }
         int ssp = 0, scur = __any_sync(FULL, active) ? 0 : DONE;     // shared walk: stack pointer and current link (uniform)
         int s_tests = 0, s_wanted = 0;                                // child tests made together / of them wanted by their lane
+        bool drain = false;                                           // (uniform) a private stack is about to fill up
         for (;;) {
         // ---- shared phase (left early when a private stack is about to fill up: deferred subtrees pile up there) ----
         if (scur != DONE) {
             for (;;) {
-                if (__any_sync(FULL, sp >= DST_ENUM_DEFER)) break;     // drain the private stacks first, then come back to scur
-                if (s_tests >= 64 * 32 && s_wanted * 100 < s_tests * share_min_pct && ssp + 1 <= DST_ENUM_STACK - DST_ENUM_DEFER - 40) {
+                if (drain) { drain = false; break; }                  // drain the private stacks first, then come back to scur
+                if (share_min_pct > 0 && s_tests >= 64 * 32 && s_wanted * 100 < s_tests * share_min_pct && ssp + 1 <= DST_ENUM_STACK - DST_ENUM_DEFER - 40) {
                     // these rays do not travel together (most lanes sit out most tests): every lane takes the
                     // pending subtrees onto its own stack and the batch continues lane by lane
                     if (active) {
@@ -538,9 +543,9 @@ __global__ void __launch_bounds__(ENUM_THREADS, DST_ENUM_MIN_BLOCKS) k_enum(BvhV
                     if (COUNT && lane == 0) tc.nodes++;
                     const bool w0 = active && h0, w1 = active && h1;
                     const unsigned int m0 = __ballot_sync(FULL, w0), m1 = __ballot_sync(FULL, w1);
-                    s_tests += 64; s_wanted += __popc(m0) + __popc(m1);
+                    if (share_min_pct > 0) { s_tests += 64; s_wanted += __popc(m0) + __popc(m1); }
                     RSTAT(1, 1); RSTAT(6, __popc(m0) + __popc(m1));
-                    const bool s0 = __popc(m0) >= DST_SHARE_VOTE, s1 = __popc(m1) >= DST_SHARE_VOTE;
+                    const bool s0 = DST_SHARE_VOTE <= 1 ? m0 != 0u : __popc(m0) >= DST_SHARE_VOTE, s1 = DST_SHARE_VOTE <= 1 ? m1 != 0u : __popc(m1) >= DST_SHARE_VOTE;
                     int next = DONE;
                     if (s0 && s1) {
                         // the majority of the lanes that want both decides which child comes first
@@ -548,14 +553,20 @@ __global__ void __launch_bounds__(ENUM_THREADS, DST_ENUM_MIN_BLOCKS) k_enum(BvhV
                         const bool first1 = 2 * __popc(pref1) > __popc(m0 & m1);
                         const int other = first1 ? l0 : l1;
                         if (ssp < DST_SHARED_STACK) { if (lane == 0) sstack[wid][ssp] = other; ssp++; }
-                        else if (first1 ? w0 : w1) push(other, first1 ? tn0 : tn1);       // shared stack full: defer privately
+                        else {                                                            // shared stack full: defer privately
+                            if (first1 ? w0 : w1) push(other, first1 ? tn0 : tn1);
+                            drain = __any_sync(FULL, sp >= DST_ENUM_DEFER);
+                        }
                         next = first1 ? l1 : l0;
                     } else {
-                        // children wanted by too few lanes go onto those lanes' own stacks (farther one first)
-                        const bool d0 = w0 && !s0, d1 = w1 && !s1;
-                        if (d0 && d1) { if (tn1 < tn0) { push(l0, tn0); push(l1, tn1); } else { push(l1, tn1); push(l0, tn0); } }
-                        else if (d0) push(l0, tn0);
-                        else if (d1) push(l1, tn1);
+                        if (DST_SHARE_VOTE > 1) {
+                            // children wanted by too few lanes go onto those lanes' own stacks (farther one first)
+                            const bool d0 = w0 && !s0, d1 = w1 && !s1;
+                            if (d0 && d1) { if (tn1 < tn0) { push(l0, tn0); push(l1, tn1); } else { push(l1, tn1); push(l0, tn0); } }
+                            else if (d0) push(l0, tn0);
+                            else if (d1) push(l1, tn1);
+                            drain = __any_sync(FULL, sp >= DST_ENUM_DEFER);
+                        }
                         if (s0) next = l0; else if (s1) next = l1;
                     }
                     if (next != DONE) { scur = next; continue; }
