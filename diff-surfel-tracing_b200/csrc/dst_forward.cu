@@ -14,7 +14,7 @@
 #define DST_ENUM_GRID_PER_SM 12       // blocks per SM of the forward gather and composite kernels (persistent: more blocks than fit just start later)
 #endif
 #ifndef DST_TAIL_DIV
-#define DST_TAIL_DIV 128             // the wavefront hands over to the tail kernel when fewer than rays / DST_TAIL_DIV
+#define DST_TAIL_DIV 64              // the wavefront hands over to the tail kernel when fewer than rays / DST_TAIL_DIV
 #define DST_TAIL_MIN 8192            // (but at least DST_TAIL_MIN, at most DST_WARP_TAIL_MAX_RAYS) rays are left
 #endif
 #ifndef DST_WARP_TAIL_MAX_RAYS
