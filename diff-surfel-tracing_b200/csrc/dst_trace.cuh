@@ -445,8 +445,8 @@ __global__ void __launch_bounds__(ENUM_THREADS, DST_ENUM_MIN_BLOCKS) k_enum(BvhV
         const float tf0 = fminf(fminf(fmaf(f0x, sl.ix, -sl.ofx), fmaf(f0y, sl.iy, -sl.ofy)), fmaf(f0z, sl.iz, -sl.ofz));
         tn1 = fmaxf(fmaxf(fmaf(n1x, sl.ix, -sl.onx), fmaf(n1y, sl.iy, -sl.ony)), fmaxf(fmaf(n1z, sl.iz, -sl.onz), 0.0f));
         const float tf1 = fminf(fminf(fmaf(f1x, sl.ix, -sl.ofx), fmaf(f1y, sl.iy, -sl.ofy)), fmaf(f1z, sl.iz, -sl.ofz));
-        h0 = (tn0 <= tf0) && (tn0 <= kmax);
-        h1 = (tn1 <= tf1) && (tn1 <= kmax);
+        h0 = tn0 <= fminf(tf0, kmax);
+        h1 = tn1 <= fminf(tf1, kmax);
         l0 = lk.z; l1 = lk.w;
     };
     // exact test of one quad and insertion into this lane's k-buffer
@@ -541,7 +541,7 @@ __global__ void __launch_bounds__(ENUM_THREADS, DST_ENUM_MIN_BLOCKS) k_enum(BvhV
                     float tn0, tn1; bool h0, h1; int l0, l1;
                     test_node(scur, tn0, tn1, h0, h1, l0, l1);
                     if (COUNT && lane == 0) tc.nodes++;
-                    const bool w0 = active && h0, w1 = active && h1;
+                    const bool w0 = h0, w1 = h1;           // (a lane without a ray has kmax = -1 and every tn is >= 0: it never wants a child)
                     const unsigned int m0 = __ballot_sync(FULL, w0), m1 = __ballot_sync(FULL, w1);
                     if (share_min_pct > 0) { s_tests += 64; s_wanted += __popc(m0) + __popc(m1); }
                     RSTAT(1, 1); RSTAT(6, __popc(m0) + __popc(m1));
@@ -590,7 +590,7 @@ __global__ void __launch_bounds__(ENUM_THREADS, DST_ENUM_MIN_BLOCKS) k_enum(BvhV
                         qa = __ldg(qp); qb = __ldg(qp + 1); qc = __ldg(qp + 2);
                         qgid = (unsigned int)__ldg(bvh.leaf_gid + first + lane);
                     }
-                    const float krun = wmax_f(active ? kmax : -1.0f);
+                    const float krun = wmax_f(kmax);        // (-1 on lanes without a ray)
                     unsigned int maybe = __ballot_sync(FULL, mine && hull_quad(sbeam[wid], qa, qb, qc, krun));
                     RSTAT(4, count);
                     while (maybe) {
