@@ -270,7 +270,8 @@ int dst_debug_knearest(dst_handle* h, const float* ray_o, const float* ray_d, in
                        unsigned long long* keys, int32_t* counts, int brute, const float* t_cut,
                        unsigned long long* counters, void* stream);
 /* Diagnostics: synchronises `stream` and copies the live-list length of every wavefront round of the last trace
- * call (host array of `cap` ints; round r of the call saw counts[r] rays, 0 from the first unused round on). */
+ * call (host array of `cap` ints; round r of the call saw counts[r] rays, 0 from the first unused round on; for a
+ * forward that ran as slices, the sum over the slices' rounds r). */
 int dst_debug_round_counts(dst_handle* h, int32_t* counts, int32_t cap, void* stream);
 /* Diagnostics: bandwidth of repeated streaming reads (16-byte loads that bypass L1) of a zeroed scratch buffer of
  * `bytes` bytes, `reps` passes, timed with CUDA events on `stream` after a warming pass; allocates and frees
