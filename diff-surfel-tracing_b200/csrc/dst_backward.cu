@@ -170,6 +170,15 @@ __device__ __forceinline__ bool bulk_stage_aggregate(const BulkStage& b, int gid
 // before the kernel ends: every row has been read from shared memory and added
 __device__ __forceinline__ void bulk_stage_drain() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+// The colour of a contribution as the backward needs it: a factor of gradients, not an input of a decision, so the sum
+// may be fused (the forward's sh_channel() rounds every product and sum as the reference does: twice the instructions).
+__device__ __forceinline__ float sh_channel_fused(int ncoef, const float* b, const float* c, int ch) {
+    float r = b[0] * c[ch];
+#pragma unroll
+    for (int j = 1; j < 16; j++) if (j < ncoef) r = fmaf(b[j], c[3 * j + ch], r);
+    return r + 0.5f;
+}
+
 struct V3 { float x, y, z; };
 __device__ __forceinline__ V3 v3(float x, float y, float z) { V3 r; r.x = x; r.y = y; r.z = z; return r; }
 __device__ __forceinline__ V3 operator+(V3 a, V3 b) { return v3(a.x + b.x, a.y + b.y, a.z + b.z); }
@@ -411,7 +420,7 @@ __device__ __forceinline__ bool bwd_shade(const BwdParams& p, int ray, BwdState&
         const V3 pm = v3(__ldg(in.means3D + 3 * (size_t)gidx), __ldg(in.means3D + 3 * (size_t)gidx + 1), __ldg(in.means3D + 3 * (size_t)gidx + 2));
         const float4 q = __ldg(reinterpret_cast<const float4*>(in.rotations) + gidx);
         if (use_sh) {
-            c0 = sh_channel(ncoef, sb, csh, 0); c1 = sh_channel(ncoef, sb, csh, 1); c2 = sh_channel(ncoef, sb, csh, 2);
+            c0 = sh_channel_fused(ncoef, sb, csh, 0); c1 = sh_channel_fused(ncoef, sb, csh, 1); c2 = sh_channel_fused(ncoef, sb, csh, 2);
             k0 = c0 < 0.f ? 0.f : 1.f; k1 = c1 < 0.f ? 0.f : 1.f; k2 = c2 < 0.f ? 0.f : 1.f;
             c0 = fmaxf(c0, 0.f); c1 = fmaxf(c1, 0.f); c2 = fmaxf(c2, 0.f);
         } else { c0 = pc0; c1 = pc1; c2 = pc2; }
