@@ -111,6 +111,9 @@ int dst_destroy(dst_handle* h) {
     cudaFree(h->log_keys); cudaFree(h->log_hdr); cudaFree(h->log_count); cudaFree(h->log_seg_head); cudaFree(h->log_ray_ok);
     cudaFree(h->wf_state); cudaFree(h->wf_req); cudaFree(h->wf_kbuf); cudaFree(h->wf_kcnt); cudaFree(h->wf_list[0]); cudaFree(h->wf_list[1]); cudaFree(h->wf_counts);
     cudaFree(h->wf_tmp); cudaFree(h->wf_wcnt); cudaFree(h->wf_bcnt);
+    cudaFree(h->bound_stats);
+    if (h->bound_host) cudaFreeHost(h->bound_host);
+    if (h->bound_event) cudaEventDestroy(h->bound_event);
     if (h->slice_streams_ready) {
         cudaEventDestroy(h->slice_fork);
         for (int g = 0; g < DST_MAX_SLICES - 1; g++) { cudaStreamDestroy(h->slice_stream[g]); cudaEventDestroy(h->slice_join[g]); }

@@ -94,6 +94,10 @@ struct dst_handle {
     cudaStream_t slice_stream[DST_MAX_SLICES - 1];
     cudaEvent_t slice_fork, slice_join[DST_MAX_SLICES - 1];
     bool slice_streams_ready;
+    // Predicted search bounds of the forward gather (forward_common): device counters {bounded searches, of them failed} of
+    // the current call, their pinned read-back, and how many coming calls leave the prediction off after a call in which it
+    // failed too often.
+    int* bound_stats; int* bound_host; cudaEvent_t bound_event; bool bound_pending; int bound_off_calls;
     // chunk log: the 16-hit chunks every ray composited in the last training forward, chained per ray and segment,
     // so that the backward re-composites them without walking the hierarchy again
     unsigned long long* log_keys; int2* log_hdr; int* log_count; int* log_seg_head; unsigned char* log_ray_ok;

@@ -26,6 +26,10 @@
 #ifndef DST_SLICE_MIN_SLOTS
 #define DST_SLICE_MIN_SLOTS 262144     // a slice is at least this many ray slots
 #endif
+#ifndef DST_BOUND_FACTOR
+#define DST_BOUND_FACTOR 3.0f         // search bound of a continuing segment in units of the previous chunk's span (0: none)
+#endif
+#define DST_BOUND_OFF_CALLS 64        // calls without predicted bounds after a call in which they failed too often
 #ifndef DST_SHADE_GRID_PER_SM
 #define DST_SHADE_GRID_PER_SM 4        // what fits an SM at once at 128 registers (measured: 8 is 2.5 % slower on the headline workload)
 #endif
@@ -56,6 +60,8 @@ struct FwdParams {
     unsigned int* status;
     int tiled, grid_h, grid_w;      // ray order: 8x4 tiles over a grid_h x grid_w pixel grid, or linear
     long long slot0;                // first ray slot of the slice these lists belong to (see forward_common)
+    int* bound_stats;               // {bounded searches issued, of them failed} in this call, or null: no predicted bounds
+    float bound_factor;
     // wavefront scratch
     void* state;
     EnumReq* req;
@@ -384,21 +390,52 @@ __global__ void __launch_bounds__(SHADE_THREADS) k_fwd_shade(const __grid_consta
     int* next_list = p.list[(round + 1) & 1];
     TraceCounters tc = { 0, 0, 0, 0, 0, 0 };
     const int n_pad = (n + 31) & ~31;
+    // Predicted bounds stay on while they hold: where rays run out of hits (a sparse scene, the rim of an object) a bounded
+    // search that comes back short has to be repeated, and past one failure in twelve the repeats cost more than the bounds save.
+    bool bound_on = false;
+    if (p.bound_stats && p.bound_factor > 0.0f) {
+        const int issued = __ldcg(p.bound_stats), fails = __ldcg(p.bound_stats + 1);
+        bound_on = issued < 4096 || fails * 12 < issued;
+    }
     for (int i = blockIdx.x * SHADE_THREADS + threadIdx.x; i < n_pad; i += gridDim.x * SHADE_THREADS) {
         const int ray = i < n ? list[i] : -1;
-        bool alive = false;
+        bool alive = false, bounded = false, failed = false;
         int cls = 0;
         if (ray >= 0) {
             FwdState s;
             load_state(p.state, ray, s);
-            alive = fwd_shade<DIAG, 1>(p, ray, s, p.kbuf + (size_t)ray * DST_CHUNK, p.kcnt[ray], tc);
-            if (alive) {
-                store_state(p.state, ray, s);
-                EnumReq q;
-                fwd_request(s, q);
-                p.req[ray] = q;
+            const unsigned long long* kb = p.kbuf + (size_t)ray * DST_CHUNK;
+            const int cnt = p.kcnt[ray];
+            if (cnt < DST_CHUNK && p.req[ray].kmax0 < DST_T_MAX) {
+                // The gather searched within a predicted distance (below) and found fewer than 16 hits there: that says nothing
+                // about what lies beyond. Nothing is composited; the same request goes out again without a bound.
+                p.req[ray].kmax0 = DST_T_MAX;
+                alive = true;
                 cls = s.bounce > 0;
+                failed = true;
+                if (DIAG && p.a.counters) atomicAdd(p.a.counters + 1, ~0ull);        // (the counter reports completed enumerations)
+            } else {
+                alive = fwd_shade<DIAG, 1>(p, ray, s, kb, cnt, tc);
+                if (alive) {
+                    store_state(p.state, ray, s);
+                    EnumReq q;
+                    fwd_request(s, q);
+                    // A segment that goes on: its next 16 hits are searched within bound_factor times the distance the last 16
+                    // spanned (first to last). A walk that knows its bound from the start opens a fifth fewer nodes than one that
+                    // learns it from its 16th hit; the spans of consecutive chunks differ by less than that factor for all but
+                    // a per cent of the rays of a dense scene, and those search again.
+                    if (bound_on && s.chunk > 0 && cnt == DST_CHUNK) {
+                        q.kmax0 = fmaxf(p.bound_factor * (hitkey_t(kb[DST_CHUNK - 1]) - hitkey_t(kb[0])), 1e-4f);
+                        bounded = true;
+                    }
+                    p.req[ray] = q;
+                    cls = s.bounce > 0;
+                }
             }
+        }
+        if (p.bound_stats) {
+            const unsigned int mb = __ballot_sync(0xffffffffu, bounded), mf = __ballot_sync(0xffffffffu, failed);
+            if ((threadIdx.x & 31) == 0) { if (mb) atomicAdd(p.bound_stats, __popc(mb)); if (mf) atomicAdd(p.bound_stats + 1, __popc(mf)); }
         }
         if (p.lv.stable) live_out(p.lv, round, i, alive, ray, cls);
         else append_alive(alive, ray, next_list, p.counts + round + 1);
@@ -751,6 +788,21 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
         }
     }
     const bool diag = a->hit_log || a->hit_cnt || a->counters;
+    // predicted search bounds: on unless the last call that used them saw them fail too often (read back without synchronising)
+    p.bound_stats = nullptr; p.bound_factor = 0.0f;
+    if (wave && DST_BOUND_FACTOR > 0.0f) {
+        if (!h->bound_stats) {
+            if (cudaMalloc(&h->bound_stats, 8) != cudaSuccess) { cudaGetLastError(); h->bound_stats = nullptr; }
+            if (h->bound_stats && cudaMallocHost(&h->bound_host, 8) != cudaSuccess) { cudaGetLastError(); h->bound_host = nullptr; }
+            if (h->bound_host && cudaEventCreateWithFlags(&h->bound_event, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); h->bound_event = nullptr; }
+        }
+        if (h->bound_pending && h->bound_event && cudaEventQuery(h->bound_event) == cudaSuccess) {
+            h->bound_pending = false;
+            if (h->bound_host[0] >= 4096 && (long long)h->bound_host[1] * 12 >= h->bound_host[0]) h->bound_off_calls = DST_BOUND_OFF_CALLS;
+        } else cudaGetLastError();
+        if (h->bound_off_calls > 0) h->bound_off_calls--;
+        else if (h->bound_stats) { p.bound_stats = h->bound_stats; p.bound_factor = DST_BOUND_FACTOR; DST_CUDA_TRY(h, cudaMemsetAsync(h->bound_stats, 0, 8, st)); }
+    }
     DST_CUDA_TRY(h, cudaMemsetAsync(h->wf_counts, 0, 4 * (size_t)DST_COUNTS_STRIDE * DST_MAX_SLICES, st));
     rc = dst_live_lists(h, slots, &p.lv, st);
     if (rc != DST_OK) return rc;
@@ -827,6 +879,11 @@ static int forward_common(dst_handle* h, const dst_fwd_args* a, const dst_camera
             cudaEventRecord(h->rounds_event, st);
             h->rounds_pending_sig = sig; h->rounds_pending_min = p.min_count;
         }
+    }
+    if (p.bound_stats && h->bound_host && h->bound_event && !h->bound_pending) {
+        cudaMemcpyAsync(h->bound_host, h->bound_stats, 8, cudaMemcpyDeviceToHost, st);
+        cudaEventRecord(h->bound_event, st);
+        h->bound_pending = true;
     }
     if (p.log_keys) {
         // how many records this call wanted, for sizing the log of the next one (no synchronisation here)
@@ -910,7 +967,7 @@ extern "C" int dst_forward_static(dst_handle* h, const dst_fwd_args* a, void* st
     FwdParams p;
     p.a = *a; p.bvh = dst_bvh_view(h); p.status = h->status; p.tiled = tiled; p.grid_h = a->in.H; p.grid_w = a->in.W;
     p.cam_on = 0; memset(&p.cam, 0, sizeof(p.cam));
-    p.slot0 = 0;
+    p.slot0 = 0; p.bound_stats = nullptr; p.bound_factor = 0.0f;
     p.dist_on = h->distortion;
     p.cache = reinterpret_cast<const float4*>(base + ST_OFF_CACHE);
     p.state = base + ST_OFF_STATE;
