@@ -319,8 +319,9 @@ __device__ __forceinline__ RaySlab make_slab(float ox, float oy, float oz, float
 //                  takes the pending subtrees onto its own stack (see DST_SHARE_MIN_PCT_TILED above).
 //   private phase  every lane drains its own stack as in knearest(), lanes alternating between a node phase (kept
 //                  while at least DST_NODE_VOTE lanes have node work) and a leaf phase.
-// Pruning uses each lane's own 16th-nearest distance throughout and the hull test is conservative, so the hit set is
-// exactly that of an independent walk per ray. Blocks are persistent and take batches from a shared cursor.
+// Pruning uses each lane's own 16th-nearest distance throughout (before a lane has 16 hits: the bound its request carries,
+// see k_fwd_shade, or none) and the hull test is conservative, so the hit set is exactly that of an independent walk per
+// ray within that bound. Blocks are persistent and take batches from a shared cursor.
 #define DST_SHARED_STACK 64
 #define DST_ENUM_STACK 160       // private stack of k_enum: subtrees deferred by the shared walk + one depth-first descent
 #define DST_ENUM_DEFER 64        // the shared walk pauses to drain the private stacks when a lane holds this many entries
